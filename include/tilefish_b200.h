@@ -1,0 +1,128 @@
+/*
+ * tilefish_b200 -- C ABI of the sm_100a backend for tilefish's quantized-inference hot path.
+ *
+ * Conventions (modelled on the reference's C ABI, crates/tilefish-capi/include/tilefish.h:388-430 and
+ * crates/tilefish-capi/src/error.rs:14-102):
+ *   - every entry point returns a tf_status (0 = OK); tf_last_error() gives the message of the last failure on the
+ *     calling thread;
+ *   - tensors are regions the caller vouches for: plain device pointers plus sizes, caller-owned, caller-ordered;
+ *   - the stream is a borrowed CUDA stream handle (NULL = the legacy default stream); calls only enqueue work and
+ *     never synchronize or allocate, unless their comment says otherwise; the CUDA context is left as found;
+ *   - nothing is allocated inside a launch: scratch memory is passed in as a workspace;
+ *   - no C++ exception crosses the boundary.
+ *
+ * The reference binds this path through three leaves, which these entry points replace:
+ *   - a Triton cubin launched with cuLaunchKernel  (python/src/tilefish/_cuda.py:356-458)  -> the row kernels below;
+ *   - a pinned cublasLtMatmul                      (python/src/tilefish/_cublaslt.py:1372-1455) -> tf_gemm_blockscaled;
+ *   - the runner back-end interface                (python/src/tilefish/_planrun.py:240-376: launch / gemm).
+ */
+#ifndef TILEFISH_B200_H
+#define TILEFISH_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define TF_API __attribute__((visibility("default")))
+#else
+#define TF_API
+#endif
+
+typedef int32_t tf_status;
+
+enum {
+  TF_OK = 0,
+  TF_ERR_INVALID_ARGUMENT = 1, /* null pointer, negative size, unknown enum value */
+  TF_ERR_ALIGNMENT = 2,        /* a pointer or leading dimension is not aligned as the entry point requires */
+  TF_ERR_UNSUPPORTED = 3,      /* a shape this build has no kernel for (K not a multiple of the block, D too large ...) */
+  TF_ERR_CUDA = 4,             /* a CUDA runtime/driver call failed; the message carries its error string */
+  TF_ERR_WORKSPACE = 5,        /* the workspace is too small (see the *_workspace_bytes query) */
+  TF_ERR_DEVICE_TIMEOUT = 6    /* a bounded wait inside a kernel ran out (read by tf_device_status) */
+};
+
+/* BlockScaled formats (python/src/tilefish/dtypes.py:145-232; README.md:47-49 of the reference). */
+enum {
+  TF_FMT_MXFP8 = 0, /* e4m3 elements, ue8m0 scale, block 32 */
+  TF_FMT_MXFP4 = 1, /* e2m1 elements (two per byte, element 2i in bits 0-3), ue8m0 scale, block 32 */
+  TF_FMT_NVFP4 = 2  /* e2m1 elements, e4m3 scale, block 16, f32 global scale */
+};
+
+/* Scale-byte layouts. PLAIN is row-major [rows, K/block]. SWIZZLED is the sm_100 block-scaled MMA operand layout:
+ * 128-row x 4-column tiles of 512 bytes, row-tile major; inside a tile byte(r, c) = (r%32)*16 + (r/32)*4 + c; rows are
+ * padded to 128 and columns to 4 with zero bytes. */
+enum { TF_SCALES_PLAIN = 0, TF_SCALES_SWIZZLED = 1 };
+
+/* GEMM epilogues. */
+enum {
+  TF_EPI_NONE = 0,      /* out[M,N] = bf16(acc) */
+  TF_EPI_SILU_GATE = 1, /* b holds gate rows [0,N) then up rows [N,2N): out[M,N] = bf16(silu(bf16(acc_g)) * bf16(acc_u)) */
+  TF_EPI_RESIDUAL = 2   /* out[M,N] = bf16(acc); residual_f32[M,N] += f32(out) */
+};
+
+/* Library identity and errors. Replaces tilefish_version / tilefish_last_error (crates/tilefish-capi/src/error.rs:86-102). */
+TF_API const char* tf_version(void);
+TF_API const char* tf_last_error(void);
+
+/* Reads and clears the device-side status word that kernels with bounded waits set when a wait runs out.
+ * SYNCHRONIZES the device. *status is TF_OK or TF_ERR_DEVICE_TIMEOUT; *detail identifies the wait that gave up. */
+TF_API tf_status tf_device_status(int32_t* status, int32_t* detail);
+
+/* Bytes of the scale tensor of a [rows, k] operand in `format`, in `layout`. Returns -1 on a bad argument. */
+TF_API int64_t tf_scale_bytes(int32_t format, int64_t rows, int64_t k, int32_t layout);
+
+/* BlockScaled quantization of a bf16 matrix along its last axis. The reference types this operation but refuses to run
+ * it (python/src/tilefish/ops.py:556-559); these entry points are what `x.to(mxfp8)` lowers to here.
+ *   x        bf16 [m, k], row stride ldx elements (ldx >= k, ldx % 8 == 0), 16-byte aligned
+ *   codes    [m, k] bytes (mxfp8) or [m, k/2] bytes (fp4), dense, 16-byte aligned
+ *   scales   tf_scale_bytes(format, m, k, layout) bytes; with TF_SCALES_SWIZZLED the padding is zeroed by the call
+ *   k        a multiple of 32
+ * nvfp4: global_scale points to ONE f32 on the device holding amax(|x|)/2688 (tf_nvfp4_global_scale computes it). */
+TF_API tf_status tf_quantize_mxfp8(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout, void* stream);
+TF_API tf_status tf_quantize_mxfp4(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout, void* stream);
+TF_API tf_status tf_quantize_nvfp4(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout,
+                            const float* global_scale, void* stream);
+/* global_scale_out[0] = max|x| / 2688.0f (one IEEE division), computed on the device in stream order. */
+TF_API tf_status tf_nvfp4_global_scale(const void* x, int64_t m, int64_t k, int64_t ldx, float* global_scale_out, void* stream);
+
+/* Plain <-> swizzled scale bytes ([rows, cols] scale entries). The swizzled buffer's padding is zeroed. */
+TF_API tf_status tf_swizzle_scales(const void* plain, int64_t rows, int64_t cols, void* swizzled, void* stream);
+TF_API tf_status tf_unswizzle_scales(const void* swizzled, int64_t rows, int64_t cols, void* plain, void* stream);
+
+/* residual_add_rmsnorm (README.md:53-63 of the reference; its Triton lowering python/tests/golden/residual_add_rmsnorm.py):
+ *   r = residual + f32(x); residual <- r; out = bf16(r * rsqrt(mean(r*r) + eps) * f32(w)), mean = sum * f32(1/D).
+ *   x bf16 [m, d]; residual f32 [m, d] (updated in place); w bf16 [d]; all dense and 16-byte aligned; d % 8 == 0.
+ *   out      bf16 [m, d] or NULL when only the quantized output is wanted
+ *   q_format -1 for none, else a TF_FMT_*: the bf16 result is also quantized along d (d % 32 == 0) into q_codes/q_scales
+ *            exactly as tf_quantize_* would quantize `out`; nvfp4 needs q_global_scale (given, on the device). */
+TF_API tf_status tf_residual_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int64_t m, int64_t d, float eps,
+                                  int32_t q_format, void* q_codes, void* q_scales, int32_t q_layout, const float* q_global_scale,
+                                  void* stream);
+
+/* SiLU gate over the column halves of t (README.md:83-84; the fused region of python/src/tilefish/_fusion.py):
+ *   out[m, f] = bf16( silu(f32(t[m, j])) * f32(t[m, f + j]) ), silu(x) = x * (1 / (1 + exp(-x))).
+ *   t bf16 [m, 2f] with row stride ldt; out bf16 [m, f] with row stride ldo; f, ldt, ldo multiples of 8. */
+TF_API tf_status tf_silu_gate(const void* t, int64_t m, int64_t f, int64_t ldt, void* out, int64_t ldo, void* stream);
+
+/* Block-scaled GEMM on tcgen05 tensor cores: out[M,N] = bf16( sum_k deq(a)[m,k] * deq(b)[n,k] ), f32 accumulate.
+ * Replaces the pinned cublasLtMatmul of `@tilefish.library("gemm", acc=f32)` (python/src/tilefish/_library.py:9-16) for
+ * BlockScaled operands, which the reference cannot run.
+ *   a_codes [m, k] (or k/2) bytes, b_codes [n_rows, k] bytes, dense, 16-byte aligned, k % 32 == 0
+ *   a_scales, b_scales   SWIZZLED scale bytes of the two operands
+ *   a_global_scale, b_global_scale   device f32 (nvfp4) or NULL
+ *   out      bf16 [m, n] row stride ldo (ldo % 8 == 0)
+ *   epilogue TF_EPI_*: with TF_EPI_SILU_GATE b has 2n rows (n % 128 == 0); with TF_EPI_RESIDUAL epilogue_arg is the f32
+ *            residual [m, n] (dense)
+ *   workspace / workspace_bytes   at least tf_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when 0) */
+TF_API int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue);
+TF_API tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
+                              const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
+                              int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, void* workspace,
+                              int64_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TILEFISH_B200_H */

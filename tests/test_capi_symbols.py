@@ -1,0 +1,56 @@
+"""The C-ABI library loads and exports every symbol include/tilefish_b200.h declares (no compute calls: runs without a GPU)."""
+
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "tilefish_b200.h")).read()
+    return sorted(set(re.findall(r"TF_API[^;(]*?\b(tf_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_declares_the_expected_entry_points():
+    names = declared_symbols()
+    for must in ("tf_quantize_mxfp8", "tf_quantize_mxfp4", "tf_quantize_nvfp4", "tf_residual_add_rmsnorm", "tf_silu_gate",
+                 "tf_gemm_blockscaled", "tf_swizzle_scales", "tf_last_error"):
+        assert must in names
+
+
+def test_library_exports_every_declared_symbol():
+    from tilefish_b200 import _native
+
+    if not os.path.exists(_native.LIB_PATH):
+        pytest.skip("library not built here (python tilefish_b200/csrc/build.py)")
+    lib = _native.load()
+    for name in declared_symbols():
+        assert hasattr(lib, name), name
+        assert name in _native.SIGNATURES, f"{name} has no ctypes signature"
+    assert set(_native.SIGNATURES) == set(declared_symbols())
+    assert _native.version().startswith("tilefish_b200")
+
+
+def test_host_only_queries():
+    from tilefish_b200 import _native
+
+    if not os.path.exists(_native.LIB_PATH):
+        pytest.skip("library not built here")
+    assert _native.scale_bytes(_native.FMT_MXFP8, 256, 4096, _native.SCALES_PLAIN) == 256 * 128
+    assert _native.scale_bytes(_native.FMT_NVFP4, 1, 64, _native.SCALES_SWIZZLED) == 512
+    assert _native.scale_bytes(_native.FMT_MXFP4, 129, 160, _native.SCALES_SWIZZLED) == 2 * 2 * 512
+    from tilefish_b200 import TilefishPreconditionError
+
+    with pytest.raises(TilefishPreconditionError):
+        _native.scale_bytes(7, 1, 32, 0)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    from tilefish_b200 import TilefishRuntimeError, _native
+
+    monkeypatch.setattr(_native, "_lib", None)
+    monkeypatch.setattr(_native, "LIB_PATH", str(tmp_path / "nope.so"))
+    with pytest.raises(TilefishRuntimeError, match="no CPU or Triton fallback"):
+        _native.load()

@@ -1,0 +1,83 @@
+// Per-thread core of the BlockScaled quantizers: one thread owns 8 consecutive bf16 values (one 128-bit load); the
+// 4 (block 32) or 2 (block 16) adjacent lanes that share a scale block combine their maxima with warp shuffles.
+//
+// Every arithmetic step is a single correctly rounded f32 operation or an integer operation, in a fixed order, so the
+// bytes are the same as the torch restatement's:
+//   MX     amax on the 15 magnitude bits; E = amax >> 7; scale = amax == 0 ? 127 : max(E - emax, 0);
+//          code = cast(f32(x) * 2^(127 - scale))                      (exact product)
+//   NVFP4  s8 = e4m3(amax / (6 * gs)); d = f32(s8) * gs; code = e2m1(f32(x) * (1 / d)); zero when gs == 0 or d == 0
+#pragma once
+
+#include "common.cuh"
+
+namespace tf {
+
+// Maximum of the 15 magnitude bits of the 8 bf16 words of v.
+__device__ __forceinline__ uint32_t amax_bits8(const uint4& v) {
+  uint32_t m = max(v.x & 0x7FFFu, (v.x >> 16) & 0x7FFFu);
+  m = max(m, max(v.y & 0x7FFFu, (v.y >> 16) & 0x7FFFu));
+  m = max(m, max(v.z & 0x7FFFu, (v.z >> 16) & 0x7FFFu));
+  m = max(m, max(v.w & 0x7FFFu, (v.w >> 16) & 0x7FFFu));
+  return m;
+}
+
+// Quantizes the 8 bf16 values of `v`. All 32 lanes of the warp must call it together (lanes without data pass zeros).
+// Returns the packed codes in c0 (and c1 for 8-bit elements) and the scale byte of the lane's block.
+template <int FMT>
+__device__ __forceinline__ void quantize_vec8(const uint4& v, float gs, uint32_t& c0, uint32_t& c1, uint32_t& scale) {
+  uint32_t m = amax_bits8(v);
+  m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+  if (FMT != TF_FMT_NVFP4) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
+
+  float inv;
+  bool zero = false;
+  if (FMT == TF_FMT_NVFP4) {
+    const float amax = __uint_as_float(m << 16);
+    uint32_t s8 = 0;
+    if (gs != 0.0f) s8 = cvt_e4m3x2(__fdiv_rn(amax, __fmul_rn(6.0f, gs)), 0.0f) & 0xFFu;
+    const float d = __fmul_rn(e4m3_to_f32(s8), gs);
+    zero = (d == 0.0f);
+    inv = zero ? 0.0f : __fdiv_rn(1.0f, d);
+    scale = s8;
+  } else {
+    const int emax = (FMT == TF_FMT_MXFP8) ? 8 : 2;
+    const int e = (int)(m >> 7) - emax;
+    scale = (m == 0) ? 127u : (uint32_t)max(e, 0);
+    inv = __uint_as_float((254u - scale) << 23);
+  }
+
+  const float f0 = __fmul_rn(bf16lo_to_f32(v.x), inv), f1 = __fmul_rn(bf16hi_to_f32(v.x), inv);
+  const float f2 = __fmul_rn(bf16lo_to_f32(v.y), inv), f3 = __fmul_rn(bf16hi_to_f32(v.y), inv);
+  const float f4 = __fmul_rn(bf16lo_to_f32(v.z), inv), f5 = __fmul_rn(bf16hi_to_f32(v.z), inv);
+  const float f6 = __fmul_rn(bf16lo_to_f32(v.w), inv), f7 = __fmul_rn(bf16hi_to_f32(v.w), inv);
+  if (FMT == TF_FMT_MXFP8) {
+    c0 = cvt_e4m3x2(f0, f1) | (cvt_e4m3x2(f2, f3) << 16);
+    c1 = cvt_e4m3x2(f4, f5) | (cvt_e4m3x2(f6, f7) << 16);
+  } else {
+    c0 = cvt_e2m1x2(f0, f1) | (cvt_e2m1x2(f2, f3) << 8) | (cvt_e2m1x2(f4, f5) << 16) | (cvt_e2m1x2(f6, f7) << 24);
+    if (zero) c0 = 0;
+    c1 = 0;
+  }
+}
+
+// Stores one thread's codes (8 elements starting at element column `col` of row `row`) and, from the first lane of each
+// block, the scale byte. `vec` is the index of the 8-element vector inside the row.
+template <int FMT>
+__device__ __forceinline__ void store_quantized(uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int swizzled,
+                                                int64_t row, int vec, int64_t k, uint32_t c0, uint32_t c1, uint32_t scale) {
+  if (FMT == TF_FMT_MXFP8) {
+    *reinterpret_cast<uint2*>(codes + row * k + (int64_t)vec * 8) = make_uint2(c0, c1);
+  } else {
+    *reinterpret_cast<uint32_t*>(codes + row * (k >> 1) + (int64_t)vec * 4) = c0;
+  }
+  const int lanes_per_block = (FMT == TF_FMT_NVFP4) ? 2 : 4;
+  if ((vec & (lanes_per_block - 1)) == 0) {
+    const int blk = (FMT == TF_FMT_NVFP4) ? 16 : 32;
+    const int64_t cols = k / blk;
+    const int64_t c = vec / lanes_per_block;
+    const int64_t off = swizzled ? swizzled_scale_offset(row, c, (cols + 3) >> 2) : row * cols + c;
+    scales[off] = (uint8_t)scale;
+  }
+}
+
+}  // namespace tf

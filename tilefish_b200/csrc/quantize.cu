@@ -1,0 +1,210 @@
+// BlockScaled quantization row kernels (bf16 -> MXFP8 / MXFP4 / NVFP4) and the scale-layout helpers.
+//
+// HBM-bound: every thread moves one 128-bit vector of 8 bf16 per step (coalesced: consecutive lanes, consecutive
+// vectors), block maxima are combined with warp shuffles, codes leave as 8-byte (e4m3) or 4-byte (e2m1) coalesced
+// stores. Algorithmic bytes per element: 2 + 1 + 1/32 (mxfp8), 2 + 0.5 + 1/32 (mxfp4), 2 + 0.5 + 1/16 (nvfp4).
+#include "quant_core.cuh"
+
+namespace tf {
+
+constexpr int kQuantThreads = 256;
+constexpr int kQuantUnroll = 4;
+
+// Block = (TPR threads along the row) x (256 / TPR rows); rows are taken grid-stride.
+template <int FMT>
+__global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint4* __restrict__ x, int64_t m, int64_t k, int64_t ldx_vec,
+                                                                      uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                                                                      int swizzled, const float* __restrict__ gs_ptr) {
+  const int tpr = blockDim.x;
+  const int nvec = (int)(k >> 3);
+  const float gs = (FMT == TF_FMT_NVFP4) ? __ldg(gs_ptr) : 0.0f;
+  const int64_t row_stride = (int64_t)gridDim.x * blockDim.y;
+  // Both loops run the same number of times for every thread of the block, so the warp shuffles inside quantize_vec8 always
+  // see whole warps; threads without data (row >= m or vector >= nvec) quantize zeros and store nothing. nvec is a
+  // multiple of 4 and tpr a power of two >= 4, so the lanes of one scale block have data together.
+  for (int64_t row_base = (int64_t)blockIdx.x * blockDim.y; row_base < m; row_base += row_stride) {
+    const int64_t row = row_base + threadIdx.y;
+    const bool row_ok = row < m;
+    const uint4* xr = x + (row_ok ? row : 0) * ldx_vec;
+    for (int base = 0; base < nvec; base += kQuantUnroll * tpr) {  // kQuantUnroll 128-bit loads in flight per thread
+      uint4 v[kQuantUnroll];
+      bool has[kQuantUnroll];
+#pragma unroll
+      for (int j = 0; j < kQuantUnroll; ++j) {
+        const int vj = base + threadIdx.x + j * tpr;
+        has[j] = row_ok && vj < nvec;
+        v[j] = has[j] ? __ldcs(xr + vj) : make_uint4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int j = 0; j < kQuantUnroll; ++j) {
+        if (base + j * tpr < nvec) {  // uniform over the block
+          uint32_t c0, c1, sc;
+          quantize_vec8<FMT>(v[j], gs, c0, c1, sc);
+          if (has[j]) store_quantized<FMT>(codes, scales, swizzled, row, base + threadIdx.x + j * tpr, k, c0, c1, sc);
+        }
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) amax_bits_kernel(const uint4* __restrict__ x, int64_t m, int nvec, int64_t ldx_vec,
+                                                        unsigned int* __restrict__ out_bits) {
+  uint32_t mx = 0;
+  const int64_t total = m * nvec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  const bool dense = ldx_vec == nvec;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {  // four loads in flight
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t i = i0 + j * stride;
+      if (i < total) {
+        int64_t off = i;
+        if (!dense) {
+          const int64_t row = i / nvec;
+          off = row * ldx_vec + (i - row * nvec);
+        }
+        v[j] = __ldcs(x + off);
+      } else {
+        v[j] = make_uint4(0, 0, 0, 0);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mx = max(mx, amax_bits8(v[j]));
+  }
+  for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+  __shared__ uint32_t warp_max[8];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = mx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) mx = max(mx, warp_max[w]);
+    if (mx) atomicMax(out_bits, mx << 16);  // the f32 bit pattern of a non-negative bf16 orders like the integer
+  }
+}
+
+__global__ void finalize_global_scale_kernel(float* gs) { gs[0] = __fdiv_rn(gs[0], 2688.0f); }
+
+__global__ void __launch_bounds__(256) swizzle_kernel(const uint8_t* __restrict__ src, uint8_t* __restrict__ dst, int64_t rows, int64_t cols,
+                                                      int to_swizzled) {
+  const int64_t n_ct = (cols + 3) >> 2;
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / cols, c = i - r * cols;
+    const int64_t off = swizzled_scale_offset(r, c, n_ct);
+    if (to_swizzled) dst[off] = src[i];
+    else dst[i] = src[off];
+  }
+}
+
+static int block_of(int format) { return format == TF_FMT_NVFP4 ? 16 : 32; }
+
+static tf_status check_quant_args(const char* fn, const void* x, int64_t m, int64_t k, int64_t ldx, const void* codes, const void* scales,
+                                  int layout) {
+  if (!x || !codes || !scales) return fail(TF_ERR_INVALID_ARGUMENT, "%s: null pointer", fn);
+  if (m < 0 || k <= 0) return fail(TF_ERR_INVALID_ARGUMENT, "%s: bad shape m=%lld k=%lld", fn, (long long)m, (long long)k);
+  if (layout != TF_SCALES_PLAIN && layout != TF_SCALES_SWIZZLED) return fail(TF_ERR_INVALID_ARGUMENT, "%s: unknown scale layout %d", fn, layout);
+  if (k % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: k=%lld is not a multiple of 32", fn, (long long)k);
+  if (ldx < k || ldx % 8 != 0) return fail(TF_ERR_ALIGNMENT, "%s: ldx=%lld must be >= k and a multiple of 8", fn, (long long)ldx);
+  if (k > (int64_t)1 << 30) return fail(TF_ERR_UNSUPPORTED, "%s: k too large", fn);
+  if ((uintptr_t)x % 16 || (uintptr_t)codes % 16) return fail(TF_ERR_ALIGNMENT, "%s: x and codes must be 16-byte aligned", fn);
+  return TF_OK;
+}
+
+template <int FMT>
+static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int layout,
+                                 const float* gs, cudaStream_t stream) {
+  tf_status st = check_quant_args(fn, x, m, k, ldx, codes, scales, layout);
+  if (st != TF_OK) return st;
+  if (FMT == TF_FMT_NVFP4 && !gs) return fail(TF_ERR_INVALID_ARGUMENT, "%s: nvfp4 needs a global scale", fn);
+  if (m == 0) return TF_OK;
+  const int64_t cols = k / block_of(FMT);
+  if (layout == TF_SCALES_SWIZZLED && ((m & 127) || (cols & 3)))
+    TF_CUDA(cudaMemsetAsync(scales, 0, (size_t)tf_scale_bytes(FMT, m, k, layout), stream));
+  int tpr = 4;
+  while (tpr < kQuantThreads && tpr * kQuantUnroll < (k >> 3)) tpr <<= 1;
+  const int rpb = kQuantThreads / tpr;
+  const int64_t blocks_needed = (m + rpb - 1) / rpb;
+  const int64_t cap = (int64_t)sm_count() * 8;
+  dim3 block(tpr, rpb);
+  dim3 grid((unsigned)(blocks_needed < cap ? blocks_needed : cap));
+  quantize_rows_kernel<FMT><<<grid, block, 0, stream>>>(static_cast<const uint4*>(x), m, k, ldx >> 3, static_cast<uint8_t*>(codes),
+                                                        static_cast<uint8_t*>(scales), layout == TF_SCALES_SWIZZLED, gs);
+  TF_LAUNCH_CHECK();
+  return TF_OK;
+}
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" {
+
+int64_t tf_scale_bytes(int32_t format, int64_t rows, int64_t k, int32_t layout) {
+  if (format < TF_FMT_MXFP8 || format > TF_FMT_NVFP4 || rows < 0 || k < 0) return -1;
+  const int64_t blk = block_of(format);
+  if (k % blk) return -1;
+  const int64_t cols = k / blk;
+  if (layout == TF_SCALES_PLAIN) return rows * cols;
+  if (layout == TF_SCALES_SWIZZLED) return ((rows + 127) / 128) * ((cols + 3) / 4) * 512;
+  return -1;
+}
+
+tf_status tf_quantize_mxfp8(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout, void* stream) {
+  clear_error();
+  return launch_quantize<TF_FMT_MXFP8>(__func__, x, m, k, ldx, codes, scales, layout, nullptr, (cudaStream_t)stream);
+}
+tf_status tf_quantize_mxfp4(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout, void* stream) {
+  clear_error();
+  return launch_quantize<TF_FMT_MXFP4>(__func__, x, m, k, ldx, codes, scales, layout, nullptr, (cudaStream_t)stream);
+}
+tf_status tf_quantize_nvfp4(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout,
+                            const float* global_scale, void* stream) {
+  clear_error();
+  return launch_quantize<TF_FMT_NVFP4>(__func__, x, m, k, ldx, codes, scales, layout, global_scale, (cudaStream_t)stream);
+}
+
+tf_status tf_nvfp4_global_scale(const void* x, int64_t m, int64_t k, int64_t ldx, float* out, void* stream_) {
+  clear_error();
+  cudaStream_t stream = (cudaStream_t)stream_;
+  TF_CHECK_ARG(x && out, "%s: null pointer", __func__);
+  TF_CHECK_ARG(m >= 0 && k > 0 && k % 8 == 0 && ldx >= k && ldx % 8 == 0, "%s: bad shape", __func__);
+  TF_CHECK_ALIGNED(x, 16, "x");
+  TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float), stream));
+  if (m > 0) {
+    const int64_t total = m * (k >> 3);
+    const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
+    amax_bits_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, stream>>>(static_cast<const uint4*>(x), m, (int)(k >> 3), ldx >> 3,
+                                                                              reinterpret_cast<unsigned int*>(out));
+    TF_LAUNCH_CHECK();
+  }
+  finalize_global_scale_kernel<<<1, 1, 0, stream>>>(out);
+  TF_LAUNCH_CHECK();
+  return TF_OK;
+}
+
+static tf_status swizzle_impl(const char* fn, const void* src, void* dst, int64_t rows, int64_t cols, int to_swizzled, cudaStream_t stream) {
+  if (!src || !dst) return fail(TF_ERR_INVALID_ARGUMENT, "%s: null pointer", fn);
+  if (rows < 0 || cols < 0) return fail(TF_ERR_INVALID_ARGUMENT, "%s: bad shape", fn);
+  if (to_swizzled) {
+    const size_t bytes = (size_t)(((rows + 127) / 128) * ((cols + 3) / 4) * 512);
+    if (bytes) TF_CUDA(cudaMemsetAsync(dst, 0, bytes, stream));
+  }
+  const int64_t total = rows * cols;
+  if (total == 0) return TF_OK;
+  const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
+  swizzle_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, stream>>>(static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), rows,
+                                                                          cols, to_swizzled);
+  TF_LAUNCH_CHECK();
+  return TF_OK;
+}
+
+tf_status tf_swizzle_scales(const void* plain, int64_t rows, int64_t cols, void* swizzled, void* stream) {
+  clear_error();
+  return swizzle_impl(__func__, plain, swizzled, rows, cols, 1, (cudaStream_t)stream);
+}
+tf_status tf_unswizzle_scales(const void* swizzled, int64_t rows, int64_t cols, void* plain, void* stream) {
+  clear_error();
+  return swizzle_impl(__func__, swizzled, plain, rows, cols, 0, (cudaStream_t)stream);
+}
+
+}  // extern "C"

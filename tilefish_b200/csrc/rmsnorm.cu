@@ -1,0 +1,155 @@
+// residual_add_rmsnorm row kernel, optionally fused with the BlockScaled quantization of its bf16 result.
+//
+//   r = residual + f32(x)           one exact f32 add; written back to residual
+//   out = bf16(r * rstd * f32(w))   rstd = rsqrt(sum(r*r) * f32(1/D) + eps); the only rounding point is the bf16 cast
+//
+// HBM-bound: 12 bytes per element (2 read x, 4 read + 4 write residual, 2 write out), plus the quantized copy when asked
+// for. One block per row (grid-stride), 128-bit loads, the row's r values stay in registers between the reduction and the
+// normalisation, warp-shuffle + shared-memory block reduction.
+#include "quant_core.cuh"
+
+namespace tf {
+
+template <int VPT, int QFMT>  // VPT: 8-element vectors per thread; QFMT: -1 none, else TF_FMT_*
+__global__ void __launch_bounds__(512) residual_add_rmsnorm_kernel(const uint4* __restrict__ x, float4* __restrict__ residual,
+                                                                   const uint4* __restrict__ w, uint4* __restrict__ out, int64_t m, int d,
+                                                                   float eps, float inv_d, uint8_t* __restrict__ q_codes,
+                                                                   uint8_t* __restrict__ q_scales, int q_swizzled,
+                                                                   const float* __restrict__ q_gs_ptr) {
+  __shared__ float warp_sums[16];
+  __shared__ float row_rstd;
+  const int nvec = d >> 3;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const float gs = (QFMT == TF_FMT_NVFP4) ? __ldg(q_gs_ptr) : 0.0f;
+
+  for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
+    const uint4* xr = x + row * nvec;
+    float4* rr = residual + row * (nvec * 2);
+    float r[VPT][8];
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * nthreads;
+      if (v < nvec) {
+        const uint4 xv = __ldcs(xr + v);
+        const float4 a = __ldcs(rr + 2 * v), b = __ldcs(rr + 2 * v + 1);
+        r[i][0] = __fadd_rn(a.x, bf16lo_to_f32(xv.x));
+        r[i][1] = __fadd_rn(a.y, bf16hi_to_f32(xv.x));
+        r[i][2] = __fadd_rn(a.z, bf16lo_to_f32(xv.y));
+        r[i][3] = __fadd_rn(a.w, bf16hi_to_f32(xv.y));
+        r[i][4] = __fadd_rn(b.x, bf16lo_to_f32(xv.z));
+        r[i][5] = __fadd_rn(b.y, bf16hi_to_f32(xv.z));
+        r[i][6] = __fadd_rn(b.z, bf16lo_to_f32(xv.w));
+        r[i][7] = __fadd_rn(b.w, bf16hi_to_f32(xv.w));
+        __stcs(rr + 2 * v, make_float4(r[i][0], r[i][1], r[i][2], r[i][3]));
+        __stcs(rr + 2 * v + 1, make_float4(r[i][4], r[i][5], r[i][6], r[i][7]));
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc = fmaf(r[i][j], r[i][j], acc);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) r[i][j] = 0.0f;
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+    if ((tid & 31) == 0) warp_sums[tid >> 5] = acc;
+    __syncthreads();
+    if (tid < 32) {
+      float s = (tid < (nthreads >> 5)) ? warp_sums[tid] : 0.0f;
+      for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+      if (tid == 0) row_rstd = __frsqrt_rn(__fadd_rn(__fmul_rn(s, inv_d), eps));
+    }
+    __syncthreads();
+    const float rstd = row_rstd;
+
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int v = tid + i * nthreads;
+      const bool has = v < nvec;
+      uint4 o = make_uint4(0, 0, 0, 0);
+      if (has) {
+        const uint4 wv = __ldg(w + v);
+        o.x = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][0], rstd), bf16lo_to_f32(wv.x)), __fmul_rn(__fmul_rn(r[i][1], rstd), bf16hi_to_f32(wv.x)));
+        o.y = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][2], rstd), bf16lo_to_f32(wv.y)), __fmul_rn(__fmul_rn(r[i][3], rstd), bf16hi_to_f32(wv.y)));
+        o.z = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][4], rstd), bf16lo_to_f32(wv.z)), __fmul_rn(__fmul_rn(r[i][5], rstd), bf16hi_to_f32(wv.z)));
+        o.w = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][6], rstd), bf16lo_to_f32(wv.w)), __fmul_rn(__fmul_rn(r[i][7], rstd), bf16hi_to_f32(wv.w)));
+        if (out) __stcs(out + row * nvec + v, o);
+      }
+      if (QFMT >= 0) {
+        // uniform over the block: i * nthreads < nvec decides whether any thread has a vector in this round
+        if (i * nthreads < nvec) {
+          uint32_t c0, c1, sc;
+          quantize_vec8<(QFMT < 0 ? 0 : QFMT)>(o, gs, c0, c1, sc);
+          if (has) store_quantized<(QFMT < 0 ? 0 : QFMT)>(q_codes, q_scales, q_swizzled, row, v, d, c0, c1, sc);
+        }
+      }
+    }
+    __syncthreads();  // warp_sums / row_rstd are reused by the next row
+  }
+}
+
+template <int VPT>
+static void launch_vpt(int qfmt, dim3 grid, dim3 block, cudaStream_t s, const uint4* x, float4* res, const uint4* w, uint4* out, int64_t m, int d,
+                       float eps, float inv_d, uint8_t* qc, uint8_t* qs, int qsw, const float* qgs) {
+  switch (qfmt) {
+    case TF_FMT_MXFP8: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP8><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
+    case TF_FMT_MXFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
+    case TF_FMT_NVFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_NVFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
+    default: residual_add_rmsnorm_kernel<VPT, -1><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
+  }
+}
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" tf_status tf_residual_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int64_t m, int64_t d, float eps,
+                                             int32_t q_format, void* q_codes, void* q_scales, int32_t q_layout, const float* q_global_scale,
+                                             void* stream_) {
+  clear_error();
+  cudaStream_t stream = (cudaStream_t)stream_;
+  TF_CHECK_ARG(x && residual && w, "%s: null pointer", __func__);
+  TF_CHECK_ARG(m >= 0 && d > 0, "%s: bad shape m=%lld d=%lld", __func__, (long long)m, (long long)d);
+  TF_CHECK_ARG(q_format >= -1 && q_format <= TF_FMT_NVFP4, "%s: unknown q_format %d", __func__, q_format);
+  TF_CHECK_ARG(out || q_format >= 0, "%s: neither out nor a quantized output was given", __func__);
+  if (d % 8 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: d=%lld is not a multiple of 8", __func__, (long long)d);
+  if (d > 32768) return fail(TF_ERR_UNSUPPORTED, "%s: d=%lld exceeds 32768", __func__, (long long)d);
+  TF_CHECK_ALIGNED(x, 16, "x");
+  TF_CHECK_ALIGNED(residual, 16, "residual");
+  TF_CHECK_ALIGNED(w, 16, "w");
+  if (out) TF_CHECK_ALIGNED(out, 16, "out");
+  if (q_format >= 0) {
+    TF_CHECK_ARG(q_codes && q_scales, "%s: q_codes/q_scales missing", __func__);
+    TF_CHECK_ARG(q_layout == TF_SCALES_PLAIN || q_layout == TF_SCALES_SWIZZLED, "%s: unknown scale layout %d", __func__, q_layout);
+    TF_CHECK_ARG(q_format != TF_FMT_NVFP4 || q_global_scale, "%s: nvfp4 needs a global scale", __func__);
+    if (d % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: quantized output needs d %% 32 == 0", __func__);
+    TF_CHECK_ALIGNED(q_codes, 16, "q_codes");
+    const int64_t cols = d / (q_format == TF_FMT_NVFP4 ? 16 : 32);
+    if (q_layout == TF_SCALES_SWIZZLED && m > 0 && ((m & 127) || (cols & 3)))
+      TF_CUDA(cudaMemsetAsync(q_scales, 0, (size_t)tf_scale_bytes(q_format, m, d, q_layout), stream));
+  }
+  if (m == 0) return TF_OK;
+
+  const int nvec = (int)(d >> 3);
+  int vpt = (nvec + 511) / 512;
+  vpt = vpt <= 1 ? 1 : vpt <= 2 ? 2 : vpt <= 4 ? 4 : 8;
+  int threads = (nvec + vpt - 1) / vpt;
+  threads = (threads + 31) / 32 * 32;
+  const int64_t cap = (int64_t)sm_count() * (2048 / threads);
+  dim3 grid((unsigned)(m < cap ? m : cap)), block(threads);
+  const float inv_d = 1.0f / (float)d;  // correctly rounded f32 reciprocal of D (IEEE division on the host)
+  const uint4* xp = static_cast<const uint4*>(x);
+  float4* rp = static_cast<float4*>(residual);
+  const uint4* wp = static_cast<const uint4*>(w);
+  uint4* op = static_cast<uint4*>(out);
+  uint8_t* qc = static_cast<uint8_t*>(q_codes);
+  uint8_t* qs = static_cast<uint8_t*>(q_scales);
+  const int qsw = q_layout == TF_SCALES_SWIZZLED;
+  switch (vpt) {
+    case 1: launch_vpt<1>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
+    case 2: launch_vpt<2>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
+    case 4: launch_vpt<4>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
+    default: launch_vpt<8>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
+  }
+  TF_LAUNCH_CHECK();
+  return TF_OK;
+}

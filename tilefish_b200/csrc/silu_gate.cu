@@ -1,0 +1,64 @@
+// SiLU gate over the column halves of a [M, 2F] bf16 matrix (the stand-alone form; the GEMM also has it as an epilogue).
+//   out[m, j] = bf16( silu(f32(t[m, j])) * f32(t[m, F + j]) ),  silu(x) = x * (1 / (1 + exp(-x)))
+// HBM-bound elementwise kernel: 6 bytes per output element, 128-bit loads and stores.
+#include "common.cuh"
+
+namespace tf {
+
+__device__ __forceinline__ float silu_gate1(float g, float u) {
+  const float s = __fmul_rn(g, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))));
+  return __fmul_rn(s, u);
+}
+
+__global__ void __launch_bounds__(256) silu_gate_kernel(const uint4* __restrict__ t, int64_t m, int fvec, int64_t ldt_vec, uint4* __restrict__ out,
+                                                        int64_t ldo_vec) {
+  const int64_t total = m * fvec;
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 2 * stride) {  // two vector pairs in flight
+    uint4 g[2], u[2];
+    int64_t oidx[2];
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int64_t i = i0 + j * stride;
+      oidx[j] = -1;
+      if (i < total) {
+        const int64_t row = i / fvec;
+        const int v = (int)(i - row * fvec);
+        g[j] = __ldcs(t + row * ldt_vec + v);
+        u[j] = __ldcs(t + row * ldt_vec + fvec + v);
+        oidx[j] = row * ldo_vec + v;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      if (oidx[j] < 0) continue;
+      uint4 o;
+      o.x = pack_bf16x2(silu_gate1(bf16lo_to_f32(g[j].x), bf16lo_to_f32(u[j].x)), silu_gate1(bf16hi_to_f32(g[j].x), bf16hi_to_f32(u[j].x)));
+      o.y = pack_bf16x2(silu_gate1(bf16lo_to_f32(g[j].y), bf16lo_to_f32(u[j].y)), silu_gate1(bf16hi_to_f32(g[j].y), bf16hi_to_f32(u[j].y)));
+      o.z = pack_bf16x2(silu_gate1(bf16lo_to_f32(g[j].z), bf16lo_to_f32(u[j].z)), silu_gate1(bf16hi_to_f32(g[j].z), bf16hi_to_f32(u[j].z)));
+      o.w = pack_bf16x2(silu_gate1(bf16lo_to_f32(g[j].w), bf16lo_to_f32(u[j].w)), silu_gate1(bf16hi_to_f32(g[j].w), bf16hi_to_f32(u[j].w)));
+      __stcs(out + oidx[j], o);
+    }
+  }
+}
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" tf_status tf_silu_gate(const void* t, int64_t m, int64_t f, int64_t ldt, void* out, int64_t ldo, void* stream) {
+  clear_error();
+  TF_CHECK_ARG(t && out, "%s: null pointer", __func__);
+  TF_CHECK_ARG(m >= 0 && f > 0, "%s: bad shape m=%lld f=%lld", __func__, (long long)m, (long long)f);
+  if (f % 8 || ldt % 8 || ldo % 8 || ldt < 2 * f || ldo < f)
+    return fail(TF_ERR_ALIGNMENT, "%s: f, ldt, ldo must be multiples of 8 with ldt >= 2f, ldo >= f", __func__);
+  TF_CHECK_ALIGNED(t, 16, "t");
+  TF_CHECK_ALIGNED(out, 16, "out");
+  if (m == 0) return TF_OK;
+  const int64_t total = m * (f >> 3);
+  const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
+  silu_gate_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(t), m, (int)(f >> 3),
+                                                                                          ldt >> 3, static_cast<uint4*>(out), ldo >> 3);
+  TF_LAUNCH_CHECK();
+  return TF_OK;
+}

@@ -1,0 +1,306 @@
+"""Tensor-level entry to the sm_100a kernels: torch tensors in, C ABI calls out.
+
+torch is used for allocation, the current stream and nothing else. Every precondition the kernels rely on is checked
+here before anything is enqueued (dtype, rank, contiguity, device, 16-byte alignment, divisibility), the way the
+reference checks a launch (python/src/tilefish/_launch.py:263-315, :433-500); failures raise
+``TilefishPreconditionError(kind=..., arg=...)``. The shared library re-validates cheaply and returns a status.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+from . import _native as N
+from .errors import TilefishPreconditionError, TilefishRuntimeError
+
+FORMATS = {"mxfp8": N.FMT_MXFP8, "mxfp4": N.FMT_MXFP4, "nvfp4": N.FMT_NVFP4}
+BLOCK = {"mxfp8": 32, "mxfp4": 32, "nvfp4": 16}
+ELEMS_PER_BYTE = {"mxfp8": 1, "mxfp4": 2, "nvfp4": 2}
+EPILOGUES = {"none": N.EPI_NONE, "silu_gate": N.EPI_SILU_GATE, "residual": N.EPI_RESIDUAL}
+
+
+def _torch():
+    import torch
+
+    return torch
+
+
+def _pre(cond: bool, msg: str, kind: str, arg: Optional[str] = None) -> None:
+    if not cond:
+        raise TilefishPreconditionError(msg, kind=kind, arg=arg)
+
+
+def _check(t, name: str, dtype, rank: Optional[int] = None, device=None) -> None:
+    torch = _torch()
+    _pre(isinstance(t, torch.Tensor), f"{name}: expected a torch tensor, got {type(t).__name__}", "dtype", name)
+    _pre(t.is_cuda, f"{name}: the tensor is on {t.device}; this backend runs on CUDA only (no CPU fallback)", "device", name)
+    _pre(t.dtype == dtype, f"{name}: expected {dtype}, got {t.dtype}", "dtype", name)
+    if rank is not None:
+        _pre(t.dim() == rank, f"{name}: expected rank {rank}, got {t.dim()}", "rank", name)
+    if device is not None:
+        _pre(t.device == device, f"{name}: on {t.device}, the other arguments are on {device}", "device", name)
+    _pre(t.numel() == 0 or t.data_ptr() % 16 == 0, f"{name}: the data pointer is not 16-byte aligned", "pointer_alignment", name)
+
+
+def _dense(t, name: str) -> None:
+    _pre(t.is_contiguous(), f"{name}: must be contiguous (strides {tuple(t.stride())})", "contiguous", name)
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        return _torch().cuda.current_stream().cuda_stream
+    return getattr(stream, "cuda_stream", stream)
+
+
+class BlockScaledTensor:
+    """Run-time value of a ``Tensor[rows, K, BlockScaled(...)]``: element codes, scale bytes and (nvfp4) the f32 global scale.
+
+    ``codes``   uint8 [rows, K] (mxfp8) or [rows, K/2] (fp4: element 2i in bits 0-3 of byte i)
+    ``scales``  uint8, flat; ``layout`` is "swizzled" (the sm_100 MMA operand layout, what the GEMM consumes) or "plain" ([rows, K/block])
+    ``global_scale``  float32 [1] on the device for nvfp4, else None
+    """
+
+    __slots__ = ("fmt", "shape", "codes", "scales", "global_scale", "layout")
+
+    def __init__(self, fmt: str, shape, codes, scales, global_scale=None, layout: str = "swizzled") -> None:
+        if fmt not in FORMATS:
+            raise TilefishPreconditionError(f"unknown block-scaled format {fmt!r}", kind="dtype")
+        self.fmt = fmt
+        self.shape = tuple(int(s) for s in shape)
+        self.codes = codes
+        self.scales = scales
+        self.global_scale = global_scale
+        self.layout = layout
+
+    @property
+    def device(self):
+        return self.codes.device
+
+    @property
+    def block(self) -> int:
+        return BLOCK[self.fmt]
+
+    def plain_scales(self):
+        """The scale bytes as a [rows, K/block] uint8 tensor (un-swizzled on the device when needed)."""
+        rows, k = self.shape
+        cols = k // self.block
+        if self.layout == "plain":
+            return self.scales.view(rows, cols)
+        return unswizzle_scales(self.scales, rows, cols)
+
+    def nbytes(self) -> int:
+        n = self.codes.numel() + self.scales.numel()
+        return n + (4 if self.global_scale is not None else 0)
+
+    def __repr__(self) -> str:
+        return f"BlockScaledTensor({self.fmt}, shape={self.shape}, scales={self.layout})"
+
+
+def scale_bytes(fmt: str, rows: int, k: int, layout: str = "swizzled") -> int:
+    return N.scale_bytes(FORMATS[fmt], rows, k, N.SCALES_SWIZZLED if layout == "swizzled" else N.SCALES_PLAIN)
+
+
+def nvfp4_global_scale(x, *, out=None, stream=None):
+    """float32 [1] on the device: max|x| / 2688, computed in stream order."""
+    torch = _torch()
+    _check(x, "x", torch.bfloat16, 2)
+    _pre(x.stride(1) == 1 and x.stride(0) % 8 == 0, "x: rows must be dense with a row stride that is a multiple of 8", "contiguous", "x")
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    m, k = x.shape
+    N.check(N.load().tf_nvfp4_global_scale(x.data_ptr(), m, k, x.stride(0), out.data_ptr(), _stream(stream)), "tf_nvfp4_global_scale")
+    return out
+
+
+def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, stream=None) -> BlockScaledTensor:
+    """BlockScaled quantization of a bf16 [M, K] tensor along K. nvfp4 computes the global scale unless one is given."""
+    torch = _torch()
+    _pre(fmt in FORMATS, f"unknown block-scaled format {fmt!r}", "dtype", "fmt")
+    _pre(layout in ("swizzled", "plain"), f"unknown scale layout {layout!r}", "argument", "layout")
+    _check(x, "x", torch.bfloat16, 2)
+    m, k = x.shape
+    _pre(x.stride(1) == 1 and (m <= 1 or (x.stride(0) >= k and x.stride(0) % 8 == 0)), "x: rows must be dense with a row stride that is a multiple of 8", "contiguous", "x")
+    _pre(k % 32 == 0 and k > 0, f"x: K={k} is not a multiple of 32", "divisible", "x")
+    ldx = x.stride(0) if m > 1 else k
+    lay = N.SCALES_SWIZZLED if layout == "swizzled" else N.SCALES_PLAIN
+    codes = torch.empty((m, k // ELEMS_PER_BYTE[fmt]), dtype=torch.uint8, device=x.device)
+    scales = torch.empty(N.scale_bytes(FORMATS[fmt], m, k, lay), dtype=torch.uint8, device=x.device)
+    s = _stream(stream)
+    lib = N.load()
+    gs = None
+    if m == 0:  # nothing to launch (an empty tensor has no data pointer)
+        if fmt == "nvfp4":
+            gs = global_scale if global_scale is not None else torch.zeros(1, dtype=torch.float32, device=x.device)
+        return BlockScaledTensor(fmt, (m, k), codes, scales, gs, layout)
+    if fmt == "nvfp4":
+        if global_scale is None:
+            gs = nvfp4_global_scale(x, stream=stream)
+        else:
+            _check(global_scale, "global_scale", torch.float32, None, x.device)
+            _pre(global_scale.numel() == 1, "global_scale: expected one element", "shape", "global_scale")
+            gs = global_scale
+        N.check(lib.tf_quantize_nvfp4(x.data_ptr(), m, k, ldx, codes.data_ptr(), scales.data_ptr(), lay, gs.data_ptr(), s), "tf_quantize_nvfp4")
+    elif fmt == "mxfp8":
+        N.check(lib.tf_quantize_mxfp8(x.data_ptr(), m, k, ldx, codes.data_ptr(), scales.data_ptr(), lay, s), "tf_quantize_mxfp8")
+    else:
+        N.check(lib.tf_quantize_mxfp4(x.data_ptr(), m, k, ldx, codes.data_ptr(), scales.data_ptr(), lay, s), "tf_quantize_mxfp4")
+    return BlockScaledTensor(fmt, (m, k), codes, scales, gs, layout)
+
+
+def swizzle_scales(plain, *, stream=None):
+    torch = _torch()
+    _check(plain, "plain", torch.uint8, 2)
+    _dense(plain, "plain")
+    rows, cols = plain.shape
+    out = torch.empty(((rows + 127) // 128) * ((cols + 3) // 4) * 512, dtype=torch.uint8, device=plain.device)
+    N.check(N.load().tf_swizzle_scales(plain.data_ptr(), rows, cols, out.data_ptr(), _stream(stream)), "tf_swizzle_scales")
+    return out
+
+
+def unswizzle_scales(swizzled, rows: int, cols: int, *, stream=None):
+    torch = _torch()
+    _check(swizzled, "swizzled", torch.uint8, 1)
+    need = ((rows + 127) // 128) * ((cols + 3) // 4) * 512
+    _pre(swizzled.numel() >= need, f"swizzled: {swizzled.numel()} bytes, {need} needed for [{rows}, {cols}]", "shape", "swizzled")
+    out = torch.empty((rows, cols), dtype=torch.uint8, device=swizzled.device)
+    N.check(N.load().tf_unswizzle_scales(swizzled.data_ptr(), rows, cols, out.data_ptr(), _stream(stream)), "tf_unswizzle_scales")
+    return out
+
+
+def residual_add_rmsnorm(x, residual, w, eps: float = 1e-6, *, out=None, quantize_to: Optional[str] = None, want_bf16: bool = True,
+                         q_global_scale=None, stream=None):
+    """``residual += f32(x)`` in place; returns bf16 ``rmsnorm(residual) * w`` and/or its BlockScaled quantization.
+
+    Returns ``out`` (bf16), or ``(out, q)`` when ``quantize_to`` is given (``out`` is None with ``want_bf16=False``).
+    """
+    torch = _torch()
+    _check(x, "x", torch.bfloat16, 2)
+    _check(residual, "residual", torch.float32, 2, x.device)
+    _check(w, "w", torch.bfloat16, 1, x.device)
+    for t, n in ((x, "x"), (residual, "residual"), (w, "w")):
+        _dense(t, n)
+    m, d = x.shape
+    _pre(tuple(residual.shape) == (m, d), f"residual: shape {tuple(residual.shape)}, expected {(m, d)}", "shape", "residual")
+    _pre(tuple(w.shape) == (d,), f"w: shape {tuple(w.shape)}, expected {(d,)}", "shape", "w")
+    _pre(d % 8 == 0, f"x: D={d} is not a multiple of 8", "divisible", "x")
+    if want_bf16:
+        if out is None:
+            out = torch.empty((m, d), dtype=torch.bfloat16, device=x.device)
+        else:
+            _check(out, "out", torch.bfloat16, 2, x.device)
+            _dense(out, "out")
+            _pre(tuple(out.shape) == (m, d), "out: wrong shape", "shape", "out")
+            _pre(out.data_ptr() != x.data_ptr(), "out aliases x", "alias", "out")
+    else:
+        _pre(quantize_to is not None, "nothing to compute: want_bf16=False without quantize_to", "argument")
+        out = None
+    q = None
+    qfmt, qc, qs, qg = -1, None, None, None
+    if quantize_to is not None:
+        _pre(quantize_to in FORMATS, f"unknown block-scaled format {quantize_to!r}", "dtype", "quantize_to")
+        _pre(d % 32 == 0, f"x: D={d} is not a multiple of 32 (needed to quantize)", "divisible", "x")
+        qfmt = FORMATS[quantize_to]
+        codes = torch.empty((m, d // ELEMS_PER_BYTE[quantize_to]), dtype=torch.uint8, device=x.device)
+        scales = torch.empty(N.scale_bytes(qfmt, m, d, N.SCALES_SWIZZLED), dtype=torch.uint8, device=x.device)
+        if quantize_to == "nvfp4":
+            _pre(q_global_scale is not None, "nvfp4 output needs q_global_scale (a float32 [1] device tensor)", "argument", "q_global_scale")
+            _check(q_global_scale, "q_global_scale", torch.float32, None, x.device)
+            qg = q_global_scale
+        q = BlockScaledTensor(quantize_to, (m, d), codes, scales, qg, "swizzled")
+        qc, qs = codes.data_ptr(), scales.data_ptr()
+    N.check(
+        N.load().tf_residual_add_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), out.data_ptr() if out is not None else None, m, d,
+                                         float(eps), qfmt, qc, qs, N.SCALES_SWIZZLED, qg.data_ptr() if qg is not None else None, _stream(stream)),
+        "tf_residual_add_rmsnorm",
+    )
+    return out if q is None else (out, q)
+
+
+def silu_gate(t, *, out=None, stream=None):
+    """bf16 [M, F] = silu(t[:, :F]) * t[:, F:] for a bf16 [M, 2F] tensor (row stride a multiple of 8)."""
+    torch = _torch()
+    _check(t, "t", torch.bfloat16, 2)
+    m, two_f = t.shape
+    _pre(two_f % 16 == 0, f"t: {two_f} columns; the halves must be multiples of 8", "divisible", "t")
+    f = two_f // 2
+    _pre(t.stride(1) == 1 and (m <= 1 or t.stride(0) % 8 == 0), "t: rows must be dense with a row stride that is a multiple of 8", "contiguous", "t")
+    if out is None:
+        out = torch.empty((m, f), dtype=torch.bfloat16, device=t.device)
+    else:
+        _check(out, "out", torch.bfloat16, 2, t.device)
+        _dense(out, "out")
+        _pre(tuple(out.shape) == (m, f), "out: wrong shape", "shape", "out")
+    ldt = t.stride(0) if m > 1 else two_f
+    N.check(N.load().tf_silu_gate(t.data_ptr(), m, f, ldt, out.data_ptr(), f, _stream(stream)), "tf_silu_gate")
+    return out
+
+
+def gemm_workspace_bytes(m: int, n: int, k: int, fmt: str, epilogue: str = "none") -> int:
+    return int(N.load().tf_gemm_workspace_bytes(m, n, k, FORMATS[fmt], EPILOGUES[epilogue]))
+
+
+def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, workspace=None, stream=None):
+    """bf16 [M, N] = deq(a)[M, K] @ deq(b)[N, K]^T on tcgen05 block-scaled MMA, f32 accumulate.
+
+    ``epilogue="silu_gate"``: b has 2N rows (gate rows then up rows); the result is silu(gate) * up, [M, N].
+    ``epilogue="residual"``: also ``residual[M, N] += f32(out)`` (f32, in place).
+    """
+    torch = _torch()
+    _pre(isinstance(a, BlockScaledTensor) and isinstance(b, BlockScaledTensor), "a and b must be BlockScaledTensor", "dtype")
+    _pre(a.fmt == b.fmt, f"a is {a.fmt} but b is {b.fmt}: block-scaled formats must match exactly", "dtype", "b")
+    _pre(a.layout == "swizzled" and b.layout == "swizzled", "the GEMM consumes swizzled scales", "contiguous")
+    _pre(epilogue in EPILOGUES, f"unknown epilogue {epilogue!r}", "argument", "epilogue")
+    m, k = a.shape
+    nb, kb = b.shape
+    _pre(k == kb, f"K differs: a is {a.shape}, b is {b.shape}", "shape", "b")
+    n = nb // 2 if epilogue == "silu_gate" else nb
+    if epilogue == "silu_gate":
+        _pre(nb % 256 == 0, f"silu_gate: b has {nb} rows; each half must be a multiple of 128", "divisible", "b")
+    _pre(a.device == b.device, "a and b are on different devices", "device", "b")
+    for t, nm in ((a.codes, "a.codes"), (b.codes, "b.codes"), (a.scales, "a.scales"), (b.scales, "b.scales")):
+        _check(t, nm, torch.uint8, None, a.device)
+        _dense(t, nm)
+    if a.fmt == "nvfp4":
+        _pre(a.global_scale is not None and b.global_scale is not None, "nvfp4 operands need their global scales", "argument")
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
+    else:
+        _check(out, "out", torch.bfloat16, 2, a.device)
+        _pre(tuple(out.shape) == (m, n) and out.stride(1) == 1 and (m <= 1 or out.stride(0) % 8 == 0), "out: wrong shape or strides", "shape", "out")
+    ldo = out.stride(0) if m > 1 else n
+    res_ptr = None
+    if epilogue == "residual":
+        _pre(residual is not None, "epilogue='residual' needs the f32 residual", "argument", "residual")
+        _check(residual, "residual", torch.float32, 2, a.device)
+        _dense(residual, "residual")
+        _pre(tuple(residual.shape) == (m, n), "residual: wrong shape", "shape", "residual")
+        res_ptr = residual.data_ptr()
+    need = gemm_workspace_bytes(m, n, k, a.fmt, epilogue)
+    ws_ptr, ws_bytes = None, 0
+    if need > 0:
+        if workspace is None:
+            workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+        _pre(workspace.numel() * workspace.element_size() >= need, f"workspace: {need} bytes needed", "workspace", "workspace")
+        ws_ptr, ws_bytes = workspace.data_ptr(), workspace.numel() * workspace.element_size()
+    N.check(
+        N.load().tf_gemm_blockscaled(
+            a.codes.data_ptr(), a.scales.data_ptr(), a.global_scale.data_ptr() if a.global_scale is not None else None,
+            b.codes.data_ptr(), b.scales.data_ptr(), b.global_scale.data_ptr() if b.global_scale is not None else None,
+            out.data_ptr(), ldo, m, n, k, FORMATS[a.fmt], EPILOGUES[epilogue], res_ptr, ws_ptr, ws_bytes, _stream(stream)),
+        "tf_gemm_blockscaled",
+    )
+    return out
+
+
+def gemm(a, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, a_global_scale=None, stream=None):
+    """The library ``gemm``: ``a`` is bf16 [M, K] (quantized on the fly in b's format) or already a BlockScaledTensor."""
+    if not isinstance(a, BlockScaledTensor):
+        a = quantize(a, b.fmt, global_scale=a_global_scale, stream=stream)
+    return gemm_blockscaled(a, b, epilogue=epilogue, out=out, residual=residual, stream=stream)
+
+
+def require_cuda() -> None:
+    torch = _torch()
+    if not torch.cuda.is_available():
+        raise TilefishRuntimeError("no CUDA device: this backend has no CPU path")
+    N.load()
