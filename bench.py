@@ -1,0 +1,389 @@
+"""Benchmark of the quantized-inference hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P bench.py --gpus N ...
+
+One step = one forward pass of the tensor-parallel MLP stack of the last benchmark configuration: 32 decoder blocks shaped
+like Llama-3-70B's MLP (H = 8192, F = 28672, SiLU-gated), NVFP4 weights quantized from seeded N(0, 1/sqrt(fan_in)) bf16,
+M = 4096 tokens of x ~ N(0, 1): residual_add_rmsnorm -> quantize -> gemm (+ SiLU-gate epilogue) -> quantize -> gemm ->
+(N > 1: one bf16 NCCL all-reduce) per block. ``value`` is tokens/s with x resident in HBM; ``e2e`` is the same step through the
+public API with x in pinned host memory and the result copied back, both copies inside the timed region. The total work is
+fixed as N grows (``scaling: strong``). At N = 1 the line also carries the two single-kernel headline metrics: quantize GB/s
+(M = 65536, K = 4096, every format) and block-scaled GEMM TFLOP/s (M = 4096, N = 6144, K = 2560, MXFP8 and NVFP4).
+
+``--impl reference`` times the CPU restatement of the same block (oracle/blockscaled.py, torch on all host threads) on a
+bounded sample of the workload; the reference project itself cannot run this path (it only types BlockScaled tensors).
+"""
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+H, F, LAYERS, M_TOKENS, FMT = 8192, 28672, 32, 4096, "nvfp4"
+WORKLOAD = f"tp_mlp_stack: {LAYERS} layers H={H} F={F} {FMT} weights, M={M_TOKENS} (prefill)"
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=8)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=LAYERS, help="development only: fewer layers (the line then says so)")
+    ap.add_argument("--tokens", type=int, default=M_TOKENS, help="development only")
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
+    return ap.parse_args()
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# CPU arm: the oracle's decoder block on a bounded sample
+# ----------------------------------------------------------------------------------------------------------------------
+_CPU_WEIGHTS: dict = {}
+
+
+def cpu_block_seconds(rows: int, repeats: int = 1):
+    """Seconds for ONE decoder block on ``rows`` tokens with the CPU oracle (weights already dequantized to f32: the values
+    do not change the time, so seeded random f32 stands in for them), best of ``repeats``."""
+    import torch
+
+    from oracle import blockscaled as O
+
+    g = torch.Generator().manual_seed(0)
+    if not _CPU_WEIGHTS:
+        _CPU_WEIGHTS["w_gu"] = torch.randn((2 * F, H), generator=g) * H**-0.5
+        _CPU_WEIGHTS["w_d"] = torch.randn((H, F), generator=g) * F**-0.5
+    w_gu, w_d = _CPU_WEIGHTS["w_gu"], _CPU_WEIGHTS["w_d"]
+    w_n = torch.ones(H, dtype=torch.bfloat16)
+    x = torch.randn((rows, H), generator=g).to(torch.bfloat16)
+    best = float("inf")
+    for _ in range(repeats):
+        res = torch.zeros((rows, H))
+        t0 = time.perf_counter()
+        r, h = O.residual_add_rmsnorm(x, res, w_n)
+        qh = O.quantize(h, FMT)
+        t = O.f32_to_bf16(O.dequantize(qh[0], qh[1], FMT, qh[2]) @ w_gu.t())
+        a = O.silu_gate(t[:, :F], t[:, F:])
+        qa = O.quantize(a, FMT)
+        y = O.f32_to_bf16(O.dequantize(qa[0], qa[1], FMT, qa[2]) @ w_d.t())
+        best = min(best, time.perf_counter() - t0)
+        del r, h, qh, t, a, qa, y
+    return best
+
+
+def run_reference(args, rank: int) -> None:
+    if rank != 0:
+        return
+    import torch
+
+    rows = 128
+    cpu_block_seconds(rows)  # warm-up (also pages the weights in)
+    for _ in range(max(0, min(args.warmup, 2) - 1)):
+        cpu_block_seconds(rows)
+    times = [cpu_block_seconds(rows) for _ in range(min(args.steps, 5))]
+    t_block = statistics.median(times)
+    t_step = t_block * LAYERS * (M_TOKENS / rows)  # the full step, scaled linearly in rows and layers
+    value = M_TOKENS / t_step
+    cores = torch.get_num_threads()
+    sample = f"{rows} of {M_TOKENS} rows x 1 of {LAYERS} layers per timed run (f32 matmuls of dequantized operands), scaled linearly"
+    line = {
+        "impl": "reference", "metric": "mlp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(times),
+        "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "note": "CPU restatement (oracle) of the block; the reference types this path but cannot run it"},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ----------------------------------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------------------------------
+class ClockSampler:
+    FIELDS = "clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+
+    def __init__(self, index: int) -> None:
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(index)],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in out.strip().splitlines():
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        # samples under load are the upper half of the clock samples' power... keep it simple: median of all samples
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def event_ms(fn, iters: int, torch, flush=None):
+    """Median device time of fn() over ``iters`` launches, CUDA events on the current stream, L2 flushed between launches."""
+    ts = []
+    for _ in range(iters):
+        if flush is not None:
+            flush.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def extras(torch, K, pk):
+    """Single-kernel headline metrics at N = 1: quantize GB/s (sweep point M = 65536) and block-scaled GEMM TFLOP/s."""
+    out = {"quantize": {}, "gemm": {}}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    m, k = 65536, 4096
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn((m, k), generator=g, device="cuda")
+    x = torch.where(torch.rand((m, k), generator=g, device="cuda") < 0.01, x * 100, x).to(torch.bfloat16)
+    gs = K.nvfp4_global_scale(x)
+    for fmt, bpe in (("mxfp8", 2 + 1 + 1 / 32), ("mxfp4", 2 + 0.5 + 1 / 32), ("nvfp4", 2 + 0.5 + 1 / 16)):
+        fn = (lambda f=fmt: K.quantize(x, f, global_scale=gs if f == "nvfp4" else None))
+        for _ in range(3):
+            fn()
+        ms = event_ms(fn, 10, torch, flush)
+        gbs = m * k * bpe / ms / 1e6
+        out["quantize"][fmt] = {"GBps": round(gbs, 1), "us": round(ms * 1e3, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 3), "shape": [m, k]}
+    ms = event_ms(lambda: K.nvfp4_global_scale(x, out=gs), 10, torch, flush)
+    out["quantize"]["nvfp4_amax_pass"] = {"GBps": round(m * k * 2 / ms / 1e6, 1), "us": round(ms * 1e3, 1)}
+    del x
+    m, n, k = 4096, 6144, 2560
+    a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g, device="cuda") * k**-0.5).to(torch.bfloat16)
+    for fmt, mult in (("mxfp8", 2), ("nvfp4", 4)):
+        qa, qb = K.quantize(a, fmt), K.quantize(w, fmt)
+        o = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+        fn = (lambda: K.gemm_blockscaled(qa, qb, out=o))
+        for _ in range(3):
+            fn()
+        # back-to-back launches so that host launch latency is hidden; operands (tens of MB) stay in L2 by design of the shape
+        iters = 20
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        s.record()
+        for _ in range(iters):
+            fn()
+        e.record()
+        e.synchronize()
+        ms = s.elapsed_time(e) / iters
+        tf = 2 * m * n * k / ms / 1e9
+        ms_q = event_ms(lambda: K.quantize(a, fmt), 5, torch)
+        out["gemm"][fmt] = {"TFLOPs": round(tf, 1), "us": round(ms * 1e3, 1), "a_quantize_us": round(ms_q * 1e3, 1), "shape": [m, n, k],
+                            "frac_of_peak": round(tf / (mult * pk["bf16_tflops"]), 3), "peak": f"{mult} x bf16 burst {pk['bf16_tflops']} ({pk['source']})",
+                            "frac_of_nominal": round(tf / (2250.0 * mult), 3)}
+    return out
+
+
+def run_ours(args) -> None:
+    import torch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device (this backend has no CPU path); use --impl reference for the CPU arm")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    group = None
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
+    if world != args.gpus:
+        raise SystemExit(f"bench.py: --gpus {args.gpus} but WORLD_SIZE={world}")
+
+    from tilefish_b200 import kernels as K
+    from tilefish_b200 import mlp as MLP
+
+    K.require_cuda()
+    pk = peaks()
+    layers, m = args.layers, args.tokens
+
+    # ---- weights: seeded per layer, identical on every rank, quantized once and sharded ----
+    blocks = []
+    for layer in range(layers):
+        g = torch.Generator(device=dev).manual_seed(1000 + layer)
+        w_gu = (torch.randn((2 * F, H), generator=g, device=dev) * H**-0.5).to(torch.bfloat16)
+        w_d = (torch.randn((H, F), generator=g, device=dev) * F**-0.5).to(torch.bfloat16)
+        w_n = (1 + 0.1 * torch.randn(H, generator=g, device=dev)).to(torch.bfloat16)
+        blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, FMT, rank=rank, world=world))
+        del w_gu, w_d
+    stack = MLP.MlpStack(blocks, group=group)
+    torch.cuda.synchronize()
+
+    gx = torch.Generator().manual_seed(0)
+    x_host = torch.randn((m, H), generator=gx).to(torch.bfloat16).pin_memory()
+    out_host = torch.empty((m, H), dtype=torch.bfloat16).pin_memory()
+    x_dev = x_host.to(dev)
+    residual = torch.zeros((m, H), dtype=torch.float32, device=dev)
+
+    # per-launch events around the dominant kernel (the first GEMM of every block) inside the timed region
+    gemm_events = []
+    orig_gemm = K.gemm_blockscaled
+
+    def timed_gemm(a, b, **kw):
+        if kw.get("epilogue") != "silu_gate" or not gemm_events_enabled[0]:
+            return orig_gemm(a, b, **kw)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        r = orig_gemm(a, b, **kw)
+        e.record()
+        gemm_events.append((s, e))
+        return r
+
+    gemm_events_enabled = [False]
+    K.gemm_blockscaled = timed_gemm
+    launches_per_step = layers * 5  # rmsnorm, 2 x quantize, 2 x gemm per block (nvfp4)
+
+    def step():
+        residual.zero_()
+        return stack(x_dev, residual)
+
+    def step_e2e():
+        x_dev.copy_(x_host, non_blocking=True)
+        residual.zero_()
+        y = stack(x_dev, residual)
+        out_host.copy_(y, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return out_host
+
+    def barrier():
+        if world > 1:
+            import torch.distributed as dist
+
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            fn()
+        e.record()
+        barrier()
+        ms = s.elapsed_time(e)
+        if world > 1:
+            import torch.distributed as dist
+
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    sampler = ClockSampler(local) if rank == 0 else None
+    gemm_events_enabled[0] = True
+    total_ms = timed(step, args.steps)
+    gemm_events_enabled[0] = False
+    clocks = sampler.stop() if sampler else None
+    gemm_ms = [s.elapsed_time(e) for s, e in gemm_events]
+    for _ in range(2):
+        step_e2e()
+    e2e_ms = timed(step_e2e, args.steps)
+    K.gemm_blockscaled = orig_gemm
+
+    ms_per_step = total_ms / args.steps
+    value = m / (ms_per_step / 1e3)
+    e2e_value = m / (e2e_ms / args.steps / 1e3)
+
+    # roofline of the dominant kernel: gemm(h, w_gu) with the SiLU-gate epilogue, on this rank's shard
+    f_local = F // world
+    flops = 2.0 * m * (2 * f_local) * H
+    avg_ms = statistics.mean(gemm_ms) if gemm_ms else float("nan")
+    achieved = flops / avg_ms / 1e9
+    peak = 4 * pk["bf16_tflops_sustained"]
+    roofline = {"bound": "tensor", "kernel": "gemm_blockscaled_kernel<nvfp4, 256, silu_gate>", "achieved": round(achieved, 1), "peak": peak,
+                "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
+                "peak_note": f"4 x sustained bf16 cuBLAS {pk['bf16_tflops_sustained']} TFLOP/s ({pk['source']}); no FP4 peak was measured on this pool. "
+                             f"Nominal dense FP4 is 9000: frac_of_nominal = {achieved / 9000.0:.4f}",
+                "launches_timed": len(gemm_ms), "avg_launch_ms": round(avg_ms, 4)}
+
+    if rank != 0:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+        return
+    line = {
+        "metric": "mlp_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp4 (e2m1 x e4m3 block scales, f32 accumulate, bf16 out)",
+        "data": "synthetic", "impl": "ours",
+        "config": {"workload": WORKLOAD if (layers, m) == (LAYERS, M_TOKENS) else f"REDUCED {layers} layers M={m} (development run, not the benchmark)",
+                   "parallelism": f"tp{world}", "l2": "inputs larger than L2: every step streams all weights (>= 1.5 GB per GPU)"},
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+                "ms_per_step": round(e2e_ms / args.steps, 4)},
+        "gpu_launches": launches_per_step * args.steps,
+        "roofline": roofline,
+        "clocks": clocks,
+    }
+    if world == 1:
+        if not args.no_extras:
+            del stack, blocks
+            torch.cuda.empty_cache()
+            line["kernels"] = extras(torch, K, pk)
+        rows = 128
+        cpu_block_seconds(rows)
+        t_block = cpu_block_seconds(rows, repeats=2)
+        cpu_value = M_TOKENS / (t_block * LAYERS * (M_TOKENS / rows))
+        line["cpu_baseline"] = {"value": round(cpu_value, 3), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                                "sample": f"{rows} of {M_TOKENS} rows x 1 of {LAYERS} layers with the CPU oracle (f32 matmuls of dequantized operands), scaled linearly"}
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        import torch.distributed as dist
+
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    args = parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -84,6 +84,11 @@ TF_API tf_status tf_quantize_mxfp8(const void* x, int64_t m, int64_t k, int64_t 
 TF_API tf_status tf_quantize_mxfp4(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout, void* stream);
 TF_API tf_status tf_quantize_nvfp4(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout,
                             const float* global_scale, void* stream);
+/* Same, but the global scale is derived inside the kernel from a device f32 holding amax(|x|) (as produced by the out_amax
+ * argument of tf_residual_add_rmsnorm / tf_gemm_blockscaled): global_scale_out[0] = amax[0] / 2688.0f is also written for
+ * the GEMM that consumes the result. Saves the separate amax pass over x. */
+TF_API tf_status tf_quantize_nvfp4_from_amax(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout,
+                                      const float* amax, float* global_scale_out, void* stream);
 /* global_scale_out[0] = max|x| / 2688.0f (one IEEE division), computed on the device in stream order. */
 TF_API tf_status tf_nvfp4_global_scale(const void* x, int64_t m, int64_t k, int64_t ldx, float* global_scale_out, void* stream);
 
@@ -96,10 +101,12 @@ TF_API tf_status tf_unswizzle_scales(const void* swizzled, int64_t rows, int64_t
  *   x bf16 [m, d]; residual f32 [m, d] (updated in place); w bf16 [d]; all dense and 16-byte aligned; d % 8 == 0.
  *   out      bf16 [m, d] or NULL when only the quantized output is wanted
  *   q_format -1 for none, else a TF_FMT_*: the bf16 result is also quantized along d (d % 32 == 0) into q_codes/q_scales
- *            exactly as tf_quantize_* would quantize `out`; nvfp4 needs q_global_scale (given, on the device). */
+ *            exactly as tf_quantize_* would quantize `out`; nvfp4 needs q_global_scale (given, on the device).
+ *   out_amax NULL, or a device f32 the caller zeroed: max(|out|) is combined into it with an atomic max (the f32 bit
+ *            pattern of a non-negative value orders like an unsigned integer). */
 TF_API tf_status tf_residual_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int64_t m, int64_t d, float eps,
                                   int32_t q_format, void* q_codes, void* q_scales, int32_t q_layout, const float* q_global_scale,
-                                  void* stream);
+                                  float* out_amax, void* stream);
 
 /* SiLU gate over the column halves of t (README.md:83-84; the fused region of python/src/tilefish/_fusion.py):
  *   out[m, f] = bf16( silu(f32(t[m, j])) * f32(t[m, f + j]) ), silu(x) = x * (1 / (1 + exp(-x))).
@@ -115,11 +122,12 @@ TF_API tf_status tf_silu_gate(const void* t, int64_t m, int64_t f, int64_t ldt, 
  *   out      bf16 [m, n] row stride ldo (ldo % 8 == 0)
  *   epilogue TF_EPI_*: with TF_EPI_SILU_GATE b has 2n rows (n % 128 == 0); with TF_EPI_RESIDUAL epilogue_arg is the f32
  *            residual [m, n] (dense)
+ *   out_amax NULL, or a device f32 the caller zeroed: max(|out|) is combined into it with an atomic max
  *   workspace / workspace_bytes   at least tf_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when 0) */
 TF_API int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue);
 TF_API tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
                               const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
-                              int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, void* workspace,
+                              int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* workspace,
                               int64_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus

@@ -32,7 +32,8 @@ MX (ue8m0 scale, block 32; e4m3 or e2m1 elements)
                 maximum saturate: the OCP "floor" convention)
 NVFP4 (e4m3 scale, block 16, f32 global scale)
     gs        = amax_tensor / 2688.0f                           (one division; or given by the caller)
-    s8        = cast_e4m3(amax_block / (6.0f * gs))             (one multiply, one division; 0 when gs == 0)
+    s8        = cast_e4m3(amax_block * (1.0f / (6.0f * gs)))    (ONE reciprocal per tensor, one multiply per block;
+                0 when gs == 0 or the block is all zero)
     d         = f32(s8) * gs                                    (decode scale, one multiply)
     code      = cast_e2m1(f32(x) * (1.0f / d))                  (ONE reciprocal per block, one multiply per element;
                 all codes 0 when d == 0)
@@ -164,8 +165,10 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: "torch.Tensor | None" = None):
     xf = x.to(torch.float32).view(m, k // block, block)
     amax = xf.abs().amax(dim=-1)  # NaN-free inputs; exact in f32
     t = torch.tensor(E2M1_MAX, dtype=torch.float32) * gs
-    s = amax / t
-    s8 = torch.where(gs == 0, torch.zeros_like(s).to(torch.uint8), cast_e4m3(torch.where(gs == 0, torch.zeros_like(s), s)))
+    inv_t = torch.ones((), dtype=torch.float32) / t
+    dead = (gs == 0) | (amax == 0)
+    s = torch.where(dead, torch.zeros_like(amax), amax * inv_t)
+    s8 = torch.where(dead, torch.zeros_like(s).to(torch.uint8), cast_e4m3(s))
     d = e4m3_to_f32(s8) * gs
     inv = torch.where(d == 0, torch.zeros_like(d), 1.0 / d)
     q = xf * inv.unsqueeze(-1)

@@ -1,0 +1,154 @@
+"""GPU parity of the block-scaled GEMM (tcgen05) and its fused epilogues against the CPU oracle.
+
+Oracle O1: bf16( f32 matmul of the DEQUANTIZED operands ), the same codes and scale bytes the kernel consumed (they are
+bit-exact with the oracle's, which test_gpu_rowkernels.py proves). Bound: max|d| <= 2**-8 * max|ref| * 1.01, the bound the
+reference asserts for its own GEMM (python/tests/test_gpu_gemm.py:103-114). A GEMM with a wrong scale layout, nibble order
+or K order fails this by orders of magnitude, so this test is also what proves the swizzled scale layout.
+"""
+
+import pytest
+import torch
+
+from oracle import blockscaled as O
+
+pytestmark = pytest.mark.gpu
+
+FMTS = ["mxfp8", "mxfp4", "nvfp4"]
+TOL = 2.0**-8 * 1.01
+
+
+@pytest.fixture(scope="module")
+def K():
+    from tilefish_b200 import kernels
+
+    kernels.require_cuda()
+    return kernels
+
+
+def operands(m, n_rows, k, seed):
+    """bf16 a ~ N(0,1), w ~ N(0, 1/K), each 32-block rescaled by a random power of two so the scale bytes vary."""
+    g = torch.Generator().manual_seed(seed)
+    a = torch.randn((m, k), generator=g)
+    w = torch.randn((n_rows, k), generator=g) * k**-0.5
+    a = a * torch.exp2(torch.randint(-2, 3, (m, k // 32), generator=g).float()).repeat_interleave(32, dim=1)
+    w = w * torch.exp2(torch.randint(-3, 4, (n_rows, k // 32), generator=g).float()).repeat_interleave(32, dim=1)
+    return a.to(torch.bfloat16), w.to(torch.bfloat16)
+
+
+def oracle_acc(a, w, fmt):
+    qa, qb = O.quantize(a, fmt), O.quantize(w, fmt)
+    return O.dequantize(qa[0], qa[1], fmt, qa[2]) @ O.dequantize(qb[0], qb[1], fmt, qb[2]).t()
+
+
+def assert_gemm_close(got, ref, what):
+    g, r = got.float(), ref.float()
+    bound = TOL * float(r.abs().max())
+    err = float((g - r).abs().max())
+    assert err <= bound, f"{what}: max|d| = {err} > {bound}"
+
+
+def no_device_timeout():
+    from tilefish_b200 import _native
+
+    assert _native.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,n,k", [(128, 256, 256), (128, 128, 128 + 128), (1, 256, 256), (16, 512, 2560), (130, 264, 288), (257, 136, 32 * 5),
+                                   (128, 6144, 2560), (384, 2560, 3072)])
+def test_gemm_matches_dequantized_oracle(K, fmt, m, n, k):
+    a, w = operands(m, n, k, seed=m + n + k)
+    out = K.gemm_blockscaled(K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt))
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16
+    assert_gemm_close(out.cpu(), O.f32_to_bf16(oracle_acc(a, w, fmt)), f"{fmt} {m}x{n}x{k}")
+    no_device_timeout()
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_gemm_bf16_a_is_quantized_on_the_fly(K, fmt):
+    a, w = operands(64, 256, 512, seed=3)
+    qb = K.quantize(w.cuda(), fmt)
+    out = K.gemm(a.cuda(), qb)
+    ref = O.gemm_bf16_a(a, O.quantize(w, fmt), fmt)
+    assert_gemm_close(out.cpu(), ref, fmt)
+    # informational second oracle: the bf16 activation against the dequantized weight (activation quantization error)
+    ob = O.quantize(w, fmt)
+    semantic = O.reference_gemm(a, O.dequantize(ob[0], ob[1], fmt, ob[2]))
+    rel = float((out.cpu().float() - semantic.float()).norm() / semantic.float().norm())
+    assert rel < {"mxfp8": 0.05, "nvfp4": 0.15}[fmt]
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,f,k", [(128, 128, 256), (200, 384, 512), (32, 3072, 2560)])
+def test_gemm_silu_gate_epilogue(K, fmt, m, f, k):
+    a, w = operands(m, 2 * f, k, seed=f + k)
+    out = K.gemm_blockscaled(K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt), epilogue="silu_gate")
+    assert out.shape == (m, f)
+    t = O.f32_to_bf16(oracle_acc(a, w, fmt))
+    ref = O.silu_gate(t[:, :f], t[:, f:])
+    # a 1-ulp difference of the bf16 GEMM result moves through silu(g)*u: bound by the GEMM tolerance times the gate's gain
+    g, r = out.cpu().float(), ref.float()
+    gain = float(t.float().abs().max()) + 1.0
+    assert float((g - r).abs().max()) <= TOL * float(t.float().abs().max()) * gain
+    frac = float(((g - r).abs() > 2.0**-7 * r.abs().max()).float().mean())
+    assert frac == 0.0
+    # and it equals the unfused pair of kernels on the same GEMM result up to that result's own rounding
+    unfused = K.silu_gate(K.gemm_blockscaled(K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt)))
+    assert torch.equal(unfused, out), "fused epilogue must reproduce gemm -> bf16 -> silu_gate bit for bit"
+    no_device_timeout()
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_gemm_residual_epilogue(K, fmt):
+    m, n, k = 130, 264, 288
+    a, w = operands(m, n, k, seed=9)
+    res0 = O.randn((m, n), 4)
+    res = res0.cuda()
+    out = K.gemm_blockscaled(K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt), epilogue="residual", residual=res)
+    plain = K.gemm_blockscaled(K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt))
+    assert torch.equal(out, plain)
+    assert torch.equal(res.cpu(), res0 + plain.cpu().float()), "residual += f32(bf16 result): one exact f32 add"
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+def test_gemm_full_size_sampled_rows(K, fmt):
+    """M = 4096, N = 6144, K = 2560 (the GEMM benchmark shape): 48 sampled rows against the oracle, plus linearity in A's rows."""
+    m, n, k = 4096, 6144, 2560
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn((m, k), generator=g).to(torch.bfloat16)
+    w = (torch.randn((n, k), generator=g) * k**-0.5).to(torch.bfloat16)
+    gs = None
+    if fmt == "nvfp4":
+        gs = torch.tensor([float(a.float().abs().max()) / 2688.0], dtype=torch.float32)
+    qa = K.quantize(a.cuda(), fmt, global_scale=gs.cuda() if gs is not None else None)
+    qb = K.quantize(w.cuda(), fmt)
+    out = K.gemm_blockscaled(qa, qb)
+    rows = torch.randint(0, m, (48,), generator=g)
+    rows[:3] = torch.tensor([0, 127, m - 1])
+    oa = O.quantize(a[rows], fmt, gs.reshape(()) if gs is not None else None)
+    ob = O.quantize(w, fmt)
+    ref = O.f32_to_bf16(O.dequantize(oa[0], oa[1], fmt, oa[2]) @ O.dequantize(ob[0], ob[1], fmt, ob[2]).t())
+    assert_gemm_close(out[rows.cuda()].cpu(), ref, f"{fmt} sampled rows")
+    # rows are independent: the same rows computed as their own small GEMM give the same bytes
+    sub = K.gemm_blockscaled(K.quantize(a[rows].cuda(), fmt, global_scale=gs.cuda() if gs is not None else None), qb)
+    assert torch.equal(sub, out[rows.cuda()])
+    no_device_timeout()
+
+
+def test_gemm_refusals(K):
+    from tilefish_b200 import TilefishPreconditionError
+
+    a, w = operands(16, 128, 64, seed=1)
+    qa, qb = K.quantize(a.cuda(), "mxfp8"), K.quantize(w.cuda(), "mxfp4")
+    with pytest.raises(TilefishPreconditionError) as e:
+        K.gemm_blockscaled(qa, qb)
+    assert e.value.kind == "dtype"
+    qb8 = K.quantize(operands(16, 128, 96, seed=1)[1].cuda(), "mxfp8")
+    with pytest.raises(TilefishPreconditionError) as e:
+        K.gemm_blockscaled(qa, qb8)
+    assert e.value.kind == "shape"
+    plain = K.quantize(w.cuda(), "mxfp8", layout="plain")
+    with pytest.raises(TilefishPreconditionError):
+        K.gemm_blockscaled(qa, plain)
+    empty = K.gemm_blockscaled(K.quantize(torch.empty((0, 64), dtype=torch.bfloat16, device="cuda"), "mxfp8"), K.quantize(w.cuda(), "mxfp8"))
+    assert empty.shape == (0, 128)

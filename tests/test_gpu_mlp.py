@@ -1,0 +1,97 @@
+"""The decoder block (residual_add_rmsnorm -> gemm + SiLU gate -> gemm) on one GPU against the CPU oracle.
+
+The oracle quantizes the activations at the same two points with the same rules and multiplies in f32. Bound:
+max|d| <= 2**-6 * max|ref| and a relative Frobenius error <= 1e-2 (re-quantizing ``a`` can flip a code where the two
+bf16 GEMM results differ by one ulp, so this is looser than a single GEMM; the reference asserts 4 * 2**-8 * max|ref| for
+a whole bf16 transformer block, python/tests/test_gpu_plan.py:333-348).
+"""
+
+import pytest
+import torch
+
+from oracle import blockscaled as O
+
+pytestmark = pytest.mark.gpu
+
+
+def make(m, h, f, seed=0):
+    x = O.randn((m, h), seed, torch.bfloat16)
+    res = O.randn((m, h), seed + 1)
+    w_n = (1 + 0.1 * O.randn((h,), seed + 2)).to(torch.bfloat16)
+    w_gu = O.randn((2 * f, h), seed + 3, torch.bfloat16, scale=h**-0.5)
+    w_d = O.randn((h, f), seed + 4, torch.bfloat16, scale=f**-0.5)
+    return x, res, w_n, w_gu, w_d
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "mxfp4", "nvfp4"])
+@pytest.mark.parametrize("m,h,f", [(1, 256, 384), (32, 2560, 3072), (200, 512, 768)])
+def test_decoder_block_matches_oracle(fmt, m, h, f):
+    from tilefish_b200 import _native
+    from tilefish_b200 import mlp as MLP
+
+    x, res, w_n, w_gu, w_d = make(m, h, f)
+    w = MLP.quantize_weights(w_n.cuda(), w_gu.cuda(), w_d.cuda(), fmt)
+    res_gpu = res.cuda()
+    y = MLP.decoder_block(x.cuda(), res_gpu, w)
+    r_ref, y_ref = O.decoder_block(x, res.clone(), w_n, O.quantize(w_gu, fmt), O.quantize(w_d, fmt), fmt)
+    assert torch.equal(res_gpu.cpu(), r_ref)
+    g, r = y.cpu().float(), y_ref.float()
+    assert float((g - r).abs().max()) <= 2.0**-6 * float(r.abs().max())
+    assert float((g - r).norm() / r.norm()) <= 1e-2
+    assert _native.device_status() == (0, 0)
+
+
+def test_stack_carries_the_residual_stream():
+    from tilefish_b200 import mlp as MLP
+
+    m, h, f = 64, 256, 384
+    layers = []
+    ref_w = []
+    for i in range(3):
+        _, _, w_n, w_gu, w_d = make(m, h, f, seed=10 * i)
+        layers.append(MLP.quantize_weights(w_n.cuda(), w_gu.cuda(), w_d.cuda(), "mxfp8"))
+        ref_w.append((w_n, O.quantize(w_gu, "mxfp8"), O.quantize(w_d, "mxfp8")))
+    x = O.randn((m, h), 99, torch.bfloat16)
+    res = torch.zeros((m, h))
+    res_gpu = res.cuda()
+    y = MLP.MlpStack(layers)(x.cuda(), res_gpu)
+    xr, rr = x, res.clone()
+    for w_n, qgu, qd in ref_w:
+        rr, xr = O.decoder_block(xr, rr, w_n, qgu, qd, "mxfp8")
+    g, r = y.cpu().float(), xr.float()
+    assert float((g - r).norm() / r.norm()) <= 2e-2
+    assert float((res_gpu.cpu() - rr).norm() / rr.norm()) <= 1e-2
+
+
+def test_sharded_weights_hold_the_bytes_of_the_full_weights():
+    """Tensor-parallel shards are cut from the quantized full weights: the sum of the shards' partial products equals the
+    single-GPU product up to the bf16 rounding of each partial (n * 2**-8 * max|ref|)."""
+    from tilefish_b200 import kernels as K
+    from tilefish_b200 import mlp as MLP
+
+    m, h, f, world = 48, 256, 512, 2
+    x, res, w_n, w_gu, w_d = make(m, h, f, seed=5)
+    for fmt in ("mxfp8", "nvfp4"):
+        full = MLP.quantize_weights(w_n.cuda(), w_gu.cuda(), w_d.cuda(), fmt)
+        y_full = MLP.decoder_block(x.cuda(), res.cuda(), full)
+        parts = []
+        for rank in range(world):
+            sh = MLP.quantize_weights(w_n.cuda(), w_gu.cuda(), w_d.cuda(), fmt, rank=rank, world=world)
+            assert sh.w_gu.shape == (2 * f // world, h) and sh.w_d.shape == (h, f // world)
+            fl = f // world
+            full_codes = full.w_gu.codes
+            assert torch.equal(sh.w_gu.codes[:fl], full_codes[rank * fl:(rank + 1) * fl])
+            assert torch.equal(sh.w_gu.codes[fl:], full_codes[f + rank * fl:f + (rank + 1) * fl])
+            parts.append(MLP.decoder_block(x.cuda(), res.cuda(), sh).float())
+        y_tp = sum(parts)
+        # mxfp8: the shards' activations quantize to the same codes (32-blocks never straddle a shard), so only the bf16
+        # rounding of each partial product differs. nvfp4: each shard derives the global scale of its slice of ``a`` from
+        # its own amax, so block scales and codes differ: the two results are two quantizations of the same product and
+        # agree to quantization noise, not to rounding.
+        err = float((y_tp - y_full.float()).abs().max())
+        top = float(y_full.float().abs().max())
+        if fmt == "mxfp8":
+            assert err <= world * 2.0**-8 * top * 1.01, (fmt, err)
+        else:
+            rel = float((y_tp - y_full.float()).norm() / y_full.float().norm())
+            assert rel <= 0.08, (fmt, rel)

@@ -39,13 +39,14 @@ SIGNATURES = {
     "tf_quantize_mxfp8": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P, c_int32, _P]),
     "tf_quantize_mxfp4": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P, c_int32, _P]),
     "tf_quantize_nvfp4": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P]),
+    "tf_quantize_nvfp4_from_amax": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P, c_int32, _P, _P, _P]),
     "tf_nvfp4_global_scale": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P]),
     "tf_swizzle_scales": (c_int32, [_P, c_int64, c_int64, _P, _P]),
     "tf_unswizzle_scales": (c_int32, [_P, c_int64, c_int64, _P, _P]),
-    "tf_residual_add_rmsnorm": (c_int32, [_P, _P, _P, _P, c_int64, c_int64, c_float, c_int32, _P, _P, c_int32, _P, _P]),
+    "tf_residual_add_rmsnorm": (c_int32, [_P, _P, _P, _P, c_int64, c_int64, c_float, c_int32, _P, _P, c_int32, _P, _P, _P]),
     "tf_silu_gate": (c_int32, [_P, c_int64, c_int64, c_int64, _P, c_int64, _P]),
     "tf_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int32, c_int32]),
-    "tf_gemm_blockscaled": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, c_int64, _P]),
+    "tf_gemm_blockscaled": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, _P, c_int64, _P]),
 }
 
 _lib = None

@@ -1,4 +1,4 @@
-// Library identity, the thread-local last error and the device status word.
+// Library identity and the thread-local last error.
 #include <string>
 
 #include "common.cuh"
@@ -32,9 +32,6 @@ int sm_count() {
   return cached;
 }
 
-// Written by kernels whose bounded waits ran out: [0] = status, [1] = detail (which wait, which block).
-__device__ int g_device_status[2];
-
 }  // namespace tf
 
 using namespace tf;
@@ -43,20 +40,5 @@ extern "C" {
 
 const char* tf_version(void) { return "tilefish_b200 0.1.0 (sm_100a)"; }
 const char* tf_last_error(void) { return g_last_error.c_str(); }
-
-tf_status tf_device_status(int32_t* status, int32_t* detail) {
-  clear_error();
-  TF_CHECK_ARG(status != nullptr, "%s: null pointer", __func__);
-  int host[2] = {0, 0};
-  TF_CUDA(cudaDeviceSynchronize());
-  TF_CUDA(cudaMemcpyFromSymbol(host, g_device_status, sizeof(host)));
-  if (host[0] != 0) {
-    const int zero[2] = {0, 0};
-    TF_CUDA(cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero)));
-  }
-  *status = host[0];
-  if (detail) *detail = host[1];
-  return TF_OK;
-}
 
 }  // extern "C"

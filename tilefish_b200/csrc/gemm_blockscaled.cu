@@ -1,8 +1,621 @@
-// placeholder until the tcgen05 kernel lands
+// Block-scaled GEMM for sm_100a: out[M,N] = bf16( sum_k deq(a)[m,k] * deq(b)[n,k] ), f32 accumulation in tensor memory.
+//
+// One persistent CTA per SM walks output tiles of 128 x BLOCK_N. Three warp roles:
+//   warp 0   producer: TMA tiled loads of the A and B code tiles (128-byte swizzle) and bulk copies of the pre-swizzled
+//            scale tiles into a ring of shared-memory stages, signalled through mbarriers (complete_tx)
+//   warp 1   MMA issuer: copies the scale tiles shared -> tensor memory (tcgen05.cp) and issues
+//            tcgen05.mma.kind::{mxf8f6f4, mxf4, mxf4nvf4}.block_scale, 4 per stage (32 bytes of K each); tcgen05.commit frees
+//            the stage and, after the last one, hands the accumulator to the epilogue
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), scale, fused epilogue (none / SiLU gate /
+//            residual add), bf16 stores
+// No TMA multicast, no clusters. Every mbarrier wait is bounded (about one second): on a timeout the kernel records
+// TF_ERR_DEVICE_TIMEOUT in a device status word, every role leaves its loop, tensor memory is freed and the kernel returns.
+//
+// Scale layout consumed: the 512-byte 128x4 tiles described in the header; one tile feeds 4 tensor-memory columns through
+// tcgen05.cp.32x128b.warpx4, byte k of a column being the scale of K-block k (selected by the SF-id field of the instruction
+// descriptor for the MX formats; NVFP4 uses all four bytes per MMA).
+#include <cuda.h>
+
 #include "common.cuh"
-using namespace tf;
-extern "C" int64_t tf_gemm_workspace_bytes(int64_t, int64_t, int64_t, int32_t, int32_t) { return 0; }
-extern "C" tf_status tf_gemm_blockscaled(const void*, const void*, const float*, const void*, const void*, const float*, void*, int64_t, int64_t,
-                                         int64_t, int64_t, int32_t, int32_t, void*, void*, int64_t, void*) {
-  return fail(TF_ERR_UNSUPPORTED, "tf_gemm_blockscaled: not built yet");
+
+namespace tf {
+
+__device__ int g_device_status[2];  // [0] status, [1] detail
+
+constexpr int kBlockM = 128;
+constexpr int kStageKBytes = 128;  // bytes of K per row per stage: one 128-byte swizzle atom
+constexpr int kAStageBytes = kBlockM * kStageKBytes;
+constexpr int kGemmThreads = 192;
+constexpr int kSmemLimit = 227 * 1024;
+constexpr unsigned long long kWaitLimitNs = 1000000000ull;
+
+template <int FMT>
+struct FmtTraits;
+template <>
+struct FmtTraits<TF_FMT_MXFP8> {
+  static constexpr int kSfTiles = 1;  // 512-byte scale tiles per operand row-tile per stage
+  static constexpr uint32_t kElemFormat = 0, kScaleIsE8 = 1;
+};
+template <>
+struct FmtTraits<TF_FMT_MXFP4> {
+  static constexpr int kSfTiles = 2;
+  static constexpr uint32_t kElemFormat = 1, kScaleIsE8 = 1;
+};
+template <>
+struct FmtTraits<TF_FMT_NVFP4> {
+  static constexpr int kSfTiles = 4;
+  static constexpr uint32_t kElemFormat = 1, kScaleIsE8 = 0;
+};
+
+template <int FMT, int BLOCK_N>
+struct TileCfg {
+  static constexpr int kNB = BLOCK_N / 128;  // 128-row halves of the B tile
+  static constexpr int kST = FmtTraits<FMT>::kSfTiles;
+  static constexpr int kBStageBytes = BLOCK_N * kStageKBytes;
+  static constexpr int kSfaStageBytes = kST * 512;
+  static constexpr int kSfbStageBytes = kST * 512 * kNB;
+  static constexpr int kStageBytes = kAStageBytes + kBStageBytes + kSfaStageBytes + kSfbStageBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kStagesRaw = (kSmemLimit - 1024 - kBarrierBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  // two scale buffers in tensor memory, used by alternate stages, so that the copy of the next stage's scales does not
+  // have to wait for the MMAs that still read the current ones
+  static constexpr int kTmemSfSet = kST * 4 * (1 + kNB);  // columns of one buffer: A scales then B scales
+  static constexpr int kTmemSfa = BLOCK_N;                // first column of the A scales of buffer 0
+  static constexpr int kTmemSfb = BLOCK_N + kST * 4;      // first column of the B scales of buffer 0
+  static constexpr int kTmemUsed = BLOCK_N + 2 * kTmemSfSet;
+  static constexpr int kTmemCols = kTmemUsed <= 256 ? 256 : 512;
+};
+
+struct GemmParams {
+  int m, n, n_rows_b, k_bytes;
+  int num_k_stages, sf_col_tiles;  // K stages per tile; 512-byte tiles per scale row-tile
+  int m_blocks, n_blocks, num_tiles;
+  int sfb_row_tiles;
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  const float* a_gs;
+  const float* b_gs;
+  uint16_t* out;
+  int64_t ldo;
+  float* residual;
+  unsigned int* out_amax;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the limit ran out here or another role already gave up (abort flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  for (uint32_t spins = 1;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 0x3F) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        *abort_flag = 1;
+        if (atomicCAS(&g_device_status[0], 0, TF_ERR_DEVICE_TIMEOUT) == 0) g_device_status[1] = where * 65536 + (int)blockIdx.x;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map),
+               "r"(x), "r"(y), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+template <int FMT>
+__device__ __forceinline__ void tc_mma(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if (FMT == TF_FMT_MXFP8) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else if (FMT == TF_FMT_MXFP4) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+// 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets row (lane base + t), v[j] = column (base + j).
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, "
+      "%22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+        "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+        "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]),
+        "=r"(v[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile stored by TMA with the 128-byte swizzle: rows 128 bytes apart, 8-row
+// groups 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t desc_sw128(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Descriptor of one 512-byte scale tile for tcgen05.cp.32x128b: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t desc_sf(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 32) | ((uint64_t)1 << 46);
+}
+
+__device__ __forceinline__ uint64_t make_desc(uint32_t lo, uint32_t hi) { return ((uint64_t)hi << 32) | lo; }
+// True in exactly one lane of a converged warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xFFFFFFFF;\n selp.b32 %0, 1, 0, p;\n}" : "=r"(pred));
+  return pred != 0;
+}
+
+__device__ __forceinline__ float silu_f32(float g) { return __fmul_rn(g, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)))); }
+
+// ---- the kernel ------------------------------------------------------------------------------------------------------------
+template <int FMT, int BLOCK_N, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                                            const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
+  using Cfg = TileCfg<FMT, BLOCK_N>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kNB = Cfg::kNB;
+  constexpr int kST = Cfg::kST;
+  constexpr int kOutCols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;  // output columns per tile
+  static_assert(EPI != TF_EPI_SILU_GATE || BLOCK_N == 256, "the SiLU-gate epilogue pairs a 128-column gate tile with its up tile");
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a = smem_base;
+  const uint32_t smem_b = smem_a + kStages * kAStageBytes;
+  const uint32_t smem_sfa = smem_b + kStages * Cfg::kBStageBytes;
+  const uint32_t smem_sfb = smem_sfa + kStages * Cfg::kSfaStageBytes;
+  const uint32_t bars = smem_sfb + kStages * Cfg::kSfbStageBytes;  // 8-byte aligned
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages, bar_tmem_full = bars + 16 * kStages, bar_tmem_empty = bar_tmem_full + 8;
+  const uint32_t tmem_slot = bar_tmem_empty + 8;
+  const uint32_t abort_slot = tmem_slot + 4;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    mbar_init(bar_tmem_full, 1);
+    mbar_init(bar_tmem_empty, 4);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // whole warp: allocate tensor memory
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+        const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
+        int b_row[kNB], b_rt[kNB];
+        bool b_ok[kNB];
+#pragma unroll
+        for (int nb = 0; nb < kNB; ++nb) {
+          b_row[nb] = (EPI == TF_EPI_SILU_GATE) ? nb * p.n + n_blk * 128 : n_blk * BLOCK_N + nb * 128;
+          b_rt[nb] = b_row[nb] >> 7;
+          b_ok[nb] = b_row[nb] < p.n_rows_b;
+        }
+        for (int ks = 0; ks < p.num_k_stages; ++ks) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) {
+            ok = false;
+            break;
+          }
+          int sf_tiles = p.sf_col_tiles - ks * kST;
+          sf_tiles = sf_tiles > kST ? kST : sf_tiles;
+          const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
+          uint32_t tx = kAStageBytes + sf_bytes;
+#pragma unroll
+          for (int nb = 0; nb < kNB; ++nb)
+            if (b_ok[nb]) tx += 128 * kStageKBytes + sf_bytes;
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_expect_tx(full, tx);
+          tma_load_2d(smem_a + stage * kAStageBytes, &tma_a, ks * kStageKBytes, m_blk * kBlockM, full);
+          bulk_load(smem_sfa + stage * Cfg::kSfaStageBytes, p.sfa + ((int64_t)m_blk * p.sf_col_tiles + (int64_t)ks * kST) * 512, sf_bytes, full);
+#pragma unroll
+          for (int nb = 0; nb < kNB; ++nb) {
+            if (b_ok[nb]) {
+              tma_load_2d(smem_b + stage * Cfg::kBStageBytes + nb * 128 * kStageKBytes, &tma_b, ks * kStageKBytes, b_row[nb], full);
+              bulk_load(smem_sfb + stage * Cfg::kSfbStageBytes + nb * kST * 512,
+                        p.sfb + ((int64_t)b_rt[nb] * p.sf_col_tiles + (int64_t)ks * kST) * 512, sf_bytes, full);
+            }
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        // give copies already in flight time to land before shared memory is released
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    // The whole warp runs the loops (so every value below is warp-uniform and lives in the uniform datapath); one elected lane
+    // issues the tcgen05 instructions. A full stage is straight-line code: its descriptors differ from the stage's base by
+    // compile-time constants added to the low word (the 14-bit address field cannot carry out for addresses below 256 KB).
+    constexpr uint32_t idesc_base = (FmtTraits<FMT>::kElemFormat << 7) | (FmtTraits<FMT>::kElemFormat << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                                    (FmtTraits<FMT>::kScaleIsE8 << 23) | ((uint32_t)(kBlockM >> 4) << 24);
+    constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, SWIZZLE_128B
+    constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128 B, version 1, no swizzle
+    const bool elected = elect_one();
+    const uint32_t tmem_acc = tmem_base;
+    int stage = 0;
+    uint32_t phase = 0, tile_phase = 0, sf_buf = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      ok = mbar_wait(bar_tmem_empty, tile_phase ^ 1, abort_flag, 2);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int n_blk = tile / p.m_blocks;
+      bool all_b = true;
+      bool b_ok[kNB];
+#pragma unroll
+      for (int nb = 0; nb < kNB; ++nb) {
+        b_ok[nb] = ((EPI == TF_EPI_SILU_GATE) ? nb * p.n + n_blk * 128 : n_blk * BLOCK_N + nb * 128) < p.n_rows_b;
+        all_b = all_b && b_ok[nb];
+      }
+      for (int ks = 0; ks < p.num_k_stages; ++ks) {
+        ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_sfa = tmem_base + Cfg::kTmemSfa + sf_buf * Cfg::kTmemSfSet;
+        const uint32_t tmem_sfb = tmem_base + Cfg::kTmemSfb + sf_buf * Cfg::kTmemSfSet;
+        sf_buf ^= 1;
+        const uint32_t sfa_lo = ((smem_sfa + stage * Cfg::kSfaStageBytes) & 0x3FFFFu) >> 4;
+        const uint32_t sfb_lo = ((smem_sfb + stage * Cfg::kSfbStageBytes) & 0x3FFFFu) >> 4;
+        const uint32_t a_lo = (((smem_a + stage * kAStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
+        const uint32_t b_lo = (((smem_b + stage * Cfg::kBStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
+        const int sf_left = p.sf_col_tiles - ks * kST;
+        const int k_left = p.k_bytes - ks * kStageKBytes;
+        const uint32_t first = (ks > 0) ? 1u : 0u;
+        if (elected) {
+          if (sf_left >= kST && k_left >= kStageKBytes && all_b) {
+#pragma unroll
+            for (int t = 0; t < kST; ++t) {
+              tc_cp_sf(tmem_sfa + t * 4, make_desc(sfa_lo + t * 32, kDescHiSf));
+#pragma unroll
+              for (int nb = 0; nb < kNB; ++nb) tc_cp_sf(tmem_sfb + (t * kNB + nb) * 4, make_desc(sfb_lo + (nb * kST + t) * 32, kDescHiSf));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              constexpr int kDummy = 0;
+              (void)kDummy;
+              const int t = (FMT == TF_FMT_MXFP8) ? 0 : (FMT == TF_FMT_MXFP4) ? (j >> 1) : j;
+              const uint32_t sf_id = (FMT == TF_FMT_MXFP8) ? (uint32_t)j : (FMT == TF_FMT_MXFP4) ? (uint32_t)((j & 1) * 2) : 0u;
+              tc_mma<FMT>(tmem_acc, make_desc(a_lo + j * 2, kDescHiSw128), make_desc(b_lo + j * 2, kDescHiSw128),
+                          idesc_base | (sf_id << 4) | (sf_id << 29), tmem_sfa + t * 4, tmem_sfb + t * kNB * 4, j > 0 ? 1u : first);
+            }
+          } else {  // ragged stage: fewer scale tiles, fewer MMAs or a B half that lies outside the matrix
+            const int sf_tiles = sf_left > kST ? kST : sf_left;
+            for (int t = 0; t < sf_tiles; ++t) {
+              tc_cp_sf(tmem_sfa + t * 4, make_desc(sfa_lo + t * 32, kDescHiSf));
+#pragma unroll
+              for (int nb = 0; nb < kNB; ++nb)
+                if (b_ok[nb]) tc_cp_sf(tmem_sfb + (t * kNB + nb) * 4, make_desc(sfb_lo + (nb * kST + t) * 32, kDescHiSf));
+            }
+            const int n_mma = k_left >= kStageKBytes ? 4 : (k_left + 31) >> 5;
+            for (int j = 0; j < n_mma; ++j) {
+              const int t = (FMT == TF_FMT_MXFP8) ? 0 : (FMT == TF_FMT_MXFP4) ? (j >> 1) : j;
+              const uint32_t sf_id = (FMT == TF_FMT_MXFP8) ? (uint32_t)j : (FMT == TF_FMT_MXFP4) ? (uint32_t)((j & 1) * 2) : 0u;
+              tc_mma<FMT>(tmem_acc, make_desc(a_lo + j * 2, kDescHiSw128), make_desc(b_lo + j * 2, kDescHiSw128),
+                          idesc_base | (sf_id << 4) | (sf_id << 29), tmem_sfa + t * 4, tmem_sfb + t * kNB * 4, j > 0 ? 1u : first);
+            }
+          }
+          tc_commit(bar_empty + 8 * stage);  // the stage is free once these MMAs have read it
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
+        }
+      }
+      if (!ok) break;
+      if (elected) tc_commit(bar_tmem_full);  // accumulator complete
+      __syncwarp();
+      tile_phase ^= 1;
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5; warp w reads lanes 32*(w%4) .. +31) ----------------
+    const int q = warp & 3;
+    const float alpha = (FMT == TF_FMT_NVFP4) ? __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs)) : 1.0f;
+    uint32_t tile_phase = 0;
+    uint32_t amax2 = 0;  // running max of |out| as two packed bf16 magnitudes
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+      const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
+      bool ok = mbar_wait(bar_tmem_full, tile_phase, abort_flag, 4);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_blk * kBlockM + q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+      const int col0 = n_blk * kOutCols;
+#pragma unroll 1
+      for (int c = 0; c < kOutCols / 32; ++c) {
+        uint32_t v[32];
+        tc_ld32(t_row + c * 32, v);
+        uint32_t packed[16];
+        if (EPI == TF_EPI_SILU_GATE) {
+          uint32_t u[32];
+          tc_ld32(t_row + 128 + c * 32, u);
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            // the GEMM result is bf16 (one rounding); the gate then reads it back as f32, as the unfused graph does
+            const uint32_t g2 = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
+            const uint32_t u2 = pack_bf16x2(__fmul_rn(__uint_as_float(u[2 * j]), alpha), __fmul_rn(__uint_as_float(u[2 * j + 1]), alpha));
+            const float lo = __fmul_rn(silu_f32(bf16lo_to_f32(g2)), bf16lo_to_f32(u2));
+            const float hi = __fmul_rn(silu_f32(bf16hi_to_f32(g2)), bf16hi_to_f32(u2));
+            packed[j] = pack_bf16x2(lo, hi);
+          }
+        } else {
+          tc_wait_ld();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
+        }
+        if (row < p.m) {
+          const int col = col0 + c * 32;
+          uint16_t* orow = p.out + (int64_t)row * p.ldo + col;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col + g * 8 + 8 <= p.n) {
+              *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+              if (p.out_amax) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) amax2 = __vmaxu2(amax2, packed[4 * g + e] & 0x7FFF7FFFu);
+              }
+              if (EPI == TF_EPI_RESIDUAL) {
+                float4* rp = reinterpret_cast<float4*>(p.residual + (int64_t)row * p.n + col + g * 8);
+                float4 r0 = rp[0], r1 = rp[1];
+                r0.x = __fadd_rn(r0.x, bf16lo_to_f32(packed[4 * g]));
+                r0.y = __fadd_rn(r0.y, bf16hi_to_f32(packed[4 * g]));
+                r0.z = __fadd_rn(r0.z, bf16lo_to_f32(packed[4 * g + 1]));
+                r0.w = __fadd_rn(r0.w, bf16hi_to_f32(packed[4 * g + 1]));
+                r1.x = __fadd_rn(r1.x, bf16lo_to_f32(packed[4 * g + 2]));
+                r1.y = __fadd_rn(r1.y, bf16hi_to_f32(packed[4 * g + 2]));
+                r1.z = __fadd_rn(r1.z, bf16lo_to_f32(packed[4 * g + 3]));
+                r1.w = __fadd_rn(r1.w, bf16hi_to_f32(packed[4 * g + 3]));
+                rp[0] = r0;
+                rp[1] = r1;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tmem_empty);
+      tile_phase ^= 1;
+    }
+    if (p.out_amax) {  // one atomic per warp
+      uint32_t mx = max(amax2 & 0xFFFFu, amax2 >> 16);
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+      if (lane == 0 && mx) atomicMax(p.out_amax, mx << 16);
+    }
+  }
+
+  // ---------------- teardown: every thread arrives, then the allocating warp frees tensor memory ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+  }
+}
+
+// ---- host side -------------------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess && qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// A [rows, k_bytes] byte matrix, boxes of 128 rows x 128 bytes, 128-byte swizzle, out-of-range bytes read as zero.
+static tf_status make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(TF_ERR_CUDA, "tf_gemm_blockscaled: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {(cuuint64_t)k_bytes, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)k_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)kStageKBytes, 128u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TF_ERR_CUDA, "tf_gemm_blockscaled: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return TF_OK;
+}
+
+template <int FMT, int BLOCK_N, int EPI>
+static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+  using Cfg = TileCfg<FMT, BLOCK_N>;
+  auto kernel = gemm_blockscaled_kernel<FMT, BLOCK_N, EPI>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  TF_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    TF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    configured_dev = dev;
+  }
+  constexpr int out_cols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;
+  p.n_blocks = (p.n + out_cols - 1) / out_cols;
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
+  TF_LAUNCH_CHECK();
+  return TF_OK;
+}
+
+template <int FMT>
+static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int epilogue, cudaStream_t stream) {
+  if (epilogue == TF_EPI_SILU_GATE) return launch_gemm<FMT, 256, TF_EPI_SILU_GATE>(ta, tb, p, stream);
+  if (epilogue == TF_EPI_RESIDUAL)
+    return p.n > 128 ? launch_gemm<FMT, 256, TF_EPI_RESIDUAL>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_RESIDUAL>(ta, tb, p, stream);
+  return p.n > 128 ? launch_gemm<FMT, 256, TF_EPI_NONE>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_NONE>(ta, tb, p, stream);
+}
+
+}  // namespace tf
+
+using namespace tf;
+
+extern "C" {
+
+tf_status tf_device_status(int32_t* status, int32_t* detail) {
+  clear_error();
+  TF_CHECK_ARG(status != nullptr, "%s: null pointer", __func__);
+  int host[2] = {0, 0};
+  TF_CUDA(cudaDeviceSynchronize());
+  TF_CUDA(cudaMemcpyFromSymbol(host, g_device_status, sizeof(host)));
+  if (host[0] != 0) {
+    const int zero[2] = {0, 0};
+    TF_CUDA(cudaMemcpyToSymbol(g_device_status, zero, sizeof(zero)));
+  }
+  *status = host[0];
+  if (detail) *detail = host[1];
+  return TF_OK;
+}
+
+int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue) {
+  (void)m;
+  (void)n;
+  (void)k;
+  (void)format;
+  (void)epilogue;
+  return 0;
+}
+
+tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
+                              const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
+                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* workspace, int64_t workspace_bytes, void* stream_) {
+  clear_error();
+  (void)workspace;
+  (void)workspace_bytes;
+  cudaStream_t stream = (cudaStream_t)stream_;
+  TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", __func__, format);
+  TF_CHECK_ARG(epilogue >= TF_EPI_NONE && epilogue <= TF_EPI_RESIDUAL, "%s: unknown epilogue %d", __func__, epilogue);
+  TF_CHECK_ARG(m >= 0 && n > 0 && k > 0, "%s: bad shape m=%lld n=%lld k=%lld", __func__, (long long)m, (long long)n, (long long)k);
+  if (m == 0) return TF_OK;
+  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && out, "%s: null pointer", __func__);
+  TF_CHECK_ARG(format != TF_FMT_NVFP4 || (a_global_scale && b_global_scale), "%s: nvfp4 needs both global scales", __func__);
+  TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || epilogue_arg, "%s: the residual epilogue needs its f32 residual", __func__);
+  if (k % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: k=%lld is not a multiple of 32", __func__, (long long)k);
+  if (n % 8 != 0 || ldo % 8 != 0 || ldo < n) return fail(TF_ERR_ALIGNMENT, "%s: n and ldo must be multiples of 8 with ldo >= n", __func__);
+  if (epilogue == TF_EPI_SILU_GATE && n % 128 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: the SiLU-gate epilogue needs n %% 128 == 0", __func__);
+  if (m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return fail(TF_ERR_UNSUPPORTED, "%s: a dimension exceeds 2^30", __func__);
+  TF_CHECK_ALIGNED(a_codes, 16, "a_codes");
+  TF_CHECK_ALIGNED(b_codes, 16, "b_codes");
+  TF_CHECK_ALIGNED(a_scales, 16, "a_scales");
+  TF_CHECK_ALIGNED(b_scales, 16, "b_scales");
+  TF_CHECK_ALIGNED(out, 16, "out");
+  if (epilogue == TF_EPI_RESIDUAL) TF_CHECK_ALIGNED(epilogue_arg, 16, "residual");
+
+  const int64_t k_bytes = (format == TF_FMT_MXFP8) ? k : k / 2;
+  const int64_t n_rows_b = (epilogue == TF_EPI_SILU_GATE) ? 2 * n : n;
+  const int64_t block = (format == TF_FMT_NVFP4) ? 16 : 32;
+  CUtensorMap ta, tb;
+  tf_status st = make_operand_map(&ta, a_codes, m, k_bytes);
+  if (st != TF_OK) return st;
+  st = make_operand_map(&tb, b_codes, n_rows_b, k_bytes);
+  if (st != TF_OK) return st;
+
+  GemmParams p;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.n_rows_b = (int)n_rows_b;
+  p.k_bytes = (int)k_bytes;
+  p.num_k_stages = (int)((k_bytes + kStageKBytes - 1) / kStageKBytes);
+  p.sf_col_tiles = (int)((k / block + 3) / 4);
+  p.m_blocks = (int)((m + kBlockM - 1) / kBlockM);
+  p.n_blocks = 0;
+  p.num_tiles = 0;
+  p.sfb_row_tiles = (int)((n_rows_b + 127) / 128);
+  p.sfa = static_cast<const uint8_t*>(a_scales);
+  p.sfb = static_cast<const uint8_t*>(b_scales);
+  p.a_gs = a_global_scale;
+  p.b_gs = b_global_scale;
+  p.out = static_cast<uint16_t*>(out);
+  p.ldo = ldo;
+  p.residual = static_cast<float*>(epilogue_arg);
+  p.out_amax = reinterpret_cast<unsigned int*>(out_amax);
+  switch (format) {
+    case TF_FMT_MXFP8: return dispatch_gemm<TF_FMT_MXFP8>(ta, tb, p, epilogue, stream);
+    case TF_FMT_MXFP4: return dispatch_gemm<TF_FMT_MXFP4>(ta, tb, p, epilogue, stream);
+    default: return dispatch_gemm<TF_FMT_NVFP4>(ta, tb, p, epilogue, stream);
+  }
+}
+
+}  // extern "C"

@@ -5,57 +5,67 @@
 // bytes are the same as the torch restatement's:
 //   MX     amax on the 15 magnitude bits; E = amax >> 7; scale = amax == 0 ? 127 : max(E - emax, 0);
 //          code = cast(f32(x) * 2^(127 - scale))                      (exact product)
-//   NVFP4  s8 = e4m3(amax / (6 * gs)); d = f32(s8) * gs; code = e2m1(f32(x) * (1 / d)); zero when gs == 0 or d == 0
+//   NVFP4  s8 = e4m3(amax * (1 / (6 * gs))); d = f32(s8) * gs; code = e2m1(f32(x) * (1 / d)); zero when gs == 0 or d == 0
 #pragma once
 
 #include "common.cuh"
 
 namespace tf {
 
-// Maximum of the 15 magnitude bits of the 8 bf16 words of v.
+// Maximum of the 15 magnitude bits of the 8 bf16 words of v (packed 16-bit unsigned maxima, then the two halves).
 __device__ __forceinline__ uint32_t amax_bits8(const uint4& v) {
-  uint32_t m = max(v.x & 0x7FFFu, (v.x >> 16) & 0x7FFFu);
-  m = max(m, max(v.y & 0x7FFFu, (v.y >> 16) & 0x7FFFu));
-  m = max(m, max(v.z & 0x7FFFu, (v.z >> 16) & 0x7FFFu));
-  m = max(m, max(v.w & 0x7FFFu, (v.w >> 16) & 0x7FFFu));
-  return m;
+  const uint32_t k = 0x7FFF7FFFu;
+  uint32_t t = __vimax3_u16x2(v.x & k, v.y & k, v.z & k);
+  t = __vimax3_u16x2(t, v.w & k, 0u);
+  return max(t & 0xFFFFu, t >> 16);
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
 }
 
 // Quantizes the 8 bf16 values of `v`. All 32 lanes of the warp must call it together (lanes without data pass zeros).
 // Returns the packed codes in c0 (and c1 for 8-bit elements) and the scale byte of the lane's block.
+// nvfp4: gs is the tensor's global scale and inv_t = 1 / (6 * gs), both uniform over the kernel.
 template <int FMT>
-__device__ __forceinline__ void quantize_vec8(const uint4& v, float gs, uint32_t& c0, uint32_t& c1, uint32_t& scale) {
+__device__ __forceinline__ void quantize_vec8(const uint4& v, float gs, float inv_t, uint32_t& c0, uint32_t& c1, uint32_t& scale) {
   uint32_t m = amax_bits8(v);
   m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
   if (FMT != TF_FMT_NVFP4) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 2));
 
-  float inv;
-  bool zero = false;
   if (FMT == TF_FMT_NVFP4) {
     const float amax = __uint_as_float(m << 16);
     uint32_t s8 = 0;
-    if (gs != 0.0f) s8 = cvt_e4m3x2(__fdiv_rn(amax, __fmul_rn(6.0f, gs)), 0.0f) & 0xFFu;
+    if (gs != 0.0f && m != 0) s8 = cvt_e4m3x2(__fmul_rn(amax, inv_t), 0.0f) & 0xFFu;
     const float d = __fmul_rn(e4m3_to_f32(s8), gs);
-    zero = (d == 0.0f);
-    inv = zero ? 0.0f : __fdiv_rn(1.0f, d);
+    const bool zero = (d == 0.0f);
+    const float inv = zero ? 0.0f : __frcp_rn(d);
     scale = s8;
-  } else {
-    const int emax = (FMT == TF_FMT_MXFP8) ? 8 : 2;
-    const int e = (int)(m >> 7) - emax;
-    scale = (m == 0) ? 127u : (uint32_t)max(e, 0);
-    inv = __uint_as_float((254u - scale) << 23);
+    c0 = cvt_e2m1x2(__fmul_rn(bf16lo_to_f32(v.x), inv), __fmul_rn(bf16hi_to_f32(v.x), inv)) |
+         (cvt_e2m1x2(__fmul_rn(bf16lo_to_f32(v.y), inv), __fmul_rn(bf16hi_to_f32(v.y), inv)) << 8) |
+         (cvt_e2m1x2(__fmul_rn(bf16lo_to_f32(v.z), inv), __fmul_rn(bf16hi_to_f32(v.z), inv)) << 16) |
+         (cvt_e2m1x2(__fmul_rn(bf16lo_to_f32(v.w), inv), __fmul_rn(bf16hi_to_f32(v.w), inv)) << 24);
+    if (zero) c0 = 0;
+    c1 = 0;
+    return;
   }
 
-  const float f0 = __fmul_rn(bf16lo_to_f32(v.x), inv), f1 = __fmul_rn(bf16hi_to_f32(v.x), inv);
-  const float f2 = __fmul_rn(bf16lo_to_f32(v.y), inv), f3 = __fmul_rn(bf16hi_to_f32(v.y), inv);
-  const float f4 = __fmul_rn(bf16lo_to_f32(v.z), inv), f5 = __fmul_rn(bf16hi_to_f32(v.z), inv);
-  const float f6 = __fmul_rn(bf16lo_to_f32(v.w), inv), f7 = __fmul_rn(bf16hi_to_f32(v.w), inv);
+  const int emax = (FMT == TF_FMT_MXFP8) ? 8 : 2;
+  const int e = (int)(m >> 7) - emax;
+  scale = (m == 0) ? 127u : (uint32_t)max(e, 0);
+  // 2^(127 - scale) as two packed bf16: a power of two times a bf16 is exact in bf16 (a result below the normal range loses
+  // bits, but it is then far below half of the smallest code and becomes a signed zero either way)
+  const uint32_t inv1 = (254u - scale) << 7;
+  const uint32_t inv2 = inv1 | (inv1 << 16);
+  const uint32_t q0 = mul_bf16x2(v.x, inv2), q1 = mul_bf16x2(v.y, inv2), q2 = mul_bf16x2(v.z, inv2), q3 = mul_bf16x2(v.w, inv2);
   if (FMT == TF_FMT_MXFP8) {
-    c0 = cvt_e4m3x2(f0, f1) | (cvt_e4m3x2(f2, f3) << 16);
-    c1 = cvt_e4m3x2(f4, f5) | (cvt_e4m3x2(f6, f7) << 16);
+    c0 = cvt_e4m3x2(bf16lo_to_f32(q0), bf16hi_to_f32(q0)) | (cvt_e4m3x2(bf16lo_to_f32(q1), bf16hi_to_f32(q1)) << 16);
+    c1 = cvt_e4m3x2(bf16lo_to_f32(q2), bf16hi_to_f32(q2)) | (cvt_e4m3x2(bf16lo_to_f32(q3), bf16hi_to_f32(q3)) << 16);
   } else {
-    c0 = cvt_e2m1x2(f0, f1) | (cvt_e2m1x2(f2, f3) << 8) | (cvt_e2m1x2(f4, f5) << 16) | (cvt_e2m1x2(f6, f7) << 24);
-    if (zero) c0 = 0;
+    c0 = cvt_e2m1x2(bf16lo_to_f32(q0), bf16hi_to_f32(q0)) | (cvt_e2m1x2(bf16lo_to_f32(q1), bf16hi_to_f32(q1)) << 8) |
+         (cvt_e2m1x2(bf16lo_to_f32(q2), bf16hi_to_f32(q2)) << 16) | (cvt_e2m1x2(bf16lo_to_f32(q3), bf16hi_to_f32(q3)) << 24);
     c1 = 0;
   }
 }

@@ -11,13 +11,19 @@ constexpr int kQuantThreads = 256;
 constexpr int kQuantUnroll = 4;
 
 // Block = (TPR threads along the row) x (256 / TPR rows); rows are taken grid-stride.
+// gs_ptr holds the nvfp4 global scale, or (gs_out != nullptr) the tensor's amax from which it is derived here.
 template <int FMT>
 __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint4* __restrict__ x, int64_t m, int64_t k, int64_t ldx_vec,
                                                                       uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                                                                      int swizzled, const float* __restrict__ gs_ptr) {
+                                                                      int swizzled, const float* __restrict__ gs_ptr, float* __restrict__ gs_out) {
   const int tpr = blockDim.x;
   const int nvec = (int)(k >> 3);
-  const float gs = (FMT == TF_FMT_NVFP4) ? __ldg(gs_ptr) : 0.0f;
+  float gs = (FMT == TF_FMT_NVFP4) ? __ldg(gs_ptr) : 0.0f;
+  if (FMT == TF_FMT_NVFP4 && gs_out != nullptr) {
+    gs = __fdiv_rn(gs, 2688.0f);
+    if (blockIdx.x == 0 && threadIdx.x == 0 && threadIdx.y == 0) gs_out[0] = gs;
+  }
+  const float inv_t = (FMT == TF_FMT_NVFP4 && gs != 0.0f) ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
   const int64_t row_stride = (int64_t)gridDim.x * blockDim.y;
   // Both loops run the same number of times for every thread of the block, so the warp shuffles inside quantize_vec8 always
   // see whole warps; threads without data (row >= m or vector >= nvec) quantize zeros and store nothing. nvec is a
@@ -39,7 +45,7 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
       for (int j = 0; j < kQuantUnroll; ++j) {
         if (base + j * tpr < nvec) {  // uniform over the block
           uint32_t c0, c1, sc;
-          quantize_vec8<FMT>(v[j], gs, c0, c1, sc);
+          quantize_vec8<FMT>(v[j], gs, inv_t, c0, c1, sc);
           if (has[j]) store_quantized<FMT>(codes, scales, swizzled, row, base + threadIdx.x + j * tpr, k, c0, c1, sc);
         }
       }
@@ -112,7 +118,7 @@ static tf_status check_quant_args(const char* fn, const void* x, int64_t m, int6
 
 template <int FMT>
 static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int layout,
-                                 const float* gs, cudaStream_t stream) {
+                                 const float* gs, cudaStream_t stream, float* gs_out = nullptr) {
   tf_status st = check_quant_args(fn, x, m, k, ldx, codes, scales, layout);
   if (st != TF_OK) return st;
   if (FMT == TF_FMT_NVFP4 && !gs) return fail(TF_ERR_INVALID_ARGUMENT, "%s: nvfp4 needs a global scale", fn);
@@ -128,7 +134,7 @@ static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64
   dim3 block(tpr, rpb);
   dim3 grid((unsigned)(blocks_needed < cap ? blocks_needed : cap));
   quantize_rows_kernel<FMT><<<grid, block, 0, stream>>>(static_cast<const uint4*>(x), m, k, ldx >> 3, static_cast<uint8_t*>(codes),
-                                                        static_cast<uint8_t*>(scales), layout == TF_SCALES_SWIZZLED, gs);
+                                                        static_cast<uint8_t*>(scales), layout == TF_SCALES_SWIZZLED, gs, gs_out);
   TF_LAUNCH_CHECK();
   return TF_OK;
 }
@@ -161,6 +167,19 @@ tf_status tf_quantize_nvfp4(const void* x, int64_t m, int64_t k, int64_t ldx, vo
                             const float* global_scale, void* stream) {
   clear_error();
   return launch_quantize<TF_FMT_NVFP4>(__func__, x, m, k, ldx, codes, scales, layout, global_scale, (cudaStream_t)stream);
+}
+
+tf_status tf_quantize_nvfp4_from_amax(const void* x, int64_t m, int64_t k, int64_t ldx, void* codes, void* scales, int32_t layout,
+                                      const float* amax, float* global_scale_out, void* stream) {
+  clear_error();
+  TF_CHECK_ARG(amax && global_scale_out, "%s: null pointer", __func__);
+  if (m == 0) {  // no kernel runs for an empty tensor: derive the scale with the one-thread kernel
+    TF_CUDA(cudaMemcpyAsync(global_scale_out, amax, sizeof(float), cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
+    finalize_global_scale_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(global_scale_out);
+    TF_LAUNCH_CHECK();
+    return TF_OK;
+  }
+  return launch_quantize<TF_FMT_NVFP4>(__func__, x, m, k, ldx, codes, scales, layout, amax, (cudaStream_t)stream, global_scale_out);
 }
 
 tf_status tf_nvfp4_global_scale(const void* x, int64_t m, int64_t k, int64_t ldx, float* out, void* stream_) {

@@ -15,12 +15,15 @@ __global__ void __launch_bounds__(512) residual_add_rmsnorm_kernel(const uint4* 
                                                                    const uint4* __restrict__ w, uint4* __restrict__ out, int64_t m, int d,
                                                                    float eps, float inv_d, uint8_t* __restrict__ q_codes,
                                                                    uint8_t* __restrict__ q_scales, int q_swizzled,
-                                                                   const float* __restrict__ q_gs_ptr) {
+                                                                   const float* __restrict__ q_gs_ptr, unsigned int* __restrict__ out_amax) {
   __shared__ float warp_sums[16];
+  __shared__ unsigned int warp_amax[16];
+  uint32_t amax_bits = 0;  // over every row this thread touches; combined once at the end
   __shared__ float row_rstd;
   const int nvec = d >> 3;
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const float gs = (QFMT == TF_FMT_NVFP4) ? __ldg(q_gs_ptr) : 0.0f;
+  const float inv_t = (QFMT == TF_FMT_NVFP4 && gs != 0.0f) ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
 
   for (int64_t row = blockIdx.x; row < m; row += gridDim.x) {
     const uint4* xr = x + row * nvec;
@@ -73,28 +76,38 @@ __global__ void __launch_bounds__(512) residual_add_rmsnorm_kernel(const uint4* 
         o.z = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][4], rstd), bf16lo_to_f32(wv.z)), __fmul_rn(__fmul_rn(r[i][5], rstd), bf16hi_to_f32(wv.z)));
         o.w = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][6], rstd), bf16lo_to_f32(wv.w)), __fmul_rn(__fmul_rn(r[i][7], rstd), bf16hi_to_f32(wv.w)));
         if (out) __stcs(out + row * nvec + v, o);
+        if (out_amax) amax_bits = max(amax_bits, amax_bits8(o));
       }
       if (QFMT >= 0) {
         // uniform over the block: i * nthreads < nvec decides whether any thread has a vector in this round
         if (i * nthreads < nvec) {
           uint32_t c0, c1, sc;
-          quantize_vec8<(QFMT < 0 ? 0 : QFMT)>(o, gs, c0, c1, sc);
+          quantize_vec8<(QFMT < 0 ? 0 : QFMT)>(o, gs, inv_t, c0, c1, sc);
           if (has) store_quantized<(QFMT < 0 ? 0 : QFMT)>(q_codes, q_scales, q_swizzled, row, v, d, c0, c1, sc);
         }
       }
     }
     __syncthreads();  // warp_sums / row_rstd are reused by the next row
   }
+  if (out_amax) {  // one atomic per block
+    for (int o = 16; o > 0; o >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xFFFFFFFFu, amax_bits, o));
+    if ((tid & 31) == 0) warp_amax[tid >> 5] = amax_bits;
+    __syncthreads();
+    if (tid == 0) {
+      for (int wi = 1; wi < (nthreads >> 5); ++wi) amax_bits = max(amax_bits, warp_amax[wi]);
+      if (amax_bits) atomicMax(out_amax, amax_bits << 16);
+    }
+  }
 }
 
 template <int VPT>
 static void launch_vpt(int qfmt, dim3 grid, dim3 block, cudaStream_t s, const uint4* x, float4* res, const uint4* w, uint4* out, int64_t m, int d,
-                       float eps, float inv_d, uint8_t* qc, uint8_t* qs, int qsw, const float* qgs) {
+                       float eps, float inv_d, uint8_t* qc, uint8_t* qs, int qsw, const float* qgs, unsigned int* amax) {
   switch (qfmt) {
-    case TF_FMT_MXFP8: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP8><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
-    case TF_FMT_MXFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
-    case TF_FMT_NVFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_NVFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
-    default: residual_add_rmsnorm_kernel<VPT, -1><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs); break;
+    case TF_FMT_MXFP8: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP8><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    case TF_FMT_MXFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    case TF_FMT_NVFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_NVFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    default: residual_add_rmsnorm_kernel<VPT, -1><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
   }
 }
 
@@ -104,7 +117,7 @@ using namespace tf;
 
 extern "C" tf_status tf_residual_add_rmsnorm(const void* x, void* residual, const void* w, void* out, int64_t m, int64_t d, float eps,
                                              int32_t q_format, void* q_codes, void* q_scales, int32_t q_layout, const float* q_global_scale,
-                                             void* stream_) {
+                                             float* out_amax, void* stream_) {
   clear_error();
   cudaStream_t stream = (cudaStream_t)stream_;
   TF_CHECK_ARG(x && residual && w, "%s: null pointer", __func__);
@@ -145,10 +158,10 @@ extern "C" tf_status tf_residual_add_rmsnorm(const void* x, void* residual, cons
   uint8_t* qs = static_cast<uint8_t*>(q_scales);
   const int qsw = q_layout == TF_SCALES_SWIZZLED;
   switch (vpt) {
-    case 1: launch_vpt<1>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
-    case 2: launch_vpt<2>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
-    case 4: launch_vpt<4>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
-    default: launch_vpt<8>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale); break;
+    case 1: launch_vpt<1>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale, reinterpret_cast<unsigned int*>(out_amax)); break;
+    case 2: launch_vpt<2>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale, reinterpret_cast<unsigned int*>(out_amax)); break;
+    case 4: launch_vpt<4>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale, reinterpret_cast<unsigned int*>(out_amax)); break;
+    default: launch_vpt<8>(q_format, grid, block, stream, xp, rp, wp, op, m, (int)d, eps, inv_d, qc, qs, qsw, q_global_scale, reinterpret_cast<unsigned int*>(out_amax)); break;
   }
   TF_LAUNCH_CHECK();
   return TF_OK;

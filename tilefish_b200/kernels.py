@@ -30,7 +30,7 @@ def _pre(cond: bool, msg: str, kind: str, arg: Optional[str] = None) -> None:
         raise TilefishPreconditionError(msg, kind=kind, arg=arg)
 
 
-def _check(t, name: str, dtype, rank: Optional[int] = None, device=None) -> None:
+def _check(t, name: str, dtype, rank: Optional[int] = None, device=None, align: int = 16) -> None:
     torch = _torch()
     _pre(isinstance(t, torch.Tensor), f"{name}: expected a torch tensor, got {type(t).__name__}", "dtype", name)
     _pre(t.is_cuda, f"{name}: the tensor is on {t.device}; this backend runs on CUDA only (no CPU fallback)", "device", name)
@@ -39,7 +39,7 @@ def _check(t, name: str, dtype, rank: Optional[int] = None, device=None) -> None
         _pre(t.dim() == rank, f"{name}: expected rank {rank}, got {t.dim()}", "rank", name)
     if device is not None:
         _pre(t.device == device, f"{name}: on {t.device}, the other arguments are on {device}", "device", name)
-    _pre(t.numel() == 0 or t.data_ptr() % 16 == 0, f"{name}: the data pointer is not 16-byte aligned", "pointer_alignment", name)
+    _pre(t.numel() == 0 or t.data_ptr() % align == 0, f"{name}: the data pointer is not {align}-byte aligned", "pointer_alignment", name)
 
 
 def _dense(t, name: str) -> None:
@@ -112,8 +112,12 @@ def nvfp4_global_scale(x, *, out=None, stream=None):
     return out
 
 
-def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, stream=None) -> BlockScaledTensor:
-    """BlockScaled quantization of a bf16 [M, K] tensor along K. nvfp4 computes the global scale unless one is given."""
+def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, amax=None, stream=None) -> BlockScaledTensor:
+    """BlockScaled quantization of a bf16 [M, K] tensor along K.
+
+    nvfp4 needs the tensor's global scale: given as ``global_scale`` (float32 [1] on the device), derived inside the kernel
+    from ``amax`` (float32 [1] holding max|x|, e.g. the ``amax_out`` of the producing kernel), or computed by an extra pass.
+    """
     torch = _torch()
     _pre(fmt in FORMATS, f"unknown block-scaled format {fmt!r}", "dtype", "fmt")
     _pre(layout in ("swizzled", "plain"), f"unknown scale layout {layout!r}", "argument", "layout")
@@ -132,11 +136,17 @@ def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, stream
         if fmt == "nvfp4":
             gs = global_scale if global_scale is not None else torch.zeros(1, dtype=torch.float32, device=x.device)
         return BlockScaledTensor(fmt, (m, k), codes, scales, gs, layout)
-    if fmt == "nvfp4":
+    if fmt == "nvfp4" and amax is not None:
+        _check(amax, "amax", torch.float32, None, x.device, align=4)
+        _pre(amax.numel() == 1 and global_scale is None, "amax: expected one element and no global_scale", "shape", "amax")
+        gs = torch.empty(1, dtype=torch.float32, device=x.device)
+        N.check(lib.tf_quantize_nvfp4_from_amax(x.data_ptr(), m, k, ldx, codes.data_ptr(), scales.data_ptr(), lay, amax.data_ptr(), gs.data_ptr(), s),
+                "tf_quantize_nvfp4_from_amax")
+    elif fmt == "nvfp4":
         if global_scale is None:
             gs = nvfp4_global_scale(x, stream=stream)
         else:
-            _check(global_scale, "global_scale", torch.float32, None, x.device)
+            _check(global_scale, "global_scale", torch.float32, None, x.device, align=4)
             _pre(global_scale.numel() == 1, "global_scale: expected one element", "shape", "global_scale")
             gs = global_scale
         N.check(lib.tf_quantize_nvfp4(x.data_ptr(), m, k, ldx, codes.data_ptr(), scales.data_ptr(), lay, gs.data_ptr(), s), "tf_quantize_nvfp4")
@@ -168,10 +178,11 @@ def unswizzle_scales(swizzled, rows: int, cols: int, *, stream=None):
 
 
 def residual_add_rmsnorm(x, residual, w, eps: float = 1e-6, *, out=None, quantize_to: Optional[str] = None, want_bf16: bool = True,
-                         q_global_scale=None, stream=None):
+                         q_global_scale=None, amax_out=None, stream=None):
     """``residual += f32(x)`` in place; returns bf16 ``rmsnorm(residual) * w`` and/or its BlockScaled quantization.
 
     Returns ``out`` (bf16), or ``(out, q)`` when ``quantize_to`` is given (``out`` is None with ``want_bf16=False``).
+    ``amax_out`` (float32 [1], zeroed by the caller) receives max|out| through an atomic max.
     """
     torch = _torch()
     _check(x, "x", torch.bfloat16, 2)
@@ -204,16 +215,25 @@ def residual_add_rmsnorm(x, residual, w, eps: float = 1e-6, *, out=None, quantiz
         scales = torch.empty(N.scale_bytes(qfmt, m, d, N.SCALES_SWIZZLED), dtype=torch.uint8, device=x.device)
         if quantize_to == "nvfp4":
             _pre(q_global_scale is not None, "nvfp4 output needs q_global_scale (a float32 [1] device tensor)", "argument", "q_global_scale")
-            _check(q_global_scale, "q_global_scale", torch.float32, None, x.device)
+            _check(q_global_scale, "q_global_scale", torch.float32, None, x.device, align=4)
             qg = q_global_scale
         q = BlockScaledTensor(quantize_to, (m, d), codes, scales, qg, "swizzled")
         qc, qs = codes.data_ptr(), scales.data_ptr()
     N.check(
         N.load().tf_residual_add_rmsnorm(x.data_ptr(), residual.data_ptr(), w.data_ptr(), out.data_ptr() if out is not None else None, m, d,
-                                         float(eps), qfmt, qc, qs, N.SCALES_SWIZZLED, qg.data_ptr() if qg is not None else None, _stream(stream)),
+                                         float(eps), qfmt, qc, qs, N.SCALES_SWIZZLED, qg.data_ptr() if qg is not None else None,
+                                         _amax_ptr(amax_out, x.device), _stream(stream)),
         "tf_residual_add_rmsnorm",
     )
     return out if q is None else (out, q)
+
+
+def _amax_ptr(amax_out, device):
+    if amax_out is None:
+        return None
+    _check(amax_out, "amax_out", _torch().float32, None, device, align=4)
+    _pre(amax_out.numel() == 1, "amax_out: expected one element", "shape", "amax_out")
+    return amax_out.data_ptr()
 
 
 def silu_gate(t, *, out=None, stream=None):
@@ -239,7 +259,8 @@ def gemm_workspace_bytes(m: int, n: int, k: int, fmt: str, epilogue: str = "none
     return int(N.load().tf_gemm_workspace_bytes(m, n, k, FORMATS[fmt], EPILOGUES[epilogue]))
 
 
-def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, workspace=None, stream=None):
+def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, amax_out=None,
+                     workspace=None, stream=None):
     """bf16 [M, N] = deq(a)[M, K] @ deq(b)[N, K]^T on tcgen05 block-scaled MMA, f32 accumulate.
 
     ``epilogue="silu_gate"``: b has 2N rows (gate rows then up rows); the result is silu(gate) * up, [M, N].
@@ -286,17 +307,19 @@ def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: st
         N.load().tf_gemm_blockscaled(
             a.codes.data_ptr(), a.scales.data_ptr(), a.global_scale.data_ptr() if a.global_scale is not None else None,
             b.codes.data_ptr(), b.scales.data_ptr(), b.global_scale.data_ptr() if b.global_scale is not None else None,
-            out.data_ptr(), ldo, m, n, k, FORMATS[a.fmt], EPILOGUES[epilogue], res_ptr, ws_ptr, ws_bytes, _stream(stream)),
+            out.data_ptr(), ldo, m, n, k, FORMATS[a.fmt], EPILOGUES[epilogue], res_ptr, _amax_ptr(amax_out, a.device), ws_ptr, ws_bytes,
+            _stream(stream)),
         "tf_gemm_blockscaled",
     )
     return out
 
 
-def gemm(a, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, a_global_scale=None, stream=None):
+def gemm(a, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, a_global_scale=None, a_amax=None, amax_out=None,
+         stream=None):
     """The library ``gemm``: ``a`` is bf16 [M, K] (quantized on the fly in b's format) or already a BlockScaledTensor."""
     if not isinstance(a, BlockScaledTensor):
-        a = quantize(a, b.fmt, global_scale=a_global_scale, stream=stream)
-    return gemm_blockscaled(a, b, epilogue=epilogue, out=out, residual=residual, stream=stream)
+        a = quantize(a, b.fmt, global_scale=a_global_scale, amax=a_amax, stream=stream)
+    return gemm_blockscaled(a, b, epilogue=epilogue, out=out, residual=residual, amax_out=amax_out, stream=stream)
 
 
 def require_cuda() -> None:

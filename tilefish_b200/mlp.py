@@ -1,0 +1,122 @@
+"""The decoder-block path built from the kernels: residual_add_rmsnorm -> gemm(x, w_gu) -> SiLU gate -> gemm(a, w_d).
+
+This is what the README ``mlp`` graph of the reference (README.md:81-85, preceded by ``residual_add_rmsnorm`` :53-63)
+executes on this backend, single-GPU or tensor-parallel:
+
+* activations are quantized in the weights' format at both GEMMs (the library ``gemm`` takes a bf16 ``a``);
+* the split / SiLU gate / multiply of the graph body runs as the first GEMM's epilogue (gate and up column tiles are
+  accumulated side by side in tensor memory), so the [M, 2F] intermediate never reaches HBM;
+* mxfp8 / mxfp4: the rmsnorm kernel emits the quantized activation directly; nvfp4: the producing kernels also reduce
+  max|out| (an atomic max), from which the quantizer derives the tensor's global scale in stream order: no host sync;
+* tensor parallel: ``w_gu`` is split by columns of the output (gate rows and the matching up rows per rank), ``w_d`` by K;
+  one bf16 all-reduce (NCCL, through torch.distributed) per layer sums the partial results of the second GEMM.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+from . import kernels as K
+from .errors import TilefishPreconditionError
+
+
+@dataclass
+class MlpWeights:
+    """One decoder block's weights on one device. ``w_gu``: [2F_local, H] (gate rows then up rows); ``w_d``: [H, F_local]."""
+
+    w_n: "object"  # bf16 [H]
+    w_gu: K.BlockScaledTensor
+    w_d: K.BlockScaledTensor
+
+    @property
+    def fmt(self) -> str:
+        return self.w_gu.fmt
+
+    def nbytes(self) -> int:
+        return self.w_gu.nbytes() + self.w_d.nbytes() + self.w_n.numel() * 2
+
+
+def quantize_weights(w_n, w_gu, w_d, fmt: str, *, rank: int = 0, world: int = 1) -> MlpWeights:
+    """Quantizes the FULL bf16 weights once, then keeps this rank's shard, so that shards hold exactly the bytes of the
+    single-GPU weights (codes, scale bytes and the nvfp4 global scales of the full tensors).
+
+    w_gu bf16 [2F, H], w_d bf16 [H, F] on the device. rank r keeps gate rows [rF/n, (r+1)F/n) and the matching up rows of
+    w_gu, and columns [rF/n, (r+1)F/n) of w_d; scales are re-swizzled per shard.
+    """
+    import torch
+
+    two_f, h = w_gu.shape
+    f = two_f // 2
+    if tuple(w_d.shape) != (h, f):
+        raise TilefishPreconditionError(f"w_d: shape {tuple(w_d.shape)}, expected {(h, f)}", kind="shape", arg="w_d")
+    if world == 1:
+        return MlpWeights(w_n, K.quantize(w_gu, fmt), K.quantize(w_d, fmt))
+    if f % world or (f // world) % 128:
+        raise TilefishPreconditionError(f"F={f} cannot be split over {world} ranks in multiples of 128", kind="divisible", arg="w_gu")
+    fl = f // world
+    blk = K.BLOCK[fmt]
+    epb = K.ELEMS_PER_BYTE[fmt]
+    q_gu = K.quantize(w_gu, fmt, layout="plain")
+    rows = torch.cat([torch.arange(rank * fl, (rank + 1) * fl), torch.arange(f + rank * fl, f + (rank + 1) * fl)]).to(w_gu.device)
+    gu = K.BlockScaledTensor(fmt, (2 * fl, h), q_gu.codes[rows].contiguous(), K.swizzle_scales(q_gu.plain_scales()[rows].contiguous()),
+                             q_gu.global_scale, "swizzled")
+    del q_gu
+    q_d = K.quantize(w_d, fmt, layout="plain")
+    c0, c1 = rank * fl, (rank + 1) * fl
+    d = K.BlockScaledTensor(fmt, (h, fl), q_d.codes[:, c0 // epb:c1 // epb].contiguous(),
+                            K.swizzle_scales(q_d.plain_scales()[:, c0 // blk:c1 // blk].contiguous()), q_d.global_scale, "swizzled")
+    return MlpWeights(w_n, gu, d)
+
+
+def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, scratch: Optional[dict] = None, out=None):
+    """One block: ``residual += x`` (f32, in place), returns bf16 [M, H] = mlp(rmsnorm(residual) * w_n).
+
+    ``group``: a torch.distributed process group for the tensor-parallel all-reduce (None = single GPU).
+    ``scratch``: a dict reused between calls for the two-float amax buffer (nvfp4).
+    """
+    import torch
+
+    fmt = w.fmt
+    if fmt == "nvfp4":
+        if scratch is None:
+            scratch = {}
+        amax = scratch.get("amax")
+        if amax is None or amax.device != x.device:
+            amax = scratch["amax"] = torch.zeros(2, dtype=torch.float32, device=x.device)
+        amax.zero_()
+        h = K.residual_add_rmsnorm(x, residual, w.w_n, eps, amax_out=amax[0:1])
+        hq = K.quantize(h, fmt, amax=amax[0:1])
+        a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", amax_out=amax[1:2])
+        aq = K.quantize(a, fmt, amax=amax[1:2])
+    else:
+        _, hq = K.residual_add_rmsnorm(x, residual, w.w_n, eps, quantize_to=fmt, want_bf16=False)
+        a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate")
+        aq = K.quantize(a, fmt)
+    y = K.gemm_blockscaled(aq, w.w_d, out=out)
+    if group is not None:
+        import torch.distributed as dist
+
+        dist.all_reduce(y, group=group)
+    return y
+
+
+class MlpStack:
+    """``layers`` decoder blocks applied in sequence: the output of block l is the ``x`` of block l + 1, the f32 residual
+    stream is carried in place."""
+
+    def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None) -> None:
+        self.layers = layers
+        self.eps = eps
+        self.group = group
+        self._scratch: dict = {}
+
+    def forward(self, x, residual):
+        for w in self.layers:
+            x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch)
+        return x
+
+    __call__ = forward
+
+    def weight_bytes(self) -> int:
+        return sum(w.nbytes() for w in self.layers)
