@@ -108,10 +108,12 @@ TF_API tf_status tf_residual_add_rmsnorm(const void* x, void* residual, const vo
                                   int32_t q_format, void* q_codes, void* q_scales, int32_t q_layout, const float* q_global_scale,
                                   float* out_amax, void* stream);
 
-/* SiLU gate over the column halves of t (README.md:83-84; the fused region of python/src/tilefish/_fusion.py):
- *   out[m, f] = bf16( silu(f32(t[m, j])) * f32(t[m, f + j]) ), silu(x) = x * (1 / (1 + exp(-x))).
- *   t bf16 [m, 2f] with row stride ldt; out bf16 [m, f] with row stride ldo; f, ldt, ldo multiples of 8. */
-TF_API tf_status tf_silu_gate(const void* t, int64_t m, int64_t f, int64_t ldt, void* out, int64_t ldo, void* stream);
+/* SiLU gate (README.md:83-84; the fused region of python/src/tilefish/_fusion.py):
+ *   out[m, j] = bf16( silu(f32(gate[m, j])) * f32(up[m, j]) ), silu(x) = x * (1 / (1 + exp(-x))).
+ *   gate, up bf16 [m, f] with row strides ldg, ldu (the column halves of a [m, 2f] tensor t are gate = t, up = t + f,
+ *   ldg = ldu = 2f); out bf16 [m, f] with row stride ldo; f and the strides are multiples of 8. */
+TF_API tf_status tf_silu_gate(const void* gate, const void* up, int64_t m, int64_t f, int64_t ldg, int64_t ldu, void* out, int64_t ldo,
+                       void* stream);
 
 /* Block-scaled GEMM on tcgen05 tensor cores: out[M,N] = bf16( sum_k deq(a)[m,k] * deq(b)[n,k] ), f32 accumulate.
  * Replaces the pinned cublasLtMatmul of `@tilefish.library("gemm", acc=f32)` (python/src/tilefish/_library.py:9-16) for

@@ -1,0 +1,138 @@
+"""tilefish.run / runtime.export / replay / capture of the typed decoder-block graph on a GPU, against the CPU oracle.
+
+The graph is the README's (python/tests/test_graphs.py:27-49 of the reference) with BlockScaled weights, preceded by
+residual_add_rmsnorm: what the fourth benchmark configuration runs (H = 2560, F = 3072, MXFP8).
+"""
+
+import pytest
+import torch
+
+import tilefish_b200 as tilefish
+from oracle import blockscaled as O
+from tilefish_b200 import Dim, InOut, Tensor, bf16, const, f32, mxfp8, nvfp4
+
+pytestmark = pytest.mark.gpu
+
+M = Dim("M", buckets=[1, 32, 512])
+H = Dim("H", 2560)
+F = Dim("F", 3072)
+
+
+def declare(fmt):
+    @tilefish.kernel
+    def residual_add_rmsnorm(x: Tensor[M, H, bf16], residual: InOut[Tensor[M, H, f32]], w: Tensor[H, bf16], *, eps: const[f32] = 1e-6) -> Tensor[M, H, bf16]:
+        r = residual + x.to(f32)
+        residual[...] = r
+        rstd = tilefish.rsqrt(tilefish.mean(r * r, axis=-1, keepdims=True) + eps)
+        return (r * rstd * w.to(f32)).to(bf16)
+
+    @tilefish.library("gemm_gu", acc=f32)
+    def gemm_gu(a: Tensor[M, H, bf16], b: Tensor[2 * F, H, fmt]) -> Tensor[M, 2 * F, bf16]: ...
+
+    @tilefish.library("gemm_d", acc=f32)
+    def gemm_d(a: Tensor[M, F, bf16], b: Tensor[H, F, fmt]) -> Tensor[M, H, bf16]: ...
+
+    @tilefish.graph(inputs=("x",), weights=("w_n", "w_gu", "w_d"))
+    def block(x: Tensor[M, H, bf16], residual: InOut[Tensor[M, H, f32]], w_n: Tensor[H, bf16], w_gu: Tensor[2 * F, H, fmt], w_d: Tensor[H, F, fmt]):
+        h = residual_add_rmsnorm(x, residual, w_n)
+        g, u = gemm_gu(h, w_gu).split(F, axis=-1)
+        return gemm_d((tilefish.silu(g.to(f32)) * u.to(f32)).to(bf16), w_d)
+
+    return residual_add_rmsnorm, gemm_gu, block
+
+
+def inputs(m, seed=0):
+    x = O.randn((m, 2560), seed, torch.bfloat16)
+    res = O.randn((m, 2560), seed + 1)
+    w_n = (1 + 0.1 * O.randn((2560,), seed + 2)).to(torch.bfloat16)
+    w_gu = O.randn((6144, 2560), seed + 3, torch.bfloat16, scale=2560**-0.5)
+    w_d = O.randn((2560, 3072), seed + 4, torch.bfloat16, scale=3072**-0.5)
+    return x, res, w_n, w_gu, w_d
+
+
+def check_block(y, res_gpu, x, res, w_n, w_gu, w_d, fmt_name):
+    r_ref, y_ref = O.decoder_block(x, res.clone(), w_n, O.quantize(w_gu, fmt_name), O.quantize(w_d, fmt_name), fmt_name)
+    assert torch.equal(res_gpu.cpu(), r_ref)
+    g, r = y.cpu().float(), y_ref.float()
+    assert float((g - r).abs().max()) <= 2.0**-6 * float(r.abs().max())
+    assert float((g - r).norm() / r.norm()) <= 1e-2
+
+
+@pytest.mark.parametrize("fmt", [mxfp8, nvfp4], ids=["mxfp8", "nvfp4"])
+@pytest.mark.parametrize("m", [1, 32, 512])
+def test_run_graph_jit(fmt, m):
+    _, _, block = declare(fmt)
+    x, res, w_n, w_gu, w_d = inputs(m)
+    name = fmt.format_name
+    q_gu, q_d = tilefish.quantize(w_gu.cuda(), name), tilefish.quantize(w_d.cuda(), name)
+    res_gpu = res.cuda()
+    y = tilefish.run(block, x.cuda(), res_gpu, w_n.cuda(), q_gu, q_d)
+    assert y.shape == (m, 2560) and y.dtype == torch.bfloat16
+    check_block(y, res_gpu, x, res, w_n, w_gu, w_d, name)
+
+
+def test_run_single_operators():
+    rms, gemm_gu, _ = declare(mxfp8)
+    x, res, w_n, w_gu, _ = inputs(32)
+    res_gpu = res.cuda()
+    h = rms(x.cuda(), res_gpu, w_n.cuda())  # calling a declaration with tensors runs it
+    r_ref, h_ref = O.residual_add_rmsnorm(x, res, w_n)
+    assert torch.equal(res_gpu.cpu(), r_ref)
+    assert float((h.cpu().float() - h_ref.float()).abs().max()) <= 2.0**-7 * float(h_ref.float().abs().max())
+    t = tilefish.run(gemm_gu, h, tilefish.quantize(w_gu.cuda(), "mxfp8"))
+    ref = O.gemm_bf16_a(h.cpu(), O.quantize(w_gu, "mxfp8"), "mxfp8")
+    assert float((t.cpu().float() - ref.float()).abs().max()) <= 2.0**-8 * 1.01 * float(ref.float().abs().max())
+
+
+def test_preconditions_are_checked_before_any_launch():
+    from tilefish_b200 import TilefishPreconditionError
+
+    _, _, block = declare(mxfp8)
+    x, res, w_n, w_gu, w_d = inputs(32)
+    q_gu, q_d = tilefish.quantize(w_gu.cuda(), "mxfp8"), tilefish.quantize(w_d.cuda(), "mxfp8")
+    res_gpu = res.cuda()
+    before = res_gpu.clone()
+    cases = [
+        ((x.cuda().float(), res_gpu, w_n.cuda(), q_gu, q_d), "dtype"),
+        ((x.cuda()[:, :2048].contiguous(), res_gpu, w_n.cuda(), q_gu, q_d), "static_size"),
+        ((x.cuda(), res_gpu[:16], w_n.cuda(), q_gu, q_d), "shape"),
+        ((x.cuda(), res_gpu, w_n.cuda(), tilefish.quantize(w_gu.cuda(), "mxfp4"), q_d), "dtype"),
+        ((x.cuda(), res_gpu, w_n.cuda(), w_gu.cuda(), q_d), "dtype"),
+        ((x, res_gpu, w_n.cuda(), q_gu, q_d), "device"),
+    ]
+    for args, kind in cases:
+        with pytest.raises(TilefishPreconditionError) as e:
+            tilefish.run(block, *args)
+        assert e.value.kind == kind, (kind, str(e.value))
+    assert torch.equal(res_gpu, before), "a refused call must not have launched anything"
+
+
+def test_export_replay_and_capture(tmp_path):
+    from tilefish_b200 import TilefishManifestError, TilefishPreconditionError, runtime
+
+    _, _, block = declare(mxfp8)
+    exp = runtime.export(block, str(tmp_path / "mlp"))
+    assert len(exp.digest) == 64 and (tmp_path / "mlp" / "plan.json").exists() and (tmp_path / "mlp" / "manifest.json").exists()
+    x, res, w_n, w_gu, w_d = inputs(32, seed=7)
+    q_gu, q_d = tilefish.quantize(w_gu.cuda(), "mxfp8"), tilefish.quantize(w_d.cuda(), "mxfp8")
+    res_a, res_b = res.cuda(), res.cuda()
+    y_jit = tilefish.run(block, x.cuda(), res_a, w_n.cuda(), q_gu, q_d)
+    y_rep = tilefish.run(block, x.cuda(), res_b, w_n.cuda(), q_gu, q_d, mode="replay", plan=exp.directory, pin=exp.digest)
+    assert torch.equal(y_jit, y_rep) and torch.equal(res_a, res_b), "replay and jit run the same kernels: identical bytes"
+    check_block(y_rep, res_b, x, res, w_n, w_gu, w_d, "mxfp8")
+    with pytest.raises(TilefishManifestError):
+        tilefish.run(block, x.cuda(), res_b, w_n.cuda(), q_gu, q_d, mode="replay", plan=exp.directory, pin="0" * 64)
+    x7 = O.randn((7, 2560), 1, torch.bfloat16).cuda()
+    with pytest.raises(TilefishPreconditionError) as e:
+        tilefish.run(block, x7, torch.zeros((7, 2560), device="cuda"), w_n.cuda(), q_gu, q_d, mode="replay", plan=exp.directory, pin=exp.digest)
+    assert e.value.kind == "bucket"
+
+    # capture: one CUDA graph launch per step; new inputs are written into the captured tensors
+    xg, rg = x.cuda(), res.cuda()
+    cap = tilefish.capture(block, xg, rg, w_n.cuda(), q_gu, q_d, plan=exp.directory, pin=exp.digest)
+    x2, res2 = O.randn((32, 2560), 11, torch.bfloat16), O.randn((32, 2560), 12)
+    xg.copy_(x2.cuda())
+    rg.copy_(res2.cuda())
+    y = cap.replay()
+    torch.cuda.synchronize()
+    check_block(y, rg, x2, res2, w_n, w_gu, w_d, "mxfp8")

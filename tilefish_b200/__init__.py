@@ -19,4 +19,24 @@ from .errors import (  # noqa: F401
     TilefishTypeError,
 )
 
+from .decorators import GraphOp, KernelOp, LibraryOp, Op, graph, kernel, library  # noqa: F401,E402
+from .dims import Dim, DimExpr, cdiv  # noqa: F401,E402
+from .dtypes import BlockScaled, DType, bf16, bool_, e2m1, e4m3, e5m2, f16, f32, i32, i64, u8, ue8m0  # noqa: F401,E402
+from .ir import Graph, Node, Scalar, Value  # noqa: F401,E402
+from .trace import exp, max, mean, rsqrt, silu, sum  # noqa: F401,E402,A004
+from .types import ConstType, InOut, Marked, Out, Tensor, TensorType, const  # noqa: F401,E402
+
+mxfp8 = BlockScaled(elem=e4m3, scale=ue8m0, block=32, axis=-1)
+mxfp4 = BlockScaled(elem=e2m1, scale=ue8m0, block=32, axis=-1)
+nvfp4 = BlockScaled(elem=e2m1, scale=e4m3, block=16, global_scale=f32)
+
 __version__ = "0.1.0"
+
+
+def __getattr__(name):  # the run-time half imports torch lazily
+    if name in ("run", "plan", "capture", "runtime", "quantize", "BlockScaledTensor"):
+        import importlib
+
+        rt = importlib.import_module(".runtime", __name__)
+        return rt if name == "runtime" else getattr(rt, name)
+    raise AttributeError(f"module {__name__!r} has no attribute {name!r}")

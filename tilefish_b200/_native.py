@@ -44,7 +44,7 @@ SIGNATURES = {
     "tf_swizzle_scales": (c_int32, [_P, c_int64, c_int64, _P, _P]),
     "tf_unswizzle_scales": (c_int32, [_P, c_int64, c_int64, _P, _P]),
     "tf_residual_add_rmsnorm": (c_int32, [_P, _P, _P, _P, c_int64, c_int64, c_float, c_int32, _P, _P, c_int32, _P, _P, _P]),
-    "tf_silu_gate": (c_int32, [_P, c_int64, c_int64, c_int64, _P, c_int64, _P]),
+    "tf_silu_gate": (c_int32, [_P, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int64, _P]),
     "tf_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int32, c_int32]),
     "tf_gemm_blockscaled": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, _P, c_int64, _P]),
 }

@@ -1,4 +1,5 @@
-// SiLU gate over the column halves of a [M, 2F] bf16 matrix (the stand-alone form; the GEMM also has it as an epilogue).
+// SiLU gate of two bf16 [M, F] operands, e.g. the column halves of a [M, 2F] matrix (the stand-alone form; the GEMM also has
+// it as an epilogue).
 //   out[m, j] = bf16( silu(f32(t[m, j])) * f32(t[m, F + j]) ),  silu(x) = x * (1 / (1 + exp(-x)))
 // HBM-bound elementwise kernel: 6 bytes per output element, 128-bit loads and stores.
 #include "common.cuh"
@@ -10,8 +11,8 @@ __device__ __forceinline__ float silu_gate1(float g, float u) {
   return __fmul_rn(s, u);
 }
 
-__global__ void __launch_bounds__(256) silu_gate_kernel(const uint4* __restrict__ t, int64_t m, int fvec, int64_t ldt_vec, uint4* __restrict__ out,
-                                                        int64_t ldo_vec) {
+__global__ void __launch_bounds__(256) silu_gate_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, int64_t m, int fvec,
+                                                        int64_t ldg_vec, int64_t ldu_vec, uint4* __restrict__ out, int64_t ldo_vec) {
   const int64_t total = m * fvec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 2 * stride) {  // two vector pairs in flight
@@ -24,8 +25,8 @@ __global__ void __launch_bounds__(256) silu_gate_kernel(const uint4* __restrict_
       if (i < total) {
         const int64_t row = i / fvec;
         const int v = (int)(i - row * fvec);
-        g[j] = __ldcs(t + row * ldt_vec + v);
-        u[j] = __ldcs(t + row * ldt_vec + fvec + v);
+        g[j] = __ldcs(gate + row * ldg_vec + v);
+        u[j] = __ldcs(up + row * ldu_vec + v);
         oidx[j] = row * ldo_vec + v;
       }
     }
@@ -46,19 +47,21 @@ __global__ void __launch_bounds__(256) silu_gate_kernel(const uint4* __restrict_
 
 using namespace tf;
 
-extern "C" tf_status tf_silu_gate(const void* t, int64_t m, int64_t f, int64_t ldt, void* out, int64_t ldo, void* stream) {
+extern "C" tf_status tf_silu_gate(const void* gate, const void* up, int64_t m, int64_t f, int64_t ldg, int64_t ldu, void* out, int64_t ldo,
+                                  void* stream) {
   clear_error();
-  TF_CHECK_ARG(t && out, "%s: null pointer", __func__);
+  TF_CHECK_ARG(gate && up && out, "%s: null pointer", __func__);
   TF_CHECK_ARG(m >= 0 && f > 0, "%s: bad shape m=%lld f=%lld", __func__, (long long)m, (long long)f);
-  if (f % 8 || ldt % 8 || ldo % 8 || ldt < 2 * f || ldo < f)
-    return fail(TF_ERR_ALIGNMENT, "%s: f, ldt, ldo must be multiples of 8 with ldt >= 2f, ldo >= f", __func__);
-  TF_CHECK_ALIGNED(t, 16, "t");
+  if (f % 8 || ldg % 8 || ldu % 8 || ldo % 8 || ldg < f || ldu < f || ldo < f)
+    return fail(TF_ERR_ALIGNMENT, "%s: f and the row strides must be multiples of 8, strides >= f", __func__);
+  TF_CHECK_ALIGNED(gate, 16, "gate");
+  TF_CHECK_ALIGNED(up, 16, "up");
   TF_CHECK_ALIGNED(out, 16, "out");
   if (m == 0) return TF_OK;
   const int64_t total = m * (f >> 3);
-  const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
-  silu_gate_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4*>(t), m, (int)(f >> 3),
-                                                                                          ldt >> 3, static_cast<uint4*>(out), ldo >> 3);
+  const int64_t need = (total + 511) / 512, cap = (int64_t)sm_count() * 8;
+  silu_gate_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, (cudaStream_t)stream>>>(
+      static_cast<const uint4*>(gate), static_cast<const uint4*>(up), m, (int)(f >> 3), ldg >> 3, ldu >> 3, static_cast<uint4*>(out), ldo >> 3);
   TF_LAUNCH_CHECK();
   return TF_OK;
 }

@@ -1,0 +1,337 @@
+"""Declarations: ``@kernel`` (a traced body matched to a hand-written kernel), ``@library`` (an opaque typed operator: the
+block-scaled gemm) and ``@graph`` (a model step over them).
+
+Argument meaning, the objects returned (``KernelOp`` / ``LibraryOp`` / ``GraphOp`` with ``.name .signature .graph``) and the
+call type-checking follow the reference (python/src/tilefish/decorators.py:184-193, :241-390, :396-741;
+python/src/tilefish/signature.py:234, :797-1010): rank, dtype (BlockScaled formats must match exactly), contiguity and
+dimensions are unified at every call, an ``InOut`` argument is consumed by the call. Annotations are evaluated at
+declaration (no ``from __future__ import annotations`` in the declaring module).
+"""
+
+from __future__ import annotations
+
+import inspect
+from typing import Any, Dict, List, Optional, Tuple
+
+from . import trace as T
+from .dims import Dim, as_expr, divisible, simplify, symbols
+from .dtypes import DType, same_format
+from .errors import TilefishDeclarationError, TilefishTypeError
+from .ir import Graph, Scalar, Value
+from .types import ConstType, Marked, TensorType
+
+
+class Param:
+    __slots__ = ("name", "type", "access", "is_const", "const_dtype", "default")
+
+    def __init__(self, name, type_=None, access="in", is_const=False, const_dtype=None, default=None):
+        self.name, self.type, self.access = name, type_, access
+        self.is_const, self.const_dtype, self.default = is_const, const_dtype, default
+
+    def __repr__(self) -> str:
+        if self.is_const:
+            return f"{self.name}: const[{self.const_dtype}] = {self.default!r}"
+        t = repr(self.type)
+        if self.access == "inout":
+            t = f"InOut[{t}]"
+        elif self.access == "out":
+            t = f"Out[{t}]"
+        return f"{self.name}: {t}"
+
+
+class Signature:
+    def __init__(self, params: List[Param], returns: Tuple[TensorType, ...]) -> None:
+        self.params = tuple(params)
+        self.returns = tuple(returns)
+
+    @property
+    def tensors(self) -> Tuple[Param, ...]:
+        return tuple(p for p in self.params if not p.is_const)
+
+    @property
+    def consts(self) -> Tuple[Param, ...]:
+        return tuple(p for p in self.params if p.is_const)
+
+    def __repr__(self) -> str:
+        rets = ", ".join(repr(r) for r in self.returns)
+        if len(self.returns) != 1:
+            rets = f"({rets})"
+        return f"({', '.join(repr(p) for p in self.params)}) -> {rets}"
+
+
+def parse_signature(fn, what: str) -> Signature:
+    sig = inspect.signature(fn)
+    params = []
+    for name, p in sig.parameters.items():
+        ann = p.annotation
+        if isinstance(ann, str):
+            raise TilefishDeclarationError(f"{what} '{fn.__name__}': annotations must be evaluated at declaration; remove "
+                                           "`from __future__ import annotations` from the declaring module")
+        if isinstance(ann, TensorType):
+            params.append(Param(name, ann, "in"))
+        elif isinstance(ann, Marked):
+            params.append(Param(name, ann.type, ann.mode))
+        elif isinstance(ann, ConstType):
+            if p.kind is not inspect.Parameter.KEYWORD_ONLY or p.default is inspect.Parameter.empty:
+                raise TilefishDeclarationError(f"{what} '{fn.__name__}': const parameter '{name}' must be keyword-only with a default")
+            if ann.dtype is None:
+                raise TilefishDeclarationError(f"{what} '{fn.__name__}': const parameter '{name}' needs a dtype (const[f32])")
+            params.append(Param(name, None, "in", True, ann.dtype, p.default))
+        else:
+            raise TilefishDeclarationError(f"{what} '{fn.__name__}': parameter '{name}' needs a Tensor[...], InOut[...], Out[...] or const[...] annotation")
+    ret = sig.return_annotation
+    if ret is inspect.Signature.empty or ret is None:
+        returns: Tuple[TensorType, ...] = ()
+    elif isinstance(ret, TensorType):
+        returns = (ret,)
+    elif isinstance(ret, tuple) and all(isinstance(r, TensorType) for r in ret):
+        returns = tuple(ret)
+    else:
+        raise TilefishDeclarationError(f"{what} '{fn.__name__}': the return annotation must be a tensor type or a tuple of them")
+    return Signature(params, returns)
+
+
+# ---- call type-checking: unify the callee's dimensions with the arguments' -------------------------------------------
+def _unify(callee: str, pname: str, formal, actual, env: Dict[Dim, Any]) -> None:
+    f = as_expr(formal)
+    if f.is_static:
+        if as_expr(actual) != f:
+            raise TilefishTypeError(f"{callee}: argument '{pname}' has size {actual} where {formal} is required")
+        return
+    if f.const == 0 and len(f.terms) == 1 and isinstance(f.terms[0][0], Dim):
+        d, coef = f.terms[0]
+        a = as_expr(actual)
+        if coef != 1:
+            if not (a.const % coef == 0 and all(c % coef == 0 for _, c in a.terms)):
+                raise TilefishTypeError(f"{callee}: argument '{pname}' has size {actual}, not of the form {formal}")
+            from .dims import DimExpr
+
+            a = DimExpr({k: c // coef for k, c in a.terms}, a.const // coef)
+        if d in env:
+            if as_expr(env[d]) != a:
+                raise TilefishTypeError(f"{callee}: dimension {d} is {env[d]} for an earlier argument but {simplify(a)} for '{pname}'")
+        else:
+            if d.divisible_by and not divisible(a, d.divisible_by):
+                raise TilefishTypeError(f"{callee}: argument '{pname}' binds {d} to {simplify(a)}, which is not provably divisible by {d.divisible_by}")
+            env[d] = actual if coef == 1 else simplify(a)
+        return
+    if as_expr(actual) != f:
+        raise TilefishTypeError(f"{callee}: argument '{pname}' has size {actual} where {formal} is required")
+
+
+def _substitute(x, env: Dict[Dim, Any]):
+    if isinstance(x, Dim):
+        return env.get(x, x) if not x.is_static else x
+    e = as_expr(x)
+    total = as_expr(e.const)
+    for a, c in e.terms:
+        if isinstance(a, Dim) and a in env:
+            total = total + as_expr(env[a]) * c
+        else:
+            from .dims import DimExpr
+
+            total = total + DimExpr({a: c}, 0)
+    return simplify(total)
+
+
+def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple[List[Value], Dict[Dim, Any], Tuple[TensorType, ...]]:
+    sig = op.signature
+    tensors = sig.tensors
+    if len(args) > len(tensors):
+        raise TilefishTypeError(f"{op.name}: takes {len(tensors)} tensor arguments, {len(args)} were given")
+    bound: Dict[str, Any] = {p.name: a for p, a in zip(tensors, args)}
+    for k, v in kwargs.items():
+        if k in bound:
+            raise TilefishTypeError(f"{op.name}: argument '{k}' given twice")
+        bound[k] = v
+    env: Dict[Dim, Any] = {}
+    values = []
+    for p in tensors:
+        if p.access == "out" and p.name not in bound:
+            continue
+        if p.name not in bound:
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is missing")
+        v = bound[p.name]
+        if not isinstance(v, Value):
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' must be a traced tensor value, got {type(v).__name__}")
+        if v.consumed:
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' ({v.ref}) was consumed by an earlier in-place call and cannot be read again")
+        if v.type.rank != p.type.rank:
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' has rank {v.type.rank}, expected {p.type.rank} ({p.type!r})")
+        if not same_format(v.type.dtype, p.type.dtype, p.type.rank):
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is {v.type.dtype}, expected {p.type.dtype}")
+        if p.type.contiguous and not v.type.contiguous:
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is a strided view ({v.type!r}); the operator takes a contiguous tensor")
+        for formal, actual in zip(p.type.shape, v.type.shape):
+            _unify(op.name, p.name, formal, actual, env)
+        values.append(v)
+    for p in sig.consts:
+        if p.name in bound and bound[p.name] != p.default:
+            raise TilefishTypeError(f"{op.name}: const '{p.name}' is compiled in as {p.default!r}; a call may restate, not change, it")
+    written = [v for p, v in zip(tensors, values) if p.access != "in"]
+    if len({id(v) for v in written}) != len(written) or any(sum(1 for u in values if u is w) > 1 for w in written):
+        raise TilefishTypeError(f"{op.name}: a written argument is passed more than once (aliasing)")
+    rets = tuple(TensorType(tuple(_substitute(s, env) for s in r.shape), r.dtype, r.contiguous) for r in sig.returns)
+    return values, env, rets
+
+
+class Op:
+    kind = "op"
+
+    def __init__(self, fn, name: Optional[str], signature: Signature) -> None:
+        self.fn = fn
+        self.name = name or fn.__name__
+        self.signature = signature
+        self.__doc__ = fn.__doc__
+        self.__name__ = fn.__name__
+
+    def __call__(self, *args, **kwargs):
+        ctx = T.active()
+        if ctx is None or not any(isinstance(a, Value) for a in list(args) + list(kwargs.values())):
+            from . import runtime
+
+            return runtime.run(self, *args, **kwargs)
+        if ctx.kind != "graph":
+            raise TilefishTypeError(f"{self.name}: operators can only be called from a @graph body, not from the kernel '{ctx.name}'")
+        values, _, rets = check_call(self, args, kwargs)
+        attrs = self._call_attrs()
+        outs = ctx.emit(self.name, values, rets, attrs)
+        ctx.nodes[-1].callee = self
+        for p, v in zip(self.signature.tensors, values):
+            if p.access == "inout":
+                v.consumed = False  # the updated tensor is read back through the same name by later calls of the graph
+        if not outs:
+            return None
+        return outs[0] if len(outs) == 1 else outs
+
+    def _call_attrs(self) -> Dict[str, Any]:
+        return {"kind": self.kind}
+
+    def __repr__(self) -> str:
+        return f"<{type(self).__name__} {self.name}{self.signature!r}>"
+
+
+class LibraryOp(Op):
+    """A typed operator with an opaque body. ``acc`` is the accumulator dtype; ``impl`` names the implementation, and is
+    filled in with this backend's ("sm100.gemm_blockscaled") when the operands are block-scaled."""
+
+    kind = "library"
+
+    def __init__(self, fn, name, signature, acc: Optional[DType], impl: Optional[str]) -> None:
+        super().__init__(fn, name, signature)
+        self.acc = acc
+        self.impl = impl
+
+    def _call_attrs(self):
+        return {"kind": "library", "acc": self.acc}
+
+
+class KernelOp(Op):
+    kind = "kernel"
+
+    def __init__(self, fn, name, signature, graph: Graph, **options) -> None:
+        super().__init__(fn, name, signature)
+        self.graph = graph
+        self.options = options
+
+
+class GraphOp(Op):
+    kind = "graph"
+
+    def __init__(self, fn, name, signature, graph: Graph, param_roles: Dict[str, str]) -> None:
+        super().__init__(fn, name, signature)
+        self.graph = graph
+        self.param_roles = param_roles
+
+    @property
+    def output_names(self) -> Tuple[str, ...]:
+        return tuple(f"out{i}" for i in range(len(self.graph.outputs)))
+
+
+def _trace(fn, kind: str, name: str, sig: Signature) -> Tuple[Graph, Tuple[TensorType, ...]]:
+    with T.TraceContext(kind, name) as ctx:
+        inputs = []
+        call_args = []
+        kw = {}
+        for p in sig.params:
+            if p.is_const:
+                kw[p.name] = Scalar(p.default, p.const_dtype, p.name)
+                continue
+            v = Value(p.type, f"%{p.name}", ctx, is_param=True, access=p.access, name=p.name)
+            inputs.append(v)
+            call_args.append(v)
+        result = fn(*call_args, **kw)
+        if result is None:
+            outs: List[Value] = []
+        elif isinstance(result, Value):
+            outs = [result]
+        elif isinstance(result, (tuple, list)) and all(isinstance(r, Value) for r in result):
+            outs = list(result)
+        else:
+            raise TilefishDeclarationError(f"{kind} '{name}': the body must return traced tensor values, got {type(result).__name__}")
+        for p, v in zip(sig.tensors, inputs):
+            if p.access == "out" and p.name not in ctx.finals:
+                raise TilefishDeclarationError(f"{kind} '{name}': Out parameter '{p.name}' is never written")
+            if p.access == "inout" and kind == "kernel" and p.name not in ctx.finals:
+                raise TilefishDeclarationError(f"{kind} '{name}': InOut parameter '{p.name}' is never written")
+        for o in outs:
+            if o.is_param:
+                raise TilefishDeclarationError(f"{kind} '{name}': a parameter cannot be returned as is")
+        if sig.returns:
+            if len(sig.returns) != len(outs) or any(a != o.type for a, o in zip(sig.returns, outs)):
+                raise TilefishTypeError(f"{kind} '{name}': the body returns ({', '.join(repr(o.type) for o in outs)}) "
+                                        f"but the annotation says ({', '.join(repr(r) for r in sig.returns)})")
+        consts = [(p.name, p.const_dtype, p.default) for p in sig.consts]
+        graph = Graph(kind, name, inputs, consts, ctx.nodes, outs, ctx.finals)
+    return graph, tuple(o.type for o in outs)
+
+
+def kernel(fn=None, *, name: Optional[str] = None, num_warps: Optional[int] = None, fp_fusion: bool = True, math: str = "fast", **ignored):
+    """``@tilefish.kernel``: traces the body. The body must match one of the hand-written sm_100a kernels when it is run."""
+
+    def wrap(f):
+        sig = parse_signature(f, "kernel")
+        graph, rets = _trace(f, "kernel", name or f.__name__, sig)
+        sig = Signature(list(sig.params), rets)
+        return KernelOp(f, name, sig, graph, num_warps=num_warps, fp_fusion=fp_fusion, math=math)
+
+    return wrap(fn) if callable(fn) else wrap
+
+
+def library(name=None, *, acc: Optional[DType] = None, impl: Optional[str] = None, **ignored):
+    """``@tilefish.library("gemm", acc=f32)``: a signature with an opaque body (``...``)."""
+    if callable(name):
+        raise TilefishDeclarationError("@library takes arguments: @library('gemm', acc=f32)")
+
+    def wrap(f):
+        sig = parse_signature(f, "library")
+        if not sig.returns and not any(p.access != "in" for p in sig.tensors):
+            raise TilefishDeclarationError(f"library '{f.__name__}': needs a return type or an Out/InOut parameter")
+        return LibraryOp(f, name, sig, acc, impl)
+
+    return wrap
+
+
+def graph(fn=None, *, name: Optional[str] = None, inputs: Tuple[str, ...] = (), weights: Tuple[str, ...] = (), **ignored):
+    """``@tilefish.graph``: a model step; ``inputs=`` / ``weights=`` label read-only tensor parameters."""
+
+    def wrap(f):
+        sig = parse_signature(f, "graph")
+        g, rets = _trace(f, "graph", name or f.__name__, sig)
+        sig2 = Signature(list(sig.params), rets)
+        roles = {}
+        for p in sig2.tensors:
+            if p.access != "in":
+                roles[p.name] = p.access
+            elif p.name in weights:
+                roles[p.name] = "weight"
+            elif p.name in inputs or not (inputs or weights):
+                roles[p.name] = "input" if not p.type.is_blockscaled else "weight"
+            else:
+                roles[p.name] = "input"
+        for n in tuple(inputs) + tuple(weights):
+            if n not in {p.name for p in sig2.tensors}:
+                raise TilefishDeclarationError(f"graph '{f.__name__}': '{n}' is not a tensor parameter")
+        return GraphOp(f, name, sig2, g, roles)
+
+    return wrap(fn) if callable(fn) else wrap

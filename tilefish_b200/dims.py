@@ -218,9 +218,10 @@ def as_expr(x: DimLike) -> DimExpr:
 
 
 def simplify(x: DimLike) -> DimLike:
-    """The canonical spelling of a size inside a type: an int when static, the ``Dim`` itself when it is one, else the expression."""
+    """The canonical spelling of a size inside a type: the ``Dim`` itself when it is one (a static one keeps its name and
+    compares equal to its int), an int for any other static size, else the expression."""
     if isinstance(x, Dim):
-        return x.value if x.is_static else x
+        return x
     e = as_expr(x)
     if e.is_static:
         return e.const

@@ -112,7 +112,8 @@ def nvfp4_global_scale(x, *, out=None, stream=None):
     return out
 
 
-def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, amax=None, stream=None) -> BlockScaledTensor:
+def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, amax=None, out: Optional[BlockScaledTensor] = None,
+             stream=None) -> BlockScaledTensor:
     """BlockScaled quantization of a bf16 [M, K] tensor along K.
 
     nvfp4 needs the tensor's global scale: given as ``global_scale`` (float32 [1] on the device), derived inside the kernel
@@ -127,8 +128,12 @@ def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, amax=N
     _pre(k % 32 == 0 and k > 0, f"x: K={k} is not a multiple of 32", "divisible", "x")
     ldx = x.stride(0) if m > 1 else k
     lay = N.SCALES_SWIZZLED if layout == "swizzled" else N.SCALES_PLAIN
-    codes = torch.empty((m, k // ELEMS_PER_BYTE[fmt]), dtype=torch.uint8, device=x.device)
-    scales = torch.empty(N.scale_bytes(FORMATS[fmt], m, k, lay), dtype=torch.uint8, device=x.device)
+    if out is not None:  # preallocated result (a plan's arena): same format, shape and layout
+        _pre(out.fmt == fmt and out.shape == (m, k) and out.layout == layout, f"out: expected a {fmt} {layout} tensor of shape {(m, k)}", "shape", "out")
+        codes, scales = out.codes, out.scales
+    else:
+        codes = torch.empty((m, k // ELEMS_PER_BYTE[fmt]), dtype=torch.uint8, device=x.device)
+        scales = torch.empty(N.scale_bytes(FORMATS[fmt], m, k, lay), dtype=torch.uint8, device=x.device)
     s = _stream(stream)
     lib = N.load()
     gs = None
@@ -139,12 +144,12 @@ def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, amax=N
     if fmt == "nvfp4" and amax is not None:
         _check(amax, "amax", torch.float32, None, x.device, align=4)
         _pre(amax.numel() == 1 and global_scale is None, "amax: expected one element and no global_scale", "shape", "amax")
-        gs = torch.empty(1, dtype=torch.float32, device=x.device)
+        gs = out.global_scale if out is not None and out.global_scale is not None else torch.empty(1, dtype=torch.float32, device=x.device)
         N.check(lib.tf_quantize_nvfp4_from_amax(x.data_ptr(), m, k, ldx, codes.data_ptr(), scales.data_ptr(), lay, amax.data_ptr(), gs.data_ptr(), s),
                 "tf_quantize_nvfp4_from_amax")
     elif fmt == "nvfp4":
         if global_scale is None:
-            gs = nvfp4_global_scale(x, stream=stream)
+            gs = nvfp4_global_scale(x, out=out.global_scale if out is not None else None, stream=stream)
         else:
             _check(global_scale, "global_scale", torch.float32, None, x.device, align=4)
             _pre(global_scale.numel() == 1, "global_scale: expected one element", "shape", "global_scale")
@@ -178,7 +183,7 @@ def unswizzle_scales(swizzled, rows: int, cols: int, *, stream=None):
 
 
 def residual_add_rmsnorm(x, residual, w, eps: float = 1e-6, *, out=None, quantize_to: Optional[str] = None, want_bf16: bool = True,
-                         q_global_scale=None, amax_out=None, stream=None):
+                         q_global_scale=None, amax_out=None, q_out: Optional[BlockScaledTensor] = None, stream=None):
     """``residual += f32(x)`` in place; returns bf16 ``rmsnorm(residual) * w`` and/or its BlockScaled quantization.
 
     Returns ``out`` (bf16), or ``(out, q)`` when ``quantize_to`` is given (``out`` is None with ``want_bf16=False``).
@@ -211,8 +216,12 @@ def residual_add_rmsnorm(x, residual, w, eps: float = 1e-6, *, out=None, quantiz
         _pre(quantize_to in FORMATS, f"unknown block-scaled format {quantize_to!r}", "dtype", "quantize_to")
         _pre(d % 32 == 0, f"x: D={d} is not a multiple of 32 (needed to quantize)", "divisible", "x")
         qfmt = FORMATS[quantize_to]
-        codes = torch.empty((m, d // ELEMS_PER_BYTE[quantize_to]), dtype=torch.uint8, device=x.device)
-        scales = torch.empty(N.scale_bytes(qfmt, m, d, N.SCALES_SWIZZLED), dtype=torch.uint8, device=x.device)
+        if q_out is not None:
+            _pre(q_out.fmt == quantize_to and q_out.shape == (m, d) and q_out.layout == "swizzled", "q_out: wrong format or shape", "shape", "q_out")
+            codes, scales = q_out.codes, q_out.scales
+        else:
+            codes = torch.empty((m, d // ELEMS_PER_BYTE[quantize_to]), dtype=torch.uint8, device=x.device)
+            scales = torch.empty(N.scale_bytes(qfmt, m, d, N.SCALES_SWIZZLED), dtype=torch.uint8, device=x.device)
         if quantize_to == "nvfp4":
             _pre(q_global_scale is not None, "nvfp4 output needs q_global_scale (a float32 [1] device tensor)", "argument", "q_global_scale")
             _check(q_global_scale, "q_global_scale", torch.float32, None, x.device, align=4)
@@ -236,22 +245,35 @@ def _amax_ptr(amax_out, device):
     return amax_out.data_ptr()
 
 
-def silu_gate(t, *, out=None, stream=None):
-    """bf16 [M, F] = silu(t[:, :F]) * t[:, F:] for a bf16 [M, 2F] tensor (row stride a multiple of 8)."""
+def silu_gate(t, up=None, *, out=None, stream=None):
+    """bf16 [M, F] = silu(gate) * up. ``silu_gate(t)`` takes the column halves of a bf16 [M, 2F] tensor; ``silu_gate(gate, up)``
+    two bf16 [M, F] tensors (rows dense, row strides multiples of 8: strided views of a wider tensor are fine)."""
     torch = _torch()
     _check(t, "t", torch.bfloat16, 2)
-    m, two_f = t.shape
-    _pre(two_f % 16 == 0, f"t: {two_f} columns; the halves must be multiples of 8", "divisible", "t")
-    f = two_f // 2
-    _pre(t.stride(1) == 1 and (m <= 1 or t.stride(0) % 8 == 0), "t: rows must be dense with a row stride that is a multiple of 8", "contiguous", "t")
+    if up is None:
+        m, two_f = t.shape
+        _pre(two_f % 16 == 0, f"t: {two_f} columns; the halves must be multiples of 8", "divisible", "t")
+        f = two_f // 2
+        gate, up = t[:, :f], t[:, f:]
+    else:
+        gate = t
+        _check(up, "up", torch.bfloat16, 2, gate.device)
+        m, f = gate.shape
+        _pre(tuple(up.shape) == (m, f), f"up: shape {tuple(up.shape)}, expected {(m, f)}", "shape", "up")
+        _pre(f % 8 == 0, f"gate: F={f} is not a multiple of 8", "divisible", "gate")
+    for v, nm in ((gate, "gate"), (up, "up")):
+        _pre(v.stride(1) == 1 and (m <= 1 or v.stride(0) % 8 == 0), f"{nm}: rows must be dense with a row stride that is a multiple of 8", "contiguous", nm)
     if out is None:
         out = torch.empty((m, f), dtype=torch.bfloat16, device=t.device)
     else:
         _check(out, "out", torch.bfloat16, 2, t.device)
         _dense(out, "out")
         _pre(tuple(out.shape) == (m, f), "out: wrong shape", "shape", "out")
-    ldt = t.stride(0) if m > 1 else two_f
-    N.check(N.load().tf_silu_gate(t.data_ptr(), m, f, ldt, out.data_ptr(), f, _stream(stream)), "tf_silu_gate")
+    if m == 0:
+        return out
+    ldg = gate.stride(0) if m > 1 else f
+    ldu = up.stride(0) if m > 1 else f
+    N.check(N.load().tf_silu_gate(gate.data_ptr(), up.data_ptr(), m, f, ldg, ldu, out.data_ptr(), f, _stream(stream)), "tf_silu_gate")
     return out
 
 

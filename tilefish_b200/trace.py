@@ -1,0 +1,223 @@
+"""Tracing: running a kernel or graph body over typed ``Value`` proxies; every operation type-checks and appends a node.
+
+Typing rules follow the reference's built-in ops (python/src/tilefish/ops.py:1-30, :535-600, :916-970): no implicit dtype
+promotion, python scalars and ``const`` parameters adopt the tensor's dtype, math ops are f32-only, a cast is a rounding
+point exactly when the target cannot represent every value of the source, ``split`` along a non-leading axis gives strided
+views. One addition: ``x.to(<BlockScaled>)`` of a bf16 tensor is allowed (the reference refuses it, ops.py:556-559) and
+traces to a ``quantize`` node, which this backend runs with its quantization kernels.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+from .dims import as_expr, simplify
+from .dtypes import BlockScaled, DType, f32
+from .errors import TilefishAttributeError, TilefishTypeError
+from .ir import Node, Scalar, Value
+from .types import TensorType, broadcast_shapes
+
+_ACTIVE: List["TraceContext"] = []
+
+
+def active() -> Optional["TraceContext"]:
+    return _ACTIVE[-1] if _ACTIVE else None
+
+
+class TraceContext:
+    def __init__(self, kind: str, name: str) -> None:
+        self.kind, self.name = kind, name
+        self.nodes: List[Node] = []
+        self.counter = 0
+        self.finals: Dict[str, Value] = {}
+        self.consts: Dict[str, Scalar] = {}
+
+    def __enter__(self):
+        _ACTIVE.append(self)
+        return self
+
+    def __exit__(self, *exc):
+        _ACTIVE.pop()
+
+    def emit(self, op: str, inputs: Sequence[Any], out_types: Sequence[TensorType], attrs: Optional[Dict[str, Any]] = None) -> Tuple[Value, ...]:
+        node = Node(op, tuple(inputs), dict(attrs or {}))
+        outs = []
+        for i, t in enumerate(out_types):
+            outs.append(Value(t, f"%{self.counter}", self, producer=node, index=i))
+            self.counter += 1
+        node.outputs = tuple(outs)
+        self.nodes.append(node)
+        return node.outputs
+
+
+def _ctx_of(v: Value) -> TraceContext:
+    ctx = active()
+    if ctx is None or v._ctx is not ctx:
+        raise TilefishTypeError(f"{v.ref} is used outside the declaration that traced it")
+    return ctx
+
+
+def _require_computable(v: Value, op: str) -> None:
+    if not getattr(v.type.dtype, "computable", False):
+        raise TilefishTypeError(f"{op}: {v.ref} has dtype {v.type.dtype}, which is storage only; cast it first (.to(f32))")
+
+
+def _operand(x, like: Value, op: str):
+    """A tensor operand as is; a python scalar or const adopts ``like``'s dtype."""
+    if isinstance(x, Value):
+        return x
+    if isinstance(x, Scalar):
+        if x.dtype is not like.type.dtype:
+            raise TilefishTypeError(f"{op}: const {x.name} is {x.dtype} but the tensor is {like.type.dtype}")
+        return x
+    if isinstance(x, (int, float)) and not isinstance(x, bool):
+        return Scalar(x, like.type.dtype)
+    raise TilefishTypeError(f"{op}: unsupported operand {x!r}")
+
+
+def binary(op: str, a, b) -> Value:
+    like = a if isinstance(a, Value) else b
+    ctx = _ctx_of(like)
+    a, b = _operand(a, like, op), _operand(b, like, op)
+    for v in (a, b):
+        if isinstance(v, Value):
+            _require_computable(v, op)
+    if isinstance(a, Value) and isinstance(b, Value):
+        if a.type.dtype is not b.type.dtype:
+            raise TilefishTypeError(f"{op}: {a.ref} is {a.type.dtype} but {b.ref} is {b.type.dtype}; there is no implicit promotion, cast one side")
+        shape = broadcast_shapes(a.type.shape, b.type.shape, op)
+    else:
+        shape = like.type.shape
+    return ctx.emit(op, (a, b), (TensorType(shape, like.type.dtype),))[0]
+
+
+def cast(x: Value, dtype) -> Value:
+    ctx = _ctx_of(x)
+    src = x.type.dtype
+    if isinstance(dtype, BlockScaled):
+        if isinstance(src, BlockScaled) or src.name != "bf16":
+            raise TilefishTypeError(f"cast: only a bf16 tensor can be quantized to {dtype}, {x.ref} is {src}")
+        if dtype.format_name is None:
+            raise TilefishTypeError(f"cast: this backend has no quantizer for {dtype} (mxfp8, mxfp4 and nvfp4 are implemented)")
+        if dtype.normalized(x.type.rank).axis != x.type.rank - 1:
+            raise TilefishTypeError(f"cast: {dtype} must block the last axis")
+        return ctx.emit("quantize", (x,), (TensorType(x.type.shape, dtype),), {"to": dtype, "rounding": True})[0]
+    if isinstance(src, BlockScaled):
+        raise TilefishTypeError(f"cast: dequantizing {x.ref} ({src}) is not an operation of this backend; the gemm consumes block-scaled operands directly")
+    if not isinstance(dtype, DType):
+        raise TilefishTypeError(f"cast: expected a dtype, got {dtype!r}")
+    rounding = src.is_narrowing_to(dtype)
+    return ctx.emit("cast", (x,), (TensorType(x.type.shape, dtype),), {"to": dtype, "rounding": rounding})[0]
+
+
+def unary_f32(op: str, x: Value) -> Value:
+    ctx = _ctx_of(x)
+    if x.type.dtype is not f32:
+        raise TilefishTypeError(f"{op}: needs an f32 tensor, {x.ref} is {x.type.dtype}; cast first")
+    return ctx.emit(op, (x,), (TensorType(x.type.shape, f32),))[0]
+
+
+def reduce(op: str, x: Value, axis, keepdims: bool) -> Value:
+    ctx = _ctx_of(x)
+    _require_computable(x, op)
+    axes = (axis,) if isinstance(axis, int) else tuple(axis)
+    rank = x.type.rank
+    norm = []
+    for ax in axes:
+        a = ax + rank if ax < 0 else ax
+        if not 0 <= a < rank:
+            raise TilefishTypeError(f"{op}: axis {ax} is out of range for {x.type!r}")
+        norm.append(a)
+    if keepdims:
+        shape = tuple(1 if i in norm else s for i, s in enumerate(x.type.shape))
+    else:
+        shape = tuple(s for i, s in enumerate(x.type.shape) if i not in norm)
+    return ctx.emit(op, (x,), (TensorType(shape, x.type.dtype),), {"axes": tuple(norm), "keepdims": bool(keepdims)})[0]
+
+
+def split(x: Value, size, axis: int = -1) -> Tuple[Value, ...]:
+    ctx = _ctx_of(x)
+    rank = x.type.rank
+    ax = axis + rank if axis < 0 else axis
+    if not 0 <= ax < rank:
+        raise TilefishTypeError(f"split: axis {axis} is out of range for {x.type!r}")
+    total, part = as_expr(x.type.shape[ax]), as_expr(size)
+    if not (total.is_static and part.is_static) or part.const <= 0 or total.const % part.const:
+        if not (total.is_static and part.is_static):
+            raise TilefishTypeError(f"split: the axis size {x.type.shape[ax]} and the part size {size} must be static")
+        raise TilefishTypeError(f"split: {x.type.shape[ax]} is not a multiple of {size}")
+    count = total.const // part.const
+    size = simplify(size)
+    shape = tuple(size if i == ax else s for i, s in enumerate(x.type.shape))
+    if isinstance(x.type.dtype, BlockScaled):
+        fmt = x.type.dtype.normalized(rank)
+        if fmt.axis == ax and part.const % fmt.block:
+            raise TilefishTypeError(f"split: parts of {size} along the blocked axis are not whole blocks of {fmt.block}")
+    leading = all(as_expr(s) == as_expr(1) for s in x.type.shape[:ax])
+    t = TensorType(shape, x.type.dtype, contiguous=leading and x.type.contiguous)
+    return ctx.emit("split", (x,), (t,) * count, {"axis": ax, "sizes": (size,) * count})
+
+
+def store(target: Value, value: Value) -> None:
+    ctx = _ctx_of(target)
+    if not target.is_param or target.access not in ("inout", "out"):
+        raise TilefishTypeError(f"{target.ref} is not an InOut or Out parameter: it cannot be stored to")
+    if not isinstance(value, Value) or value.type.dtype is not target.type.dtype:
+        raise TilefishTypeError(f"store to {target.name}: the value must be a {target.type.dtype} tensor")
+    if tuple(as_expr(s) for s in value.type.shape) != tuple(as_expr(s) for s in target.type.shape):
+        raise TilefishTypeError(f"store to {target.name}: shape {value.type!r} does not match {target.type!r}")
+    (out,) = ctx.emit("store", (target, value), (target.type,), {"target": target.name})
+    ctx.finals[target.name] = out
+
+
+# ---- the methods of a traced value ------------------------------------------------------------------------------------
+def _install() -> None:
+    Value.to = lambda self, dtype: cast(self, dtype)
+    Value.split = lambda self, size, axis=-1: split(self, size, axis)
+    Value.__add__ = lambda self, o: binary("add", self, o)
+    Value.__radd__ = lambda self, o: binary("add", o, self)
+    Value.__sub__ = lambda self, o: binary("sub", self, o)
+    Value.__rsub__ = lambda self, o: binary("sub", o, self)
+    Value.__mul__ = lambda self, o: binary("mul", self, o)
+    Value.__rmul__ = lambda self, o: binary("mul", o, self)
+    Value.__truediv__ = lambda self, o: binary("div", self, o)
+
+    def setitem(self, key, value):
+        if key is not Ellipsis:
+            raise TilefishTypeError("only whole-tensor stores are supported: write `x[...] = value`")
+        store(self, value)
+
+    Value.__setitem__ = setitem
+
+    def missing(self, name):
+        raise TilefishAttributeError(f"traced values have no attribute {name!r}")
+
+    Value.__getattr__ = missing
+
+
+_install()
+
+
+# ---- public math ops ----------------------------------------------------------------------------------------------------
+def silu(x: Value) -> Value:
+    return unary_f32("silu", x)
+
+
+def rsqrt(x: Value) -> Value:
+    return unary_f32("rsqrt", x)
+
+
+def exp(x: Value) -> Value:
+    return unary_f32("exp", x)
+
+
+def mean(x: Value, axis=-1, keepdims: bool = False) -> Value:
+    return reduce("mean", x, axis, keepdims)
+
+
+def sum(x: Value, axis=-1, keepdims: bool = False) -> Value:  # noqa: A001 - the reference's spelling
+    return reduce("sum", x, axis, keepdims)
+
+
+def max(x: Value, axis=-1, keepdims: bool = False) -> Value:  # noqa: A001
+    return reduce("max", x, axis, keepdims)
