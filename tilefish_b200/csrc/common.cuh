@@ -72,6 +72,10 @@ __device__ __forceinline__ float e4m3_to_f32(uint32_t code) {
   return f;
 }
 
+// silu(x) = x * (1 / (1 + exp(-x))) with the hardware's approximate exp2 and reciprocal (what the reference's own binaries use:
+// ex2.approx and div.full). One definition for the stand-alone kernel and the GEMM epilogue, so both give the same bytes.
+__device__ __forceinline__ float silu_f32(float g) { return __fmul_rn(g, __fdividef(1.0f, __fadd_rn(1.0f, __expf(-g)))); }
+
 // Byte offset of scale entry (r, c) of a [rows, cols] scale tensor in the swizzled layout; n_ct = ceil(cols / 4).
 __host__ __device__ __forceinline__ int64_t swizzled_scale_offset(int64_t r, int64_t c, int64_t n_ct) {
   int64_t tile = (r >> 7) * n_ct + (c >> 2);

@@ -8,6 +8,8 @@
 //            the stage and, after the last one, hands the accumulator to the epilogue
 //   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), scale, fused epilogue (none / SiLU gate /
 //            residual add), bf16 stores
+// The accumulator is double-buffered in tensor memory (overlapped for 256-column tiles, see TileCfg), so a tile's epilogue
+// runs while the next tile's MMAs are issued.
 // No TMA multicast, no clusters. Every mbarrier wait is bounded (about one second): on a timeout the kernel records
 // TF_ERR_DEVICE_TIMEOUT in a device status word, every role leaves its loop, tensor memory is freed and the kernel returns.
 //
@@ -59,13 +61,20 @@ struct TileCfg {
   static constexpr int kStagesRaw = (kSmemLimit - 1024 - kBarrierBytes) / kStageBytes;
   static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
-  // two scale buffers in tensor memory, used by alternate stages, so that the copy of the next stage's scales does not
-  // have to wait for the MMAs that still read the current ones
-  static constexpr int kTmemSfSet = kST * 4 * (1 + kNB);  // columns of one buffer: A scales then B scales
-  static constexpr int kTmemSfa = BLOCK_N;                // first column of the A scales of buffer 0
-  static constexpr int kTmemSfb = BLOCK_N + kST * 4;      // first column of the B scales of buffer 0
-  static constexpr int kTmemUsed = BLOCK_N + 2 * kTmemSfSet;
-  static constexpr int kTmemCols = kTmemUsed <= 256 ? 256 : 512;
+  // Tensor memory (512 columns): two accumulators used by alternate tiles, so that the epilogue of one tile runs under the
+  // MMAs of the next, then two scale buffers used by alternate stages. Two 256-column accumulators plus 96 scale columns do
+  // not fit, so with BLOCK_N = 256 the accumulators OVERLAP: accumulator 1 starts at column 160 and shares columns
+  // [160, 256) with accumulator 0. The epilogue first moves the shared columns of its tile into registers, then releases
+  // the next tile's MMAs, then drains the rest. With BLOCK_N = 128 the accumulators are disjoint.
+  static constexpr int kAccStride = BLOCK_N == 256 ? 160 : BLOCK_N;  // first column of accumulator 1
+  static constexpr int kOverlapChunks = BLOCK_N == 256 ? 3 : 0;      // 32-column chunks both accumulators cover
+  static constexpr int kTmemSfSet = kST * 4 * (1 + kNB);             // columns of one scale buffer: A scales then B scales
+  static constexpr int kTmemSfBase = kAccStride + BLOCK_N;           // 416 or 256
+  static constexpr int kTmemSfa = kTmemSfBase;                       // first column of the A scales of buffer 0
+  static constexpr int kTmemSfb = kTmemSfBase + kST * 4;             // first column of the B scales of buffer 0
+  static constexpr int kTmemUsed = kTmemSfBase + 2 * kTmemSfSet;
+  static constexpr int kTmemCols = 512;
+  static_assert(kTmemUsed <= 512, "tensor memory budget");
 };
 
 struct GemmParams {
@@ -193,7 +202,98 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
-__device__ __forceinline__ float silu_f32(float g) { return __fmul_rn(g, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g)))); }
+
+// ---- epilogue helpers ------------------------------------------------------------------------------------------------------
+// Stores 32 consecutive bf16 outputs of one row (packed two per word) and applies the residual / amax side effects.
+template <int EPI>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t (&packed)[16], int row, int col, uint32_t& amax2) {
+  if (row >= p.m) return;
+  uint16_t* orow = p.out + (int64_t)row * p.ldo + col;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    if (col + g * 8 + 8 <= p.n) {
+      *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+      if (p.out_amax) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) amax2 = __vmaxu2(amax2, packed[4 * g + e] & 0x7FFF7FFFu);
+      }
+      if (EPI == TF_EPI_RESIDUAL) {
+        float4* rp = reinterpret_cast<float4*>(p.residual + (int64_t)row * p.n + col + g * 8);
+        float4 r0 = rp[0], r1 = rp[1];
+        r0.x = __fadd_rn(r0.x, bf16lo_to_f32(packed[4 * g]));
+        r0.y = __fadd_rn(r0.y, bf16hi_to_f32(packed[4 * g]));
+        r0.z = __fadd_rn(r0.z, bf16lo_to_f32(packed[4 * g + 1]));
+        r0.w = __fadd_rn(r0.w, bf16hi_to_f32(packed[4 * g + 1]));
+        r1.x = __fadd_rn(r1.x, bf16lo_to_f32(packed[4 * g + 2]));
+        r1.y = __fadd_rn(r1.y, bf16hi_to_f32(packed[4 * g + 2]));
+        r1.z = __fadd_rn(r1.z, bf16lo_to_f32(packed[4 * g + 3]));
+        r1.w = __fadd_rn(r1.w, bf16hi_to_f32(packed[4 * g + 3]));
+        rp[0] = r0;
+        rp[1] = r1;
+      }
+    }
+  }
+}
+
+// One tile's epilogue for accumulator BUF (compile time, so that the chunks held in registers are indexed statically).
+// t_acc: tensor-memory address of the accumulator for this warp's 32 lanes. Returns after the last store.
+template <int FMT, int BLOCK_N, int EPI, int BUF>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_acc, uint32_t bar_release, int lane, int row, int col0, float alpha,
+                                              uint32_t& amax2) {
+  using Cfg = TileCfg<FMT, BLOCK_N>;
+  constexpr int kOutCols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;
+  constexpr int kOv = Cfg::kOverlapChunks;
+  constexpr int kOvFirst = (BUF == 0) ? (BLOCK_N / 32 - kOv) : 0;  // first chunk (of this accumulator) the other accumulator also covers
+  uint32_t ov[kOv > 0 ? kOv : 1][32];
+#pragma unroll
+  for (int i = 0; i < kOv; ++i) tc_ld32(t_acc + (kOvFirst + i) * 32, ov[i]);
+  if (kOv > 0) tc_wait_ld();
+  // the columns shared with the other accumulator are in registers (or there are none): the next tile's MMAs may start
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_release);
+
+#pragma unroll
+  for (int c = 0; c < kOutCols / 32; ++c) {
+    uint32_t v[32], packed[16];
+    constexpr int dummy = 0;
+    (void)dummy;
+    const bool v_in_regs = kOv > 0 && c >= kOvFirst && c < kOvFirst + kOv;
+    if (v_in_regs) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = ov[(c - kOvFirst) < 0 ? 0 : ((c - kOvFirst) >= kOv ? 0 : (c - kOvFirst))][j];
+    } else {
+      tc_ld32(t_acc + c * 32, v);
+    }
+    if (EPI == TF_EPI_SILU_GATE) {
+      uint32_t u[32];
+      const int cu = BLOCK_N / 64 + c;  // the up chunk that pairs with gate chunk c
+      const bool u_in_regs = kOv > 0 && cu >= kOvFirst && cu < kOvFirst + kOv;
+      if (u_in_regs) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) u[j] = ov[(cu - kOvFirst) < 0 ? 0 : ((cu - kOvFirst) >= kOv ? 0 : (cu - kOvFirst))][j];
+      } else {
+        tc_ld32(t_acc + cu * 32, u);
+      }
+      if (!v_in_regs || !u_in_regs) tc_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        // the GEMM result is bf16 (one rounding); the gate then reads it back as f32, as the unfused graph does
+        const uint32_t g2 = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
+        const uint32_t u2 = pack_bf16x2(__fmul_rn(__uint_as_float(u[2 * j]), alpha), __fmul_rn(__uint_as_float(u[2 * j + 1]), alpha));
+        const float lo = __fmul_rn(silu_f32(bf16lo_to_f32(g2)), bf16lo_to_f32(u2));
+        const float hi = __fmul_rn(silu_f32(bf16hi_to_f32(g2)), bf16hi_to_f32(u2));
+        packed[j] = pack_bf16x2(lo, hi);
+      }
+    } else {
+      if (!v_in_regs) tc_wait_ld();
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        packed[j] = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
+    }
+    store_chunk<EPI>(p, packed, row, col0 + c * 32, amax2);
+  }
+}
 
 // ---- the kernel ------------------------------------------------------------------------------------------------------------
 template <int FMT, int BLOCK_N, int EPI>
@@ -304,15 +404,16 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
     constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);  // SBO 1024 B, version 1, SWIZZLE_128B
     constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);                   // SBO 128 B, version 1, no swizzle
     const bool elected = elect_one();
-    const uint32_t tmem_acc = tmem_base;
     int stage = 0;
-    uint32_t phase = 0, tile_phase = 0, sf_buf = 0;
+    uint32_t phase = 0, tile_phase = 0, sf_buf = 0, acc_buf = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
       ok = mbar_wait(bar_tmem_empty, tile_phase ^ 1, abort_flag, 2);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t tmem_acc = tmem_base + acc_buf * Cfg::kAccStride;
+      acc_buf ^= 1;
       const int n_blk = tile / p.m_blocks;
       bool all_b = true;
       bool b_ok[kNB];
@@ -386,7 +487,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
     // ---------------- epilogue (warps 2..5; warp w reads lanes 32*(w%4) .. +31) ----------------
     const int q = warp & 3;
     const float alpha = (FMT == TF_FMT_NVFP4) ? __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs)) : 1.0f;
-    uint32_t tile_phase = 0;
+    uint32_t tile_phase = 0, acc_buf = 0;
     uint32_t amax2 = 0;  // running max of |out| as two packed bf16 magnitudes
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
       const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
@@ -397,62 +498,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       const int row = m_blk * kBlockM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
       const int col0 = n_blk * kOutCols;
-#pragma unroll 1
-      for (int c = 0; c < kOutCols / 32; ++c) {
-        uint32_t v[32];
-        tc_ld32(t_row + c * 32, v);
-        uint32_t packed[16];
-        if (EPI == TF_EPI_SILU_GATE) {
-          uint32_t u[32];
-          tc_ld32(t_row + 128 + c * 32, u);
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            // the GEMM result is bf16 (one rounding); the gate then reads it back as f32, as the unfused graph does
-            const uint32_t g2 = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
-            const uint32_t u2 = pack_bf16x2(__fmul_rn(__uint_as_float(u[2 * j]), alpha), __fmul_rn(__uint_as_float(u[2 * j + 1]), alpha));
-            const float lo = __fmul_rn(silu_f32(bf16lo_to_f32(g2)), bf16lo_to_f32(u2));
-            const float hi = __fmul_rn(silu_f32(bf16hi_to_f32(g2)), bf16hi_to_f32(u2));
-            packed[j] = pack_bf16x2(lo, hi);
-          }
-        } else {
-          tc_wait_ld();
-#pragma unroll
-          for (int j = 0; j < 16; ++j)
-            packed[j] = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
-        }
-        if (row < p.m) {
-          const int col = col0 + c * 32;
-          uint16_t* orow = p.out + (int64_t)row * p.ldo + col;
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col + g * 8 + 8 <= p.n) {
-              *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
-              if (p.out_amax) {
-#pragma unroll
-                for (int e = 0; e < 4; ++e) amax2 = __vmaxu2(amax2, packed[4 * g + e] & 0x7FFF7FFFu);
-              }
-              if (EPI == TF_EPI_RESIDUAL) {
-                float4* rp = reinterpret_cast<float4*>(p.residual + (int64_t)row * p.n + col + g * 8);
-                float4 r0 = rp[0], r1 = rp[1];
-                r0.x = __fadd_rn(r0.x, bf16lo_to_f32(packed[4 * g]));
-                r0.y = __fadd_rn(r0.y, bf16hi_to_f32(packed[4 * g]));
-                r0.z = __fadd_rn(r0.z, bf16lo_to_f32(packed[4 * g + 1]));
-                r0.w = __fadd_rn(r0.w, bf16hi_to_f32(packed[4 * g + 1]));
-                r1.x = __fadd_rn(r1.x, bf16lo_to_f32(packed[4 * g + 2]));
-                r1.y = __fadd_rn(r1.y, bf16hi_to_f32(packed[4 * g + 2]));
-                r1.z = __fadd_rn(r1.z, bf16lo_to_f32(packed[4 * g + 3]));
-                r1.w = __fadd_rn(r1.w, bf16hi_to_f32(packed[4 * g + 3]));
-                rp[0] = r0;
-                rp[1] = r1;
-              }
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tmem_empty);
+      if (acc_buf == 0)
+        epilogue_tile<FMT, BLOCK_N, EPI, 0>(p, t_row, bar_tmem_empty, lane, row, col0, alpha, amax2);
+      else
+        epilogue_tile<FMT, BLOCK_N, EPI, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha, amax2);
+      acc_buf ^= 1;
       tile_phase ^= 1;
     }
     if (p.out_amax) {  // one atomic per warp

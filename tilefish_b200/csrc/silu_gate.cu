@@ -7,8 +7,7 @@
 namespace tf {
 
 __device__ __forceinline__ float silu_gate1(float g, float u) {
-  const float s = __fmul_rn(g, __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-g))));
-  return __fmul_rn(s, u);
+  return __fmul_rn(silu_f32(g), u);
 }
 
 __global__ void __launch_bounds__(256) silu_gate_kernel(const uint4* __restrict__ gate, const uint4* __restrict__ up, int64_t m, int fvec,
