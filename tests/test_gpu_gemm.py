@@ -129,9 +129,10 @@ def test_gemm_full_size_sampled_rows(K, fmt):
     ob = O.quantize(w, fmt)
     ref = O.f32_to_bf16(O.dequantize(oa[0], oa[1], fmt, oa[2]) @ O.dequantize(ob[0], ob[1], fmt, ob[2]).t())
     assert_gemm_close(out[rows.cuda()].cpu(), ref, f"{fmt} sampled rows")
-    # rows are independent: the same rows computed as their own small GEMM give the same bytes
+    # rows are independent: the same rows computed as their own small GEMM (which takes the split-K path, another summation
+    # order) agree to the GEMM tolerance
     sub = K.gemm_blockscaled(K.quantize(a[rows].cuda(), fmt, global_scale=gs.cuda() if gs is not None else None), qb)
-    assert torch.equal(sub, out[rows.cuda()])
+    assert_gemm_close(sub.cpu(), out[rows.cuda()].cpu(), f"{fmt} sub-problem")
     no_device_timeout()
 
 
@@ -152,3 +153,39 @@ def test_gemm_refusals(K):
         K.gemm_blockscaled(qa, plain)
     empty = K.gemm_blockscaled(K.quantize(torch.empty((0, 64), dtype=torch.bfloat16, device="cuda"), "mxfp8"), K.quantize(w.cuda(), "mxfp8"))
     assert empty.shape == (0, 128)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,n,k,epi", [(1, 2560, 3072, "none"), (16, 6144, 2560, "none"), (64, 1024, 8192, "none"), (32, 1536, 2560, "silu_gate"),
+                                       (40, 512, 4096, "residual")])
+def test_gemm_small_m_takes_the_split_k_path(K, fmt, m, n, k, epi):
+    """Few output tiles and a long K: the problem is cut along K into an f32 workspace and reduced by a second kernel. Same
+    oracle, same bound; the partial sums are added in split order, so two runs give identical bytes."""
+    assert K.gemm_workspace_bytes(m, n, k, fmt, epi) > 0, "this shape is meant to exercise split-K"
+    rows_b = 2 * n if epi == "silu_gate" else n
+    a, w = operands(m, rows_b, k, seed=m + n)
+    qa, qb = K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt)
+    res0 = O.randn((m, n), 8)
+    res = res0.cuda() if epi == "residual" else None
+    amax = torch.zeros(1, device="cuda")
+    out = K.gemm_blockscaled(qa, qb, epilogue=epi, residual=res, amax_out=amax)
+    acc = O.f32_to_bf16(oracle_acc(a, w, fmt))
+    if epi == "silu_gate":
+        ref = O.silu_gate(acc[:, :n], acc[:, n:])
+        g, r = out.cpu().float(), ref.float()
+        assert float(((g - r).abs() > 2.0**-7 * r.abs().max()).float().mean()) == 0.0
+        assert float((g - r).abs().max()) <= TOL * float(acc.float().abs().max()) * (float(acc.float().abs().max()) + 1.0)
+    else:
+        assert_gemm_close(out.cpu(), acc, f"{fmt} split-K {m}x{n}x{k}")
+    assert float(amax.item()) == float(out.float().abs().max().item())
+    if epi == "residual":
+        assert torch.equal(res.cpu(), res0 + out.cpu().float())
+    again = K.gemm_blockscaled(qa, qb, epilogue=epi, residual=res0.cuda() if epi == "residual" else None)
+    assert torch.equal(again, out), "split-K must be deterministic"
+    from tilefish_b200 import TilefishPreconditionError
+
+    with pytest.raises(TilefishPreconditionError) as e:
+        K.gemm_blockscaled(qa, qb, epilogue=epi, residual=res0.cuda() if epi == "residual" else None,
+                           workspace=torch.empty(256, dtype=torch.uint8, device="cuda"))
+    assert e.value.kind == "workspace"
+    no_device_timeout()

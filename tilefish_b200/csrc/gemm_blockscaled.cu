@@ -90,6 +90,8 @@ struct GemmParams {
   int64_t ldo;
   float* residual;
   unsigned int* out_amax;
+  int splits, k_stages_per_split;  // split-K: every (tile, split) accumulates a K range into the f32 workspace
+  float* ws;
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------------
@@ -295,8 +297,99 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ac
   }
 }
 
+// Split-K: dumps this (tile, split)'s raw f32 accumulator rows into the workspace [splits][M][acc columns].
+template <int FMT, int BLOCK_N, int BUF>
+__device__ __forceinline__ void epilogue_partial(const GemmParams& p, uint32_t t_acc, uint32_t bar_release, int lane, int row, int col0,
+                                                 float* __restrict__ ws_row) {
+  using Cfg = TileCfg<FMT, BLOCK_N>;
+  constexpr int kOv = Cfg::kOverlapChunks;
+  constexpr int kOvFirst = (BUF == 0) ? (BLOCK_N / 32 - kOv) : 0;
+  uint32_t ov[kOv > 0 ? kOv : 1][32];
+#pragma unroll
+  for (int i = 0; i < kOv; ++i) tc_ld32(t_acc + (kOvFirst + i) * 32, ov[i]);
+  if (kOv > 0) tc_wait_ld();
+  tc_fence_before();
+  __syncwarp();
+  if (lane == 0) mbar_arrive(bar_release);
+#pragma unroll
+  for (int c = 0; c < BLOCK_N / 32; ++c) {
+    uint32_t v[32];
+    const bool in_regs = kOv > 0 && c >= kOvFirst && c < kOvFirst + kOv;
+    if (in_regs) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = ov[(c - kOvFirst) < 0 ? 0 : ((c - kOvFirst) >= kOv ? 0 : (c - kOvFirst))][j];
+    } else {
+      tc_ld32(t_acc + c * 32, v);
+      tc_wait_ld();
+    }
+    if (row < p.m) {
+      const int col = col0 + c * 32;
+#pragma unroll
+      for (int g = 0; g < 8; ++g)
+        if (col + g * 4 + 4 <= p.n)
+          *reinterpret_cast<uint4*>(ws_row + col + g * 4) = make_uint4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+    }
+  }
+}
+
+// Split-K second pass: sums the partials in split order (deterministic), then the same epilogue arithmetic as the one-pass
+// kernel. n_acc = accumulator columns (2 * n with the SiLU gate), one thread per 8 output columns.
+template <int EPI>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int splits, int m, int n, int n_acc, const float* a_gs,
+                                                            const float* b_gs, uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ residual,
+                                                            unsigned int* __restrict__ out_amax) {
+  const float alpha = (a_gs && b_gs) ? __fmul_rn(__ldg(a_gs), __ldg(b_gs)) : 1.0f;
+  const int nvec = n >> 3;
+  const int64_t total = (int64_t)m * nvec;
+  const int64_t plane = (int64_t)m * n_acc;
+  uint32_t amax2 = 0;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int row = (int)(i / nvec), col = (int)(i - (int64_t)row * nvec) * 8;
+    float acc[8], up[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = up[j] = 0.0f;
+    const float* base = ws + (int64_t)row * n_acc + col;
+    for (int sp = 0; sp < splits; ++sp) {
+      const float4 x0 = __ldcs(reinterpret_cast<const float4*>(base + sp * plane)), x1 = __ldcs(reinterpret_cast<const float4*>(base + sp * plane) + 1);
+      acc[0] += x0.x; acc[1] += x0.y; acc[2] += x0.z; acc[3] += x0.w; acc[4] += x1.x; acc[5] += x1.y; acc[6] += x1.z; acc[7] += x1.w;
+      if (EPI == TF_EPI_SILU_GATE) {
+        const float4 u0 = __ldcs(reinterpret_cast<const float4*>(base + n + sp * plane)), u1 = __ldcs(reinterpret_cast<const float4*>(base + n + sp * plane) + 1);
+        up[0] += u0.x; up[1] += u0.y; up[2] += u0.z; up[3] += u0.w; up[4] += u1.x; up[5] += u1.y; up[6] += u1.z; up[7] += u1.w;
+      }
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t g2 = pack_bf16x2(__fmul_rn(acc[2 * j], alpha), __fmul_rn(acc[2 * j + 1], alpha));
+      if (EPI == TF_EPI_SILU_GATE) {
+        const uint32_t u2 = pack_bf16x2(__fmul_rn(up[2 * j], alpha), __fmul_rn(up[2 * j + 1], alpha));
+        packed[j] = pack_bf16x2(__fmul_rn(silu_f32(bf16lo_to_f32(g2)), bf16lo_to_f32(u2)), __fmul_rn(silu_f32(bf16hi_to_f32(g2)), bf16hi_to_f32(u2)));
+      } else {
+        packed[j] = g2;
+      }
+      amax2 = __vmaxu2(amax2, packed[j] & 0x7FFF7FFFu);
+    }
+    *reinterpret_cast<uint4*>(out + (int64_t)row * ldo + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    if (EPI == TF_EPI_RESIDUAL) {
+      float4* rp = reinterpret_cast<float4*>(residual + (int64_t)row * n + col);
+      float4 r0 = rp[0], r1 = rp[1];
+      r0.x = __fadd_rn(r0.x, bf16lo_to_f32(packed[0])); r0.y = __fadd_rn(r0.y, bf16hi_to_f32(packed[0]));
+      r0.z = __fadd_rn(r0.z, bf16lo_to_f32(packed[1])); r0.w = __fadd_rn(r0.w, bf16hi_to_f32(packed[1]));
+      r1.x = __fadd_rn(r1.x, bf16lo_to_f32(packed[2])); r1.y = __fadd_rn(r1.y, bf16hi_to_f32(packed[2]));
+      r1.z = __fadd_rn(r1.z, bf16lo_to_f32(packed[3])); r1.w = __fadd_rn(r1.w, bf16hi_to_f32(packed[3]));
+      rp[0] = r0;
+      rp[1] = r1;
+    }
+  }
+  if (out_amax) {
+    uint32_t mx = max(amax2 & 0xFFFFu, amax2 >> 16);
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    if ((threadIdx.x & 31) == 0 && mx) atomicMax(out_amax, mx << 16);
+  }
+}
+
 // ---- the kernel ------------------------------------------------------------------------------------------------------------
-template <int FMT, int BLOCK_N, int EPI>
+template <int FMT, int BLOCK_N, int EPI, bool SPLITK>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                             const __grid_constant__ CUtensorMap tma_b, const GemmParams p) {
   using Cfg = TileCfg<FMT, BLOCK_N>;
@@ -348,7 +441,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-        const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
+        const int split = SPLITK ? tile / (p.m_blocks * p.n_blocks) : 0;
+        const int rest = SPLITK ? tile % (p.m_blocks * p.n_blocks) : tile;
+        const int m_blk = rest % p.m_blocks, n_blk = rest / p.m_blocks;
+        const int ks_begin = split * p.k_stages_per_split;
+        const int ks_end = min(ks_begin + p.k_stages_per_split, p.num_k_stages);
         int b_row[kNB], b_rt[kNB];
         bool b_ok[kNB];
 #pragma unroll
@@ -357,7 +454,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
           b_rt[nb] = b_row[nb] >> 7;
           b_ok[nb] = b_row[nb] < p.n_rows_b;
         }
-        for (int ks = 0; ks < p.num_k_stages; ++ks) {
+        for (int ks = ks_begin; ks < ks_end; ++ks) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) {
             ok = false;
             break;
@@ -414,7 +511,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       tc_fence_after();
       const uint32_t tmem_acc = tmem_base + acc_buf * Cfg::kAccStride;
       acc_buf ^= 1;
-      const int n_blk = tile / p.m_blocks;
+      const int split = SPLITK ? tile / (p.m_blocks * p.n_blocks) : 0;
+      const int n_blk = (SPLITK ? tile % (p.m_blocks * p.n_blocks) : tile) / p.m_blocks;
+      const int ks_begin = split * p.k_stages_per_split;
+      const int ks_end = min(ks_begin + p.k_stages_per_split, p.num_k_stages);
       bool all_b = true;
       bool b_ok[kNB];
 #pragma unroll
@@ -422,7 +522,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
         b_ok[nb] = ((EPI == TF_EPI_SILU_GATE) ? nb * p.n + n_blk * 128 : n_blk * BLOCK_N + nb * 128) < p.n_rows_b;
         all_b = all_b && b_ok[nb];
       }
-      for (int ks = 0; ks < p.num_k_stages; ++ks) {
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
         ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3);
         ok = __all_sync(0xFFFFFFFFu, ok);
         if (!ok) break;
@@ -436,7 +536,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
         const uint32_t b_lo = (((smem_b + stage * Cfg::kBStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
         const int sf_left = p.sf_col_tiles - ks * kST;
         const int k_left = p.k_bytes - ks * kStageKBytes;
-        const uint32_t first = (ks > 0) ? 1u : 0u;
+        const uint32_t first = (ks > ks_begin) ? 1u : 0u;
         if (elected) {
           if (sf_left >= kST && k_left >= kStageKBytes && all_b) {
 #pragma unroll
@@ -490,7 +590,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
     uint32_t tile_phase = 0, acc_buf = 0;
     uint32_t amax2 = 0;  // running max of |out| as two packed bf16 magnitudes
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-      const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
+      const int split = SPLITK ? tile / (p.m_blocks * p.n_blocks) : 0;
+      const int rest = SPLITK ? tile % (p.m_blocks * p.n_blocks) : tile;
+      const int m_blk = rest % p.m_blocks, n_blk = rest / p.m_blocks;
       bool ok = mbar_wait(bar_tmem_full, tile_phase, abort_flag, 4);
       ok = __all_sync(0xFFFFFFFFu, ok);
       if (!ok) break;
@@ -498,14 +600,21 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       const int row = m_blk * kBlockM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
       const int col0 = n_blk * kOutCols;
-      if (acc_buf == 0)
+      if (SPLITK) {
+        float* ws_row = p.ws + ((int64_t)split * p.m + row) * p.n;
+        if (acc_buf == 0)
+          epilogue_partial<FMT, BLOCK_N, 0>(p, t_row, bar_tmem_empty, lane, row, col0, ws_row);
+        else
+          epilogue_partial<FMT, BLOCK_N, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, ws_row);
+      } else if (acc_buf == 0) {
         epilogue_tile<FMT, BLOCK_N, EPI, 0>(p, t_row, bar_tmem_empty, lane, row, col0, alpha, amax2);
-      else
+      } else {
         epilogue_tile<FMT, BLOCK_N, EPI, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha, amax2);
+      }
       acc_buf ^= 1;
       tile_phase ^= 1;
     }
-    if (p.out_amax) {  // one atomic per warp
+    if (!SPLITK && p.out_amax) {  // one atomic per warp
       uint32_t mx = max(amax2 & 0xFFFFu, amax2 >> 16);
       for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
       if (lane == 0 && mx) atomicMax(p.out_amax, mx << 16);
@@ -550,10 +659,42 @@ static tf_status make_operand_map(CUtensorMap* map, const void* base, int64_t ro
   return TF_OK;
 }
 
-template <int FMT, int BLOCK_N, int EPI>
+// Split-K plan of a problem: how many K ranges each output tile is cut into, so that small-M problems (few tiles, long K: the
+// weight-streaming regime) still occupy every SM. Depends only on the sizes and the SM count: the workspace query and the launch
+// agree by construction.
+struct SplitPlan {
+  int block_n, splits, k_stages_per_split;
+};
+
+static SplitPlan split_plan(int64_t m, int64_t n, int64_t k_bytes, int epilogue) {
+  SplitPlan sp;
+  const int sms = sm_count();
+  const int64_t m_blocks = (m + kBlockM - 1) / kBlockM;
+  const int64_t n_acc = epilogue == TF_EPI_SILU_GATE ? 2 * n : n;
+  const int64_t stages = (k_bytes + kStageKBytes - 1) / kStageKBytes;
+  sp.block_n = 256;
+  sp.splits = 1;
+  sp.k_stages_per_split = (int)stages;
+  const int64_t tiles256 = m_blocks * ((n_acc + 255) / 256);
+  if (n <= 128 && epilogue != TF_EPI_SILU_GATE) sp.block_n = 128;
+  if (tiles256 * 2 <= sms && m <= 256) {  // few tiles: narrower tiles first, then cut K
+    sp.block_n = 128;
+    const int64_t tiles = m_blocks * ((n_acc + 127) / 128);
+    int64_t want = (sms + tiles - 1) / tiles;
+    if (want > stages / 4) want = stages / 4;
+    if (want > 16) want = 16;
+    if (want >= 2) {
+      sp.k_stages_per_split = (int)((stages + want - 1) / want);
+      sp.splits = (int)((stages + sp.k_stages_per_split - 1) / sp.k_stages_per_split);
+    }
+  }
+  return sp;
+}
+
+template <int FMT, int BLOCK_N, int EPI, bool SPLITK>
 static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
   using Cfg = TileCfg<FMT, BLOCK_N>;
-  auto kernel = gemm_blockscaled_kernel<FMT, BLOCK_N, EPI>;
+  auto kernel = gemm_blockscaled_kernel<FMT, BLOCK_N, EPI, SPLITK>;
   static thread_local int configured_dev = -1;
   int dev = 0;
   TF_CUDA(cudaGetDevice(&dev));
@@ -563,7 +704,7 @@ static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmP
   }
   constexpr int out_cols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;
   p.n_blocks = (p.n + out_cols - 1) / out_cols;
-  p.num_tiles = p.m_blocks * p.n_blocks;
+  p.num_tiles = p.m_blocks * p.n_blocks * p.splits;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   TF_LAUNCH_CHECK();
@@ -571,11 +712,34 @@ static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmP
 }
 
 template <int FMT>
-static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int epilogue, cudaStream_t stream) {
-  if (epilogue == TF_EPI_SILU_GATE) return launch_gemm<FMT, 256, TF_EPI_SILU_GATE>(ta, tb, p, stream);
+static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int epilogue, const SplitPlan& sp, cudaStream_t stream) {
+  if (sp.splits > 1) {
+    // first pass: plain accumulation over all accumulator columns into the workspace; second pass: reduce + epilogue
+    const int n_out = p.n;
+    float* residual = p.residual;
+    unsigned int* amax = p.out_amax;
+    p.n = p.n_rows_b;
+    p.out_amax = nullptr;
+    tf_status st = sp.block_n == 128 ? launch_gemm<FMT, 128, TF_EPI_NONE, true>(ta, tb, p, stream) : launch_gemm<FMT, 256, TF_EPI_NONE, true>(ta, tb, p, stream);
+    if (st != TF_OK) return st;
+    const int64_t total = (int64_t)p.m * (n_out >> 3);
+    const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
+    const unsigned grid = (unsigned)(need < cap ? need : cap);
+    const float* ags = FMT == TF_FMT_NVFP4 ? p.a_gs : nullptr;
+    const float* bgs = FMT == TF_FMT_NVFP4 ? p.b_gs : nullptr;
+    if (epilogue == TF_EPI_SILU_GATE)
+      splitk_reduce_kernel<TF_EPI_SILU_GATE><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
+    else if (epilogue == TF_EPI_RESIDUAL)
+      splitk_reduce_kernel<TF_EPI_RESIDUAL><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
+    else
+      splitk_reduce_kernel<TF_EPI_NONE><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
+    TF_LAUNCH_CHECK();
+    return TF_OK;
+  }
+  if (epilogue == TF_EPI_SILU_GATE) return launch_gemm<FMT, 256, TF_EPI_SILU_GATE, false>(ta, tb, p, stream);
   if (epilogue == TF_EPI_RESIDUAL)
-    return p.n > 128 ? launch_gemm<FMT, 256, TF_EPI_RESIDUAL>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_RESIDUAL>(ta, tb, p, stream);
-  return p.n > 128 ? launch_gemm<FMT, 256, TF_EPI_NONE>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_NONE>(ta, tb, p, stream);
+    return sp.block_n == 256 ? launch_gemm<FMT, 256, TF_EPI_RESIDUAL, false>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_RESIDUAL, false>(ta, tb, p, stream);
+  return sp.block_n == 256 ? launch_gemm<FMT, 256, TF_EPI_NONE, false>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_NONE, false>(ta, tb, p, stream);
 }
 
 }  // namespace tf
@@ -600,20 +764,18 @@ tf_status tf_device_status(int32_t* status, int32_t* detail) {
 }
 
 int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue) {
-  (void)m;
-  (void)n;
-  (void)k;
-  (void)format;
-  (void)epilogue;
-  return 0;
+  if (m <= 0 || n <= 0 || k <= 0 || format < TF_FMT_MXFP8 || format > TF_FMT_NVFP4 || epilogue < TF_EPI_NONE || epilogue > TF_EPI_RESIDUAL) return 0;
+  const int64_t k_bytes = format == TF_FMT_MXFP8 ? k : k / 2;
+  const SplitPlan sp = split_plan(m, n, k_bytes, epilogue);
+  if (sp.splits <= 1) return 0;
+  const int64_t n_acc = epilogue == TF_EPI_SILU_GATE ? 2 * n : n;
+  return (int64_t)sp.splits * m * n_acc * 4;
 }
 
 tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
                               const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
                               int32_t epilogue, void* epilogue_arg, float* out_amax, void* workspace, int64_t workspace_bytes, void* stream_) {
   clear_error();
-  (void)workspace;
-  (void)workspace_bytes;
   cudaStream_t stream = (cudaStream_t)stream_;
   TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", __func__, format);
   TF_CHECK_ARG(epilogue >= TF_EPI_NONE && epilogue <= TF_EPI_RESIDUAL, "%s: unknown epilogue %d", __func__, epilogue);
@@ -661,10 +823,21 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
   p.ldo = ldo;
   p.residual = static_cast<float*>(epilogue_arg);
   p.out_amax = reinterpret_cast<unsigned int*>(out_amax);
+  const SplitPlan sp = split_plan(m, n, k_bytes, epilogue);
+  p.splits = sp.splits;
+  p.k_stages_per_split = sp.k_stages_per_split;
+  p.ws = static_cast<float*>(workspace);
+  if (sp.splits > 1) {
+    const int64_t need = (int64_t)sp.splits * m * n_rows_b * 4;
+    if (!workspace || workspace_bytes < need)
+      return fail(TF_ERR_WORKSPACE, "%s: this problem is split %d ways along K and needs a %lld-byte workspace (tf_gemm_workspace_bytes)", __func__,
+                  sp.splits, (long long)need);
+    TF_CHECK_ALIGNED(workspace, 256, "workspace");
+  }
   switch (format) {
-    case TF_FMT_MXFP8: return dispatch_gemm<TF_FMT_MXFP8>(ta, tb, p, epilogue, stream);
-    case TF_FMT_MXFP4: return dispatch_gemm<TF_FMT_MXFP4>(ta, tb, p, epilogue, stream);
-    default: return dispatch_gemm<TF_FMT_NVFP4>(ta, tb, p, epilogue, stream);
+    case TF_FMT_MXFP8: return dispatch_gemm<TF_FMT_MXFP8>(ta, tb, p, epilogue, sp, stream);
+    case TF_FMT_MXFP4: return dispatch_gemm<TF_FMT_MXFP4>(ta, tb, p, epilogue, sp, stream);
+    default: return dispatch_gemm<TF_FMT_NVFP4>(ta, tb, p, epilogue, sp, stream);
   }
 }
 
