@@ -132,6 +132,28 @@ TF_API tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, 
                               int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* workspace,
                               int64_t workspace_bytes, void* stream);
 
+/* The same GEMM for callers that cannot hand over a workspace. (No counterpart in the reference.)
+ *
+ * Some hosts of this library run where device memory cannot be allocated at call time: a serving process whose memory pool
+ * was sized and frozen at start-up, a plugin that is only given the tensors of its operator, a real-time loop that may not
+ * enter the allocator. tf_gemm_blockscaled needs a workspace for small-M problems (it cuts K into ranges and sums the
+ * partial products in a second pass); this variant takes that workspace from a fixed 8 MiB array inside the library's
+ * device image instead (tf_gemm_static_scratch_bytes() returns the size). Every GPU that loads the library carries the
+ * array until the process exits.
+ *   - A problem whose workspace (tf_gemm_workspace_bytes) exceeds the array is refused with TF_ERR_WORKSPACE before anything
+ *     is launched; problems that need no workspace run exactly as tf_gemm_blockscaled does.
+ *   - The first call on a device looks the array's address up (once per device, with that device current). Make that first
+ *     call before starting any stream capture.
+ *   - The call allocates nothing: no cudaMalloc / cudaFree, no allocating library routine.
+ *   - All calls on a device share the one array and it keeps the previous call's contents. Nothing in it has to start at
+ *     zero (every partial sum that is read was written by the same call first), but two calls that run at the same time on
+ *     one GPU (two streams, two threads) overwrite each other's partial sums: order them on one stream.
+ * Arguments as tf_gemm_blockscaled, without the workspace. */
+TF_API int64_t tf_gemm_static_scratch_bytes(void);
+TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
+                                     const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
+                                     int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

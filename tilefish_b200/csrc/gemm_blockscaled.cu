@@ -742,6 +742,11 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
   return sp.block_n == 256 ? launch_gemm<FMT, 256, TF_EPI_NONE, false>(ta, tb, p, stream) : launch_gemm<FMT, 128, TF_EPI_NONE, false>(ta, tb, p, stream);
 }
 
+// Scratch of tf_gemm_blockscaled_static: lives in the library's device image, one copy per GPU that loads the library,
+// from load to process exit. Host code may not use this name as a pointer: it is a host-side stand-in for the symbol.
+constexpr int64_t kStaticScratchBytes = 8ll << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
 }  // namespace tf
 
 using namespace tf;
@@ -770,6 +775,45 @@ int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format,
   if (sp.splits <= 1) return 0;
   const int64_t n_acc = epilogue == TF_EPI_SILU_GATE ? 2 * n : n;
   return (int64_t)sp.splits * m * n_acc * 4;
+}
+
+static tf_status static_scratch_address(void** out) {
+  // The device address of g_static_scratch, looked up once per device (with that device current) and cached.
+  constexpr int kMaxDevices = 64;
+  static void* cached[kMaxDevices] = {nullptr};
+  int dev = 0;
+  TF_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail(TF_ERR_UNSUPPORTED, "tf_gemm_blockscaled_static: device ordinal %d is beyond %d", dev, kMaxDevices);
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (e != cudaSuccess || !ptr)
+      return fail(TF_ERR_CUDA, "tf_gemm_blockscaled_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    cached[dev] = ptr;
+  }
+  *out = cached[dev];
+  return TF_OK;
+}
+
+int64_t tf_gemm_static_scratch_bytes(void) { return kStaticScratchBytes; }
+
+tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
+                                     const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k,
+                                     int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* stream) {
+  clear_error();
+  const int64_t need = tf_gemm_workspace_bytes(m, n, k, format, epilogue);
+  if (need > kStaticScratchBytes)
+    return fail(TF_ERR_WORKSPACE,
+                "tf_gemm_blockscaled_static: this problem needs %lld bytes of scratch, the built-in scratch holds %lld; use tf_gemm_blockscaled "
+                "with a caller-provided workspace",
+                (long long)need, (long long)kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (need > 0) {
+    const tf_status st = static_scratch_address(&scratch);
+    if (st != TF_OK) return st;
+  }
+  return tf_gemm_blockscaled(a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, out, ldo, m, n, k, format, epilogue, epilogue_arg,
+                             out_amax, scratch, need > 0 ? kStaticScratchBytes : 0, stream);
 }
 
 tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
