@@ -75,7 +75,7 @@ TF_API int64_t tf_scale_bytes(int32_t format, int64_t rows, int64_t k, int32_t l
 
 /* BlockScaled quantization of a bf16 matrix along its last axis. The reference types this operation but refuses to run
  * it (python/src/tilefish/ops.py:556-559); these entry points are what `x.to(mxfp8)` lowers to here.
- *   x        bf16 [m, k], row stride ldx elements (ldx >= k, ldx % 8 == 0), 16-byte aligned
+ *   x        bf16 [m, k], row stride ldx elements (ldx >= k, ldx % 16 == 0), 32-byte aligned (256-bit loads)
  *   codes    [m, k] bytes (mxfp8) or [m, k/2] bytes (fp4), dense, 16-byte aligned
  *   scales   tf_scale_bytes(format, m, k, layout) bytes; with TF_SCALES_SWIZZLED the padding is zeroed by the call
  *   k        a multiple of 32

@@ -189,3 +189,45 @@ def test_gemm_small_m_takes_the_split_k_path(K, fmt, m, n, k, epi):
                            workspace=torch.empty(256, dtype=torch.uint8, device="cuda"))
     assert e.value.kind == "workspace"
     no_device_timeout()
+
+
+def test_two_cta_kernel_variant_matches_the_default_kernel():
+    """TF_GEMM_TWO_CTA=1 selects the cta_group::2 kernel (a CTA pair per 256 x 256 tile). It is read once per process, so the
+    variant runs in a child process and ships its result back as bytes; both kernels must satisfy the oracle bound, and they
+    agree with each other to that bound (the accumulation order inside the tensor core may differ)."""
+    import os
+    import subprocess
+    import sys
+    import tempfile
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    script = """
+import sys, torch
+sys.path.insert(0, %r)
+from tilefish_b200 import kernels as K, _native
+from oracle import blockscaled as O
+outs = {}
+for fmt in ("mxfp8", "nvfp4"):
+    a = O.randn((384, 2560), 1, torch.bfloat16); w = O.randn((1536, 2560), 2, torch.bfloat16, scale=2560 ** -0.5)
+    qa, qb = K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt)
+    outs[fmt] = K.gemm_blockscaled(qa, qb).cpu()
+    outs[fmt + "_silu"] = K.gemm_blockscaled(qa, qb, epilogue="silu_gate").cpu()
+assert _native.device_status() == (0, 0)
+torch.save(outs, sys.argv[1])
+""" % root
+    results = {}
+    with tempfile.TemporaryDirectory() as d:
+        for flag in ("0", "1"):
+            path = os.path.join(d, f"out{flag}.pt")
+            env = dict(os.environ, TF_GEMM_TWO_CTA=flag)
+            r = subprocess.run([sys.executable, "-c", script, path], env=env, capture_output=True, text=True, timeout=300)
+            assert r.returncode == 0, r.stderr[-2000:]
+            results[flag] = torch.load(path)
+    for key, one in results["0"].items():
+        two = results["1"][key]
+        bound = TOL * float(one.float().abs().max()) * (4.0 if key.endswith("_silu") else 1.0)
+        assert float((one.float() - two.float()).abs().max()) <= bound, key
+    a = O.randn((384, 2560), 1, torch.bfloat16)
+    w = O.randn((1536, 2560), 2, torch.bfloat16, scale=2560**-0.5)
+    for fmt in ("mxfp8", "nvfp4"):
+        assert_gemm_close(results["1"][fmt], O.f32_to_bf16(oracle_acc(a, w, fmt)), f"two-CTA {fmt}")

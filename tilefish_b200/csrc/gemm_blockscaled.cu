@@ -18,6 +18,8 @@
 // descriptor for the MX formats; NVFP4 uses all four bytes per MMA).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace tf {
@@ -108,6 +110,65 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
+// ---- thread-block-cluster helpers (the 2-CTA kernel) ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// The shared::cluster address of `addr` (a shared::cta address of this CTA) in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// tcgen05.commit of a CTA pair: arrives on the barrier at the same offset in both CTAs (a barrier signal, not a data multicast).
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  const uint16_t mask = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
+}
+// TMA load issued by either CTA of a pair: the destination is this CTA's shared memory, the mbarrier may be the peer's
+// (cta_group::2 lifts the same-CTA rule). No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_cluster) {
+  asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst),
+               "l"(map), "r"(x), "r"(y), "r"(bar_cluster)
+               : "memory");
+}
+__device__ __forceinline__ void tc_cp_sf_pair(uint32_t taddr, uint64_t desc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(desc) : "memory");
+}
+template <int FMT>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if (FMT == TF_FMT_MXFP8) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else if (FMT == TF_FMT_MXFP4) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;\n}" ::"r"(d),
+        "l"(a), "l"(b), "r"(idesc), "r"(accumulate), "r"(sfa), "r"(sfb)
+        : "memory");
+  }
+}
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -239,7 +300,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
 
 // One tile's epilogue for accumulator BUF (compile time, so that the chunks held in registers are indexed statically).
 // t_acc: tensor-memory address of the accumulator for this warp's 32 lanes. Returns after the last store.
-template <int FMT, int BLOCK_N, int EPI, int BUF>
+template <int FMT, int BLOCK_N, int EPI, int BUF, bool CLUSTER_BAR = false>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_acc, uint32_t bar_release, int lane, int row, int col0, float alpha,
                                               uint32_t& amax2) {
   using Cfg = TileCfg<FMT, BLOCK_N>;
@@ -253,7 +314,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ac
   // the columns shared with the other accumulator are in registers (or there are none): the next tile's MMAs may start
   tc_fence_before();
   __syncwarp();
-  if (lane == 0) mbar_arrive(bar_release);
+  if (lane == 0) {
+    if (CLUSTER_BAR) mbar_arrive_cluster(bar_release);
+    else mbar_arrive(bar_release);
+  }
 
 #pragma unroll
   for (int c = 0; c < kOutCols / 32; ++c) {
@@ -630,6 +694,239 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
   }
 }
 
+// ---- the 2-CTA kernel ------------------------------------------------------------------------------------------------------
+// Two CTAs of a cluster (a pair of SMs) compute one 256 x 256 tile with tcgen05.mma.cta_group::2: CTA r of the pair holds rows
+// [128 r, 128 r + 128) of the A tile and of the B tile in its own shared memory and the accumulator of its 128 rows in its own
+// tensor memory. Per 32 K MACs per K-byte each SM now fills 256 operand rows instead of 384, which is what the one-CTA kernel
+// is bound by. Each CTA loads its own halves with plain (non-multicast) TMA; the scale tiles of all 256 B rows are loaded by
+// both CTAs (4 KB per stage). The leader (rank 0) issues the scale copies and MMAs for both; barriers that both CTAs wait on
+// are signalled with tcgen05.commit's multicast arrive; the peer's producer and epilogue signal the leader through
+// cluster-mapped mbarrier addresses. Same bounded waits and teardown as the one-CTA kernel, plus a cluster barrier at both ends.
+template <int FMT, int EPI>
+struct PairCfg {
+  static constexpr int kST = FmtTraits<FMT>::kSfTiles;
+  static constexpr int kBHalfBytes = 128 * kStageKBytes;
+  static constexpr int kSfaStageBytes = kST * 512;
+  static constexpr int kSfbStageBytes = kST * 512 * 2;
+  static constexpr int kStageBytes = kAStageBytes + kBHalfBytes + kSfaStageBytes + kSfbStageBytes;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kStagesRaw = (kSmemLimit - 1024 - kBarrierBytes) / kStageBytes;
+  static constexpr int kStages = kStagesRaw > 8 ? 8 : kStagesRaw;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+};
+
+template <int FMT, int EPI>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
+                                                                                 const __grid_constant__ CUtensorMap tma_b,
+                                                                                 const __grid_constant__ CUtensorMap tma_sfa,
+                                                                                 const __grid_constant__ CUtensorMap tma_sfb, const GemmParams p) {
+  constexpr int BLOCK_N = 256;
+  using Cfg = TileCfg<FMT, BLOCK_N>;  // tensor-memory layout (per CTA: 128 lanes x 256 columns) is the one-CTA kernel's
+  using PC = PairCfg<FMT, EPI>;
+  constexpr int kStages = PC::kStages;
+  constexpr int kST = PC::kST;
+  constexpr int kNB = 2;
+  constexpr int kOutCols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t smem_a = smem_base;
+  const uint32_t smem_b = smem_a + kStages * kAStageBytes;
+  const uint32_t smem_sfa = smem_b + kStages * PC::kBHalfBytes;
+  const uint32_t smem_sfb = smem_sfa + kStages * PC::kSfaStageBytes;
+  const uint32_t bars = smem_sfb + kStages * PC::kSfbStageBytes;
+  const uint32_t bar_full = bars, bar_empty = bars + 8 * kStages, bar_tmem_full = bars + 16 * kStages, bar_tmem_empty = bar_tmem_full + 8;
+  const uint32_t tmem_slot = bar_tmem_empty + 8;
+  const uint32_t abort_slot = tmem_slot + 4;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(smem_gen + (tmem_slot - smem_base));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(bar_full + 8 * s, 2);   // one arrive.expect_tx from each CTA's producer (used in the leader only)
+      mbar_init(bar_empty + 8 * s, 1);  // the leader's commit arrives in both CTAs
+    }
+    mbar_init(bar_tmem_full, 1);
+    mbar_init(bar_tmem_empty, 8);  // 4 epilogue warps of each CTA (used in the leader only)
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the same warp of both CTAs allocates the pair's tensor memory
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tmem_slot), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anything crosses
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    // ---------------- producer (each CTA loads its own halves; completion is counted on the leader's barrier) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+        const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
+        int b_row[kNB], b_rt[kNB];
+        bool b_ok[kNB];
+#pragma unroll
+        for (int nb = 0; nb < kNB; ++nb) {
+          b_row[nb] = (EPI == TF_EPI_SILU_GATE) ? nb * p.n + n_blk * 128 : n_blk * BLOCK_N + nb * 128;
+          b_rt[nb] = b_row[nb] >> 7;
+          b_ok[nb] = b_row[nb] < p.n_rows_b;
+        }
+        const int a_row = m_blk * 256 + (int)rank * 128;
+        const bool a_ok = a_row < p.m;
+        for (int ks = 0; ks < p.num_k_stages; ++ks) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) {
+            ok = false;
+            break;
+          }
+          // scale tiles come through tensor maps too ([tiles, 512 bytes] as 128 x u32 rows; a box is always kST tiles, rows
+          // past the end read as zero), because only the tensor form of the copy may signal the peer's barrier
+          constexpr uint32_t sf_bytes = (uint32_t)kST * 512u;
+          uint32_t tx = 0;
+          if (a_ok) tx += kAStageBytes + sf_bytes;
+          if (b_ok[rank]) tx += PC::kBHalfBytes;
+#pragma unroll
+          for (int nb = 0; nb < kNB; ++nb)
+            if (b_ok[nb]) tx += sf_bytes;
+          const uint32_t full = mapa_shared(bar_full + 8 * stage, 0);  // the leader's barrier
+          mbar_expect_tx_cluster(full, tx);
+          if (a_ok) {
+            tma_load_2d_pair(smem_a + stage * kAStageBytes, &tma_a, ks * kStageKBytes, a_row, full);
+            tma_load_2d_pair(smem_sfa + stage * PC::kSfaStageBytes, &tma_sfa, 0, (a_row >> 7) * p.sf_col_tiles + ks * kST, full);
+          }
+          if (b_ok[rank]) tma_load_2d_pair(smem_b + stage * PC::kBHalfBytes, &tma_b, ks * kStageKBytes, b_row[rank], full);
+#pragma unroll
+          for (int nb = 0; nb < kNB; ++nb)
+            if (b_ok[nb]) tma_load_2d_pair(smem_sfb + stage * PC::kSfbStageBytes + nb * kST * 512, &tma_sfb, 0, b_rt[nb] * p.sf_col_tiles + ks * kST, full);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+      if (!ok) {
+        const unsigned long long t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (rank == 0) {
+      constexpr uint32_t idesc_base = (FmtTraits<FMT>::kElemFormat << 7) | (FmtTraits<FMT>::kElemFormat << 10) | ((uint32_t)(BLOCK_N >> 3) << 17) |
+                                      (FmtTraits<FMT>::kScaleIsE8 << 23) | ((uint32_t)(256 >> 4) << 24);
+      constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kDescHiSf = (128u >> 4) | (1u << 14);
+      const bool elected = elect_one();
+      int stage = 0;
+      uint32_t phase = 0, tile_phase = 0, sf_buf = 0, acc_buf = 0;
+      bool ok = true;
+      for (int tile = pair; tile < p.num_tiles && ok; tile += num_pairs) {
+        ok = mbar_wait(bar_tmem_empty, tile_phase ^ 1, abort_flag, 2);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc_buf * Cfg::kAccStride;
+        acc_buf ^= 1;
+        for (int ks = 0; ks < p.num_k_stages; ++ks) {
+          ok = mbar_wait(bar_full + 8 * stage, phase, abort_flag, 3);
+          ok = __all_sync(0xFFFFFFFFu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t tmem_sfa = tmem_base + Cfg::kTmemSfa + sf_buf * Cfg::kTmemSfSet;
+          const uint32_t tmem_sfb = tmem_base + Cfg::kTmemSfb + sf_buf * Cfg::kTmemSfSet;
+          sf_buf ^= 1;
+          const uint32_t sfa_lo = ((smem_sfa + stage * PC::kSfaStageBytes) & 0x3FFFFu) >> 4;
+          const uint32_t sfb_lo = ((smem_sfb + stage * PC::kSfbStageBytes) & 0x3FFFFu) >> 4;
+          const uint32_t a_lo = (((smem_a + stage * kAStageBytes) & 0x3FFFFu) >> 4) | (1u << 16);
+          const uint32_t b_lo = (((smem_b + stage * PC::kBHalfBytes) & 0x3FFFFu) >> 4) | (1u << 16);
+          const int sf_left = p.sf_col_tiles - ks * kST;
+          const int k_left = p.k_bytes - ks * kStageKBytes;
+          const int sf_tiles = sf_left > kST ? kST : sf_left;
+          const int n_mma = k_left >= kStageKBytes ? 4 : (k_left + 31) >> 5;
+          if (elected) {
+#pragma unroll
+            for (int t = 0; t < kST; ++t) {
+              if (t < sf_tiles) {
+                tc_cp_sf_pair(tmem_sfa + t * 4, make_desc(sfa_lo + t * 32, kDescHiSf));
+#pragma unroll
+                for (int nb = 0; nb < kNB; ++nb) tc_cp_sf_pair(tmem_sfb + (t * kNB + nb) * 4, make_desc(sfb_lo + (nb * kST + t) * 32, kDescHiSf));
+              }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              if (j < n_mma) {
+                const int t = (FMT == TF_FMT_MXFP8) ? 0 : (FMT == TF_FMT_MXFP4) ? (j >> 1) : j;
+                const uint32_t sf_id = (FMT == TF_FMT_MXFP8) ? (uint32_t)j : (FMT == TF_FMT_MXFP4) ? (uint32_t)((j & 1) * 2) : 0u;
+                tc_mma_pair<FMT>(tmem_acc, make_desc(a_lo + j * 2, kDescHiSw128), make_desc(b_lo + j * 2, kDescHiSw128),
+                                 idesc_base | (sf_id << 4) | (sf_id << 29), tmem_sfa + t * 4, tmem_sfb + t * kNB * 4, (j > 0 || ks > 0) ? 1u : 0u);
+              }
+            }
+            tc_commit_pair(bar_empty + 8 * stage);  // frees the stage in both CTAs
+          }
+          __syncwarp();
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        if (!ok) break;
+        if (elected) tc_commit_pair(bar_tmem_full);  // both CTAs' epilogues may read their accumulator halves
+        __syncwarp();
+        tile_phase ^= 1;
+      }
+    }
+    __syncwarp();
+  } else {
+    // ---------------- epilogue: each CTA drains its own 128 rows; the release goes to the leader's barrier ----------------
+    const int q = warp & 3;
+    const float alpha = (FMT == TF_FMT_NVFP4) ? __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs)) : 1.0f;
+    const uint32_t release = mapa_shared(bar_tmem_empty, 0);
+    uint32_t tile_phase = 0, acc_buf = 0;
+    uint32_t amax2 = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+      const int m_blk = tile % p.m_blocks, n_blk = tile / p.m_blocks;
+      bool ok = mbar_wait(bar_tmem_full, tile_phase, abort_flag, 4);
+      ok = __all_sync(0xFFFFFFFFu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_blk * 256 + (int)rank * 128 + q * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
+      const int col0 = n_blk * kOutCols;
+      if (acc_buf == 0)
+        epilogue_tile<FMT, BLOCK_N, EPI, 0, true>(p, t_row, release, lane, row, col0, alpha, amax2);
+      else
+        epilogue_tile<FMT, BLOCK_N, EPI, 1, true>(p, t_row + Cfg::kAccStride, release, lane, row, col0, alpha, amax2);
+      acc_buf ^= 1;
+      tile_phase ^= 1;
+    }
+    if (p.out_amax) {
+      uint32_t mx = max(amax2 & 0xFFFFu, amax2 >> 16);
+      for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+      if (lane == 0 && mx) atomicMax(p.out_amax, mx << 16);
+    }
+  }
+
+  // ---------------- teardown: nobody leaves while the peer may still touch this CTA's shared or tensor memory ----------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
+  }
+}
+
 // ---- host side -------------------------------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -711,6 +1008,65 @@ static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmP
   return TF_OK;
 }
 
+// The swizzled scale buffer as a [tiles, 128 x u32] matrix: a box is kST consecutive 512-byte tiles, no swizzle.
+static tf_status make_scale_map(CUtensorMap* map, const void* base, int64_t tiles, int box_tiles) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(TF_ERR_CUDA, "tf_gemm_blockscaled: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {128u, (cuuint64_t)tiles};
+  const cuuint64_t strides[1] = {512u};
+  const cuuint32_t box[2] = {128u, (cuuint32_t)box_tiles};
+  const cuuint32_t estr[2] = {1u, 1u};
+  const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(TF_ERR_CUDA, "tf_gemm_blockscaled: cuTensorMapEncodeTiled (scales) failed with CUresult %d", (int)r);
+  return TF_OK;
+}
+
+template <int FMT, int EPI>
+static tf_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, cudaStream_t stream) {
+  using PC = PairCfg<FMT, EPI>;
+  CUtensorMap tsa, tsb;
+  tf_status st = make_scale_map(&tsa, p.sfa, (int64_t)((p.m + 127) / 128) * p.sf_col_tiles, PC::kST);
+  if (st != TF_OK) return st;
+  st = make_scale_map(&tsb, p.sfb, (int64_t)p.sfb_row_tiles * p.sf_col_tiles, PC::kST);
+  if (st != TF_OK) return st;
+  auto kernel = gemm_blockscaled_pair_kernel<FMT, EPI>;
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  TF_CUDA(cudaGetDevice(&dev));
+  if (configured_dev != dev) {
+    TF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, PC::kSmemBytes));
+    configured_dev = dev;
+  }
+  constexpr int out_cols = (EPI == TF_EPI_SILU_GATE) ? 128 : 256;
+  p.m_blocks = (p.m + 255) / 256;
+  p.n_blocks = (p.n + out_cols - 1) / out_cols;
+  p.num_tiles = p.m_blocks * p.n_blocks;
+  int pairs = sm_count() / 2;
+  if (p.num_tiles < pairs) pairs = p.num_tiles;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs);
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = PC::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  TF_CUDA(cudaLaunchKernelEx(&cfg, kernel, ta, tb, tsa, tsb, p));
+  return TF_OK;
+}
+
+// Whether the 2-CTA kernel serves this problem: asked for (TF_GEMM_TWO_CTA=1 in the environment; the one-CTA kernel measured
+// faster on B200 under its power cap and is the default), more than one 128-row block, a full pair tile wide, no split-K.
+static bool use_pair_kernel(const GemmParams& p, const SplitPlan& sp) {
+  static const int enabled = getenv("TF_GEMM_TWO_CTA") ? atoi(getenv("TF_GEMM_TWO_CTA")) : 0;
+  return enabled && sp.splits == 1 && p.m > 128 && p.n_rows_b >= 256;
+}
+
 template <int FMT>
 static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int epilogue, const SplitPlan& sp, cudaStream_t stream) {
   if (sp.splits > 1) {
@@ -735,6 +1091,11 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
       splitk_reduce_kernel<TF_EPI_NONE><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
     TF_LAUNCH_CHECK();
     return TF_OK;
+  }
+  if (use_pair_kernel(p, sp)) {
+    if (epilogue == TF_EPI_SILU_GATE) return launch_gemm_pair<FMT, TF_EPI_SILU_GATE>(ta, tb, p, stream);
+    if (epilogue == TF_EPI_RESIDUAL) return launch_gemm_pair<FMT, TF_EPI_RESIDUAL>(ta, tb, p, stream);
+    return launch_gemm_pair<FMT, TF_EPI_NONE>(ta, tb, p, stream);
   }
   if (epilogue == TF_EPI_SILU_GATE) return launch_gemm<FMT, 256, TF_EPI_SILU_GATE, false>(ta, tb, p, stream);
   if (epilogue == TF_EPI_RESIDUAL)

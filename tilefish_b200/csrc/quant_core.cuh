@@ -70,6 +70,79 @@ __device__ __forceinline__ void quantize_vec8(const uint4& v, float gs, float in
   }
 }
 
+// 16 consecutive bf16 values per thread (one 256-bit load): half the shuffles, scale arithmetic and address arithmetic per element
+// of the 8-value form. A block of 32 is two adjacent lanes; an nvfp4 block of 16 is the thread's own. Same arithmetic, same bytes.
+// codes: 4 words (e4m3) or 2 words (e2m1).
+template <int FMT>
+__device__ __forceinline__ void quantize_vec16(const uint32_t (&w)[8], float gs, float inv_t, uint32_t (&codes)[4], uint32_t& scale) {
+  const uint32_t k = 0x7FFF7FFFu;
+  uint32_t t0 = __vimax3_u16x2(w[0] & k, w[1] & k, w[2] & k);
+  uint32_t t1 = __vimax3_u16x2(w[3] & k, w[4] & k, w[5] & k);
+  t0 = __vimax3_u16x2(t0, w[6] & k, w[7] & k);
+  t0 = __vimax3_u16x2(t0, t1, 0u);
+  uint32_t m = max(t0 & 0xFFFFu, t0 >> 16);
+  if (FMT != TF_FMT_NVFP4) m = max(m, __shfl_xor_sync(0xFFFFFFFFu, m, 1));
+
+  if (FMT == TF_FMT_NVFP4) {
+    const float amax = __uint_as_float(m << 16);
+    uint32_t s8 = 0;
+    if (gs != 0.0f && m != 0) s8 = cvt_e4m3x2(__fmul_rn(amax, inv_t), 0.0f) & 0xFFu;
+    const float d = __fmul_rn(e4m3_to_f32(s8), gs);
+    const bool zero = (d == 0.0f);
+    const float inv = zero ? 0.0f : __frcp_rn(d);
+    scale = s8;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t c = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        c |= cvt_e2m1x2(__fmul_rn(bf16lo_to_f32(w[4 * h + j]), inv), __fmul_rn(bf16hi_to_f32(w[4 * h + j]), inv)) << (8 * j);
+      codes[h] = zero ? 0u : c;
+    }
+    codes[2] = codes[3] = 0;
+    return;
+  }
+  const int emax = (FMT == TF_FMT_MXFP8) ? 8 : 2;
+  const int e = (int)(m >> 7) - emax;
+  scale = (m == 0) ? 127u : (uint32_t)max(e, 0);
+  const uint32_t inv1 = (254u - scale) << 7;
+  const uint32_t inv2 = inv1 | (inv1 << 16);
+  uint32_t q[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) q[j] = mul_bf16x2(w[j], inv2);
+  if (FMT == TF_FMT_MXFP8) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      codes[j] = cvt_e4m3x2(bf16lo_to_f32(q[2 * j]), bf16hi_to_f32(q[2 * j])) | (cvt_e4m3x2(bf16lo_to_f32(q[2 * j + 1]), bf16hi_to_f32(q[2 * j + 1])) << 16);
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      uint32_t c = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) c |= cvt_e2m1x2(bf16lo_to_f32(q[4 * h + j]), bf16hi_to_f32(q[4 * h + j])) << (8 * j);
+      codes[h] = c;
+    }
+    codes[2] = codes[3] = 0;
+  }
+}
+
+// Stores the codes of 16 elements (vector index `vec` of 16-element vectors in row `row`) and the block's scale byte.
+template <int FMT>
+__device__ __forceinline__ void store_quantized16(uint8_t* __restrict__ codes_out, uint8_t* __restrict__ scales, int swizzled, int64_t row, int vec,
+                                                  int64_t k, const uint32_t (&codes)[4], uint32_t scale) {
+  if (FMT == TF_FMT_MXFP8) {
+    *reinterpret_cast<uint4*>(codes_out + row * k + (int64_t)vec * 16) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+  } else {
+    *reinterpret_cast<uint2*>(codes_out + row * (k >> 1) + (int64_t)vec * 8) = make_uint2(codes[0], codes[1]);
+  }
+  if (FMT == TF_FMT_NVFP4 || (vec & 1) == 0) {
+    const int64_t cols = k / (FMT == TF_FMT_NVFP4 ? 16 : 32);
+    const int64_t c = (FMT == TF_FMT_NVFP4) ? vec : (vec >> 1);
+    const int64_t off = swizzled ? swizzled_scale_offset(row, c, (cols + 3) >> 2) : row * cols + c;
+    scales[off] = (uint8_t)scale;
+  }
+}
+
 // Stores one thread's codes (8 elements starting at element column `col` of row `row`) and, from the first lane of each
 // block, the scale byte. `vec` is the index of the 8-element vector inside the row.
 template <int FMT>

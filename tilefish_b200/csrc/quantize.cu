@@ -1,23 +1,30 @@
 // BlockScaled quantization row kernels (bf16 -> MXFP8 / MXFP4 / NVFP4) and the scale-layout helpers.
 //
-// HBM-bound: every thread moves one 128-bit vector of 8 bf16 per step (coalesced: consecutive lanes, consecutive
-// vectors), block maxima are combined with warp shuffles, codes leave as 8-byte (e4m3) or 4-byte (e2m1) coalesced
-// stores. Algorithmic bytes per element: 2 + 1 + 1/32 (mxfp8), 2 + 0.5 + 1/32 (mxfp4), 2 + 0.5 + 1/16 (nvfp4).
+// HBM-bound: every thread moves one 256-bit vector of 16 bf16 per step (coalesced: consecutive lanes, consecutive
+// vectors), block maxima are combined with at most one warp shuffle, codes leave as 16-byte (e4m3) or 8-byte (e2m1)
+// coalesced stores. Algorithmic bytes per element: 2 + 1 + 1/32 (mxfp8), 2 + 0.5 + 1/32 (mxfp4), 2 + 0.5 + 1/16 (nvfp4).
 #include "quant_core.cuh"
 
 namespace tf {
 
 constexpr int kQuantThreads = 256;
-constexpr int kQuantUnroll = 4;
+constexpr int kQuantUnroll = 2;
 
 // Block = (TPR threads along the row) x (256 / TPR rows); rows are taken grid-stride.
+__device__ __forceinline__ void load_256(const void* p, uint32_t (&w)[8]) {
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(p));
+}
+
 // gs_ptr holds the nvfp4 global scale, or (gs_out != nullptr) the tensor's amax from which it is derived here.
+// One thread = 16 consecutive bf16 (one 256-bit load); block = (TPR threads along the row) x (256 / TPR rows).
 template <int FMT>
-__global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint4* __restrict__ x, int64_t m, int64_t k, int64_t ldx_vec,
+__global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint8_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
                                                                       uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
                                                                       int swizzled, const float* __restrict__ gs_ptr, float* __restrict__ gs_out) {
   const int tpr = blockDim.x;
-  const int nvec = (int)(k >> 3);
+  const int nvec = (int)(k >> 4);
   float gs = (FMT == TF_FMT_NVFP4) ? __ldg(gs_ptr) : 0.0f;
   if (FMT == TF_FMT_NVFP4 && gs_out != nullptr) {
     gs = __fdiv_rn(gs, 2688.0f);
@@ -25,28 +32,33 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
   }
   const float inv_t = (FMT == TF_FMT_NVFP4 && gs != 0.0f) ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
   const int64_t row_stride = (int64_t)gridDim.x * blockDim.y;
-  // Both loops run the same number of times for every thread of the block, so the warp shuffles inside quantize_vec8 always
-  // see whole warps; threads without data (row >= m or vector >= nvec) quantize zeros and store nothing. nvec is a
-  // multiple of 4 and tpr a power of two >= 4, so the lanes of one scale block have data together.
+  // Both loops run the same number of times for every thread of the block, so the warp shuffle inside quantize_vec16 always
+  // sees whole warps; threads without data (row >= m or vector >= nvec) quantize zeros and store nothing. nvec is even and
+  // tpr a power of two >= 2, so the two lanes of one 32-element block have data together.
   for (int64_t row_base = (int64_t)blockIdx.x * blockDim.y; row_base < m; row_base += row_stride) {
     const int64_t row = row_base + threadIdx.y;
     const bool row_ok = row < m;
-    const uint4* xr = x + (row_ok ? row : 0) * ldx_vec;
-    for (int base = 0; base < nvec; base += kQuantUnroll * tpr) {  // kQuantUnroll 128-bit loads in flight per thread
-      uint4 v[kQuantUnroll];
+    const uint8_t* xr = x + (row_ok ? row : 0) * ldx * 2;
+    for (int base = 0; base < nvec; base += kQuantUnroll * tpr) {  // kQuantUnroll 256-bit loads in flight per thread
+      uint32_t v[kQuantUnroll][8];
       bool has[kQuantUnroll];
 #pragma unroll
       for (int j = 0; j < kQuantUnroll; ++j) {
         const int vj = base + threadIdx.x + j * tpr;
         has[j] = row_ok && vj < nvec;
-        v[j] = has[j] ? __ldcs(xr + vj) : make_uint4(0, 0, 0, 0);
+        if (has[j]) {
+          load_256(xr + (int64_t)vj * 32, v[j]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[j][e] = 0;
+        }
       }
 #pragma unroll
       for (int j = 0; j < kQuantUnroll; ++j) {
         if (base + j * tpr < nvec) {  // uniform over the block
-          uint32_t c0, c1, sc;
-          quantize_vec8<FMT>(v[j], gs, inv_t, c0, c1, sc);
-          if (has[j]) store_quantized<FMT>(codes, scales, swizzled, row, base + threadIdx.x + j * tpr, k, c0, c1, sc);
+          uint32_t c[4], sc;
+          quantize_vec16<FMT>(v[j], gs, inv_t, c, sc);
+          if (has[j]) store_quantized16<FMT>(codes, scales, swizzled, row, base + threadIdx.x + j * tpr, k, c, sc);
         }
       }
     }
@@ -113,6 +125,7 @@ static tf_status check_quant_args(const char* fn, const void* x, int64_t m, int6
   if (ldx < k || ldx % 8 != 0) return fail(TF_ERR_ALIGNMENT, "%s: ldx=%lld must be >= k and a multiple of 8", fn, (long long)ldx);
   if (k > (int64_t)1 << 30) return fail(TF_ERR_UNSUPPORTED, "%s: k too large", fn);
   if ((uintptr_t)x % 16 || (uintptr_t)codes % 16) return fail(TF_ERR_ALIGNMENT, "%s: x and codes must be 16-byte aligned", fn);
+  if ((uintptr_t)x % 32 || ldx % 16) return fail(TF_ERR_ALIGNMENT, "%s: x must be 32-byte aligned with ldx a multiple of 16 (256-bit loads)", fn);
   return TF_OK;
 }
 
@@ -126,14 +139,14 @@ static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64
   const int64_t cols = k / block_of(FMT);
   if (layout == TF_SCALES_SWIZZLED && ((m & 127) || (cols & 3)))
     TF_CUDA(cudaMemsetAsync(scales, 0, (size_t)tf_scale_bytes(FMT, m, k, layout), stream));
-  int tpr = 4;
-  while (tpr < kQuantThreads && tpr * kQuantUnroll < (k >> 3)) tpr <<= 1;
+  int tpr = 2;
+  while (tpr < kQuantThreads && tpr * kQuantUnroll < (k >> 4)) tpr <<= 1;
   const int rpb = kQuantThreads / tpr;
   const int64_t blocks_needed = (m + rpb - 1) / rpb;
   const int64_t cap = (int64_t)sm_count() * 8;
   dim3 block(tpr, rpb);
   dim3 grid((unsigned)(blocks_needed < cap ? blocks_needed : cap));
-  quantize_rows_kernel<FMT><<<grid, block, 0, stream>>>(static_cast<const uint4*>(x), m, k, ldx >> 3, static_cast<uint8_t*>(codes),
+  quantize_rows_kernel<FMT><<<grid, block, 0, stream>>>(static_cast<const uint8_t*>(x), m, k, ldx, static_cast<uint8_t*>(codes),
                                                         static_cast<uint8_t*>(scales), layout == TF_SCALES_SWIZZLED, gs, gs_out);
   TF_LAUNCH_CHECK();
   return TF_OK;

@@ -124,8 +124,9 @@ def quantize(x, fmt: str, *, layout: str = "swizzled", global_scale=None, amax=N
     _pre(layout in ("swizzled", "plain"), f"unknown scale layout {layout!r}", "argument", "layout")
     _check(x, "x", torch.bfloat16, 2)
     m, k = x.shape
-    _pre(x.stride(1) == 1 and (m <= 1 or (x.stride(0) >= k and x.stride(0) % 8 == 0)), "x: rows must be dense with a row stride that is a multiple of 8", "contiguous", "x")
+    _pre(x.stride(1) == 1 and (m <= 1 or (x.stride(0) >= k and x.stride(0) % 16 == 0)), "x: rows must be dense with a row stride that is a multiple of 16", "contiguous", "x")
     _pre(k % 32 == 0 and k > 0, f"x: K={k} is not a multiple of 32", "divisible", "x")
+    _pre(m == 0 or x.data_ptr() % 32 == 0, "x: the data pointer is not 32-byte aligned (the quantizer uses 256-bit loads)", "pointer_alignment", "x")
     ldx = x.stride(0) if m > 1 else k
     lay = N.SCALES_SWIZZLED if layout == "swizzled" else N.SCALES_PLAIN
     if out is not None:  # preallocated result (a plan's arena): same format, shape and layout
