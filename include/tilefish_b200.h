@@ -70,6 +70,16 @@ TF_API const char* tf_last_error(void);
  * SYNCHRONIZES the device. *status is TF_OK or TF_ERR_DEVICE_TIMEOUT; *detail identifies the wait that gave up. */
 TF_API tf_status tf_device_status(int32_t* status, int32_t* detail);
 
+/* Process-wide: the persistent GEMM launches on (SM count - sms) SMs from now on, so that a collective running beside it in
+ * another stream (the tensor-parallel MLP overlaps one row chunk's all-reduce with the other chunk's GEMMs) finds free SMs.
+ * 0 restores the default. No counterpart in the reference (its GEMM is cuBLASLt's `sm_count_target`, python/src/tilefish/_cublaslt.py). */
+TF_API tf_status tf_set_sm_margin(int32_t sms);
+
+/* Failure-detection self-test (no counterpart in the reference): launches one thread that waits on a barrier nothing will ever
+ * signal, with the given limit. The wait gives up, records TF_ERR_DEVICE_TIMEOUT (detail 9 * 65536) in the device status word
+ * and the kernel returns normally; the context stays usable. Exercises the mechanism every wait of the GEMM relies on. */
+TF_API tf_status tf_selftest_bounded_wait(int32_t limit_ms, void* stream);
+
 /* Bytes of the scale tensor of a [rows, k] operand in `format`, in `layout`. Returns -1 on a bad argument. */
 TF_API int64_t tf_scale_bytes(int32_t format, int64_t rows, int64_t k, int32_t layout);
 

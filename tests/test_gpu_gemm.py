@@ -231,3 +231,22 @@ torch.save(outs, sys.argv[1])
     w = O.randn((1536, 2560), 2, torch.bfloat16, scale=2560**-0.5)
     for fmt in ("mxfp8", "nvfp4"):
         assert_gemm_close(results["1"][fmt], O.f32_to_bf16(oracle_acc(a, w, fmt)), f"two-CTA {fmt}")
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_context_survives(K):
+    """Failure detection without a fault: a kernel waits (with a 20 ms limit) on a barrier nothing signals. It must return by
+    itself, leave TF_ERR_DEVICE_TIMEOUT in the device status word, and the next GEMM on the same context must be correct."""
+    import time
+
+    from tilefish_b200 import _native as N
+
+    assert N.device_status() == (0, 0)
+    t0 = time.perf_counter()
+    N.check(N.load().tf_selftest_bounded_wait(20, torch.cuda.current_stream().cuda_stream), "tf_selftest_bounded_wait")
+    status, detail = N.device_status()  # synchronizes
+    assert time.perf_counter() - t0 < 1.0
+    assert status == N.TF_ERR_DEVICE_TIMEOUT and detail >> 16 == 9
+    assert N.device_status() == (0, 0), "reading the status clears it"
+    a, w = operands(64, 256, 256, seed=2)
+    out = K.gemm_blockscaled(K.quantize(a.cuda(), "mxfp8"), K.quantize(w.cuda(), "mxfp8"))
+    assert_gemm_close(out.cpu(), O.f32_to_bf16(oracle_acc(a, w, "mxfp8")), "after a timeout")

@@ -35,6 +35,8 @@ SIGNATURES = {
     "tf_version": (c_char_p, []),
     "tf_last_error": (c_char_p, []),
     "tf_device_status": (c_int32, [ctypes.POINTER(c_int32), ctypes.POINTER(c_int32)]),
+    "tf_selftest_bounded_wait": (c_int32, [c_int32, _P]),
+    "tf_set_sm_margin": (c_int32, [c_int32]),
     "tf_scale_bytes": (c_int64, [c_int32, c_int64, c_int64, c_int32]),
     "tf_quantize_mxfp8": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P, c_int32, _P]),
     "tf_quantize_mxfp4": (c_int32, [_P, c_int64, c_int64, c_int64, _P, _P, c_int32, _P]),

@@ -179,14 +179,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 // Bounded wait. Returns false when the limit ran out here or another role already gave up (abort flag).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
+                                          unsigned long long limit_ns = kWaitLimitNs) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t spins = 1;; ++spins) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spins & 0x3F) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *abort_flag = 1;
         if (atomicCAS(&g_device_status[0], 0, TF_ERR_DEVICE_TIMEOUT) == 0) g_device_status[1] = where * 65536 + (int)blockIdx.x;
         return false;
@@ -265,6 +266,19 @@ __device__ __forceinline__ bool elect_one() {
   return pred != 0;
 }
 
+
+// Self-test of the bounded wait: one thread waits on an mbarrier that nothing arrives at; the wait must give up after limit_ns,
+// record TF_ERR_DEVICE_TIMEOUT (detail: wait 9) and return, leaving the context usable.
+__global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns) {
+  __shared__ __align__(8) unsigned long long bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    (void)mbar_wait(smem_u32(&bar), 0, &abort_flag, 9, limit_ns);
+  }
+}
 
 // ---- epilogue helpers ------------------------------------------------------------------------------------------------------
 // Stores 32 consecutive bf16 outputs of one row (packed two per word) and applies the residual / amax side effects.
@@ -956,6 +970,13 @@ static tf_status make_operand_map(CUtensorMap* map, const void* base, int64_t ro
   return TF_OK;
 }
 
+// SMs the persistent GEMM leaves free (for a collective running beside it in another stream).
+static int g_sm_margin = 0;
+static int gemm_sms() {
+  const int n = sm_count() - g_sm_margin;
+  return n < 2 ? 2 : n;
+}
+
 // Split-K plan of a problem: how many K ranges each output tile is cut into, so that small-M problems (few tiles, long K: the
 // weight-streaming regime) still occupy every SM. Depends only on the sizes and the SM count: the workspace query and the launch
 // agree by construction.
@@ -1002,7 +1023,7 @@ static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmP
   constexpr int out_cols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;
   p.n_blocks = (p.n + out_cols - 1) / out_cols;
   p.num_tiles = p.m_blocks * p.n_blocks * p.splits;
-  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  const int grid = p.num_tiles < gemm_sms() ? p.num_tiles : gemm_sms();
   kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
   TF_LAUNCH_CHECK();
   return TF_OK;
@@ -1042,7 +1063,7 @@ static tf_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, 
   p.m_blocks = (p.m + 255) / 256;
   p.n_blocks = (p.n + out_cols - 1) / out_cols;
   p.num_tiles = p.m_blocks * p.n_blocks;
-  int pairs = sm_count() / 2;
+  int pairs = gemm_sms() / 2;
   if (p.num_tiles < pairs) pairs = p.num_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
@@ -1126,6 +1147,21 @@ tf_status tf_device_status(int32_t* status, int32_t* detail) {
   }
   *status = host[0];
   if (detail) *detail = host[1];
+  return TF_OK;
+}
+
+tf_status tf_set_sm_margin(int32_t sms) {
+  clear_error();
+  TF_CHECK_ARG(sms >= 0 && sms <= 64, "%s: the margin must be in 0..64", __func__);
+  g_sm_margin = sms;
+  return TF_OK;
+}
+
+tf_status tf_selftest_bounded_wait(int32_t limit_ms, void* stream) {
+  clear_error();
+  TF_CHECK_ARG(limit_ms > 0 && limit_ms <= 2000, "%s: limit_ms must be in 1..2000", __func__);
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ms * 1000000ull);
+  TF_LAUNCH_CHECK();
   return TF_OK;
 }
 

@@ -65,31 +65,40 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
   }
 }
 
-__global__ void __launch_bounds__(256) amax_bits_kernel(const uint4* __restrict__ x, int64_t m, int nvec, int64_t ldx_vec,
+// max |x| over the tensor as the f32 bit pattern of a bf16 magnitude: 256-bit loads, four in flight per thread.
+__global__ void __launch_bounds__(256) amax_bits_kernel(const uint8_t* __restrict__ x, int64_t m, int nvec, int64_t ldx,
                                                         unsigned int* __restrict__ out_bits) {
-  uint32_t mx = 0;
+  const uint32_t k = 0x7FFF7FFFu;
+  uint32_t acc = 0;  // two packed 16-bit maxima
   const int64_t total = m * nvec;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  const bool dense = ldx_vec == nvec;
-  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {  // four loads in flight
-    uint4 v[4];
+  const bool dense = ldx == (int64_t)nvec * 16;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+    uint32_t v[4][8];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int64_t i = i0 + j * stride;
       if (i < total) {
-        int64_t off = i;
+        int64_t off = i * 32;
         if (!dense) {
           const int64_t row = i / nvec;
-          off = row * ldx_vec + (i - row * nvec);
+          off = (row * ldx + (i - row * nvec) * 16) * 2;
         }
-        v[j] = __ldcs(x + off);
+        load_256(x + off, v[j]);
       } else {
-        v[j] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) v[j][e] = 0;
       }
     }
 #pragma unroll
-    for (int j = 0; j < 4; ++j) mx = max(mx, amax_bits8(v[j]));
+    for (int j = 0; j < 4; ++j) {
+      uint32_t t0 = __vimax3_u16x2(v[j][0] & k, v[j][1] & k, v[j][2] & k);
+      uint32_t t1 = __vimax3_u16x2(v[j][3] & k, v[j][4] & k, v[j][5] & k);
+      t0 = __vimax3_u16x2(t0, v[j][6] & k, v[j][7] & k);
+      acc = __vimax3_u16x2(acc, t0, t1);
+    }
   }
+  uint32_t mx = max(acc & 0xFFFFu, acc >> 16);
   for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
   __shared__ uint32_t warp_max[8];
   if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = mx;
@@ -199,13 +208,13 @@ tf_status tf_nvfp4_global_scale(const void* x, int64_t m, int64_t k, int64_t ldx
   clear_error();
   cudaStream_t stream = (cudaStream_t)stream_;
   TF_CHECK_ARG(x && out, "%s: null pointer", __func__);
-  TF_CHECK_ARG(m >= 0 && k > 0 && k % 8 == 0 && ldx >= k && ldx % 8 == 0, "%s: bad shape", __func__);
-  TF_CHECK_ALIGNED(x, 16, "x");
+  TF_CHECK_ARG(m >= 0 && k > 0 && k % 16 == 0 && ldx >= k && ldx % 16 == 0, "%s: bad shape (k and ldx must be multiples of 16)", __func__);
+  TF_CHECK_ALIGNED(x, 32, "x");
   TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float), stream));
   if (m > 0) {
-    const int64_t total = m * (k >> 3);
-    const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
-    amax_bits_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, stream>>>(static_cast<const uint4*>(x), m, (int)(k >> 3), ldx >> 3,
+    const int64_t total = m * (k >> 4);
+    const int64_t need = (total + 1023) / 1024, cap = (int64_t)sm_count() * 8;
+    amax_bits_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, stream>>>(static_cast<const uint8_t*>(x), m, (int)(k >> 4), ldx,
                                                                               reinterpret_cast<unsigned int*>(out));
     TF_LAUNCH_CHECK();
   }

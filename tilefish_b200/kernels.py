@@ -104,7 +104,8 @@ def nvfp4_global_scale(x, *, out=None, stream=None):
     """float32 [1] on the device: max|x| / 2688, computed in stream order."""
     torch = _torch()
     _check(x, "x", torch.bfloat16, 2)
-    _pre(x.stride(1) == 1 and x.stride(0) % 8 == 0, "x: rows must be dense with a row stride that is a multiple of 8", "contiguous", "x")
+    _pre(x.stride(1) == 1 and x.stride(0) % 16 == 0 and x.shape[1] % 16 == 0, "x: rows must be dense, K and the row stride multiples of 16", "contiguous", "x")
+    _pre(x.numel() == 0 or x.data_ptr() % 32 == 0, "x: the data pointer is not 32-byte aligned", "pointer_alignment", "x")
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=x.device)
     m, k = x.shape

@@ -103,20 +103,91 @@ def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, 
 
 class MlpStack:
     """``layers`` decoder blocks applied in sequence: the output of block l is the ``x`` of block l + 1, the f32 residual
-    stream is carried in place."""
+    stream is carried in place.
 
-    def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None) -> None:
+    ``chunks`` > 1 (tensor parallel only) cuts the rows into that many independent chunks, each on its own CUDA stream: rows
+    never interact in this stack, so while one chunk's partial results are in the all-reduce, the other chunk's GEMMs run.
+    The GEMMs then leave ``sm_margin`` SMs free for the collective's kernel. Every chunk is its own tensor for the nvfp4
+    global scales.
+    """
+
+    def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16) -> None:
         self.layers = layers
         self.eps = eps
         self.group = group
-        self._scratch: dict = {}
+        self.chunks = chunks if group is not None else 1
+        self.sm_margin = sm_margin
+        self._scratch: List[dict] = [{} for _ in range(max(1, self.chunks))]
+        self._streams = None
 
     def forward(self, x, residual):
-        for w in self.layers:
-            x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch)
-        return x
+        if self.chunks <= 1:
+            for w in self.layers:
+                x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
+            return x
+        return self._forward_chunked(x, residual)
+
+    def _forward_chunked(self, x, residual):
+        import torch
+
+        from . import _native as N
+
+        m = x.shape[0]
+        c = self.chunks
+        bounds = [((m * i // c) + 127) // 128 * 128 if 0 < i < c else m * i // c for i in range(c + 1)]
+        bounds = [min(b, m) for b in bounds]
+        spans = [(bounds[i], bounds[i + 1]) for i in range(c) if bounds[i + 1] > bounds[i]]
+        if len(spans) < 2:
+            for w in self.layers:
+                x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
+            return x
+        if self._streams is None or len(self._streams) < len(spans):
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in spans]
+        main = torch.cuda.current_stream()
+        out = torch.empty_like(x)
+        N.check(N.load().tf_set_sm_margin(self.sm_margin), "tf_set_sm_margin")
+        try:
+            xs = [x[a:b] for a, b in spans]
+            rs = [residual[a:b] for a, b in spans]
+            for s in self._streams[:len(spans)]:
+                s.wait_stream(main)
+            last = len(self.layers) - 1
+            for li, w in enumerate(self.layers):
+                for ci, (a, b) in enumerate(spans):
+                    with torch.cuda.stream(self._streams[ci]):
+                        xs[ci] = decoder_block(xs[ci], rs[ci], w, self.eps, group=self.group, scratch=self._scratch[ci], out=out[a:b] if li == last else None)
+            for s in self._streams[:len(spans)]:
+                main.wait_stream(s)
+        finally:
+            N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
+        return out
 
     __call__ = forward
 
+    def capture(self, x, residual):
+        """Captures one ``forward(x, residual)`` into a CUDA graph (after one eager warm-up run, which also sets the kernels'
+        attributes). ``x`` and ``residual`` are the graph's fixed input buffers: write new inputs into them, then
+        ``replay()``. With tensor parallelism the all-reduces and both row-chunk streams are part of the graph, so a step
+        costs one launch on the host: at 4-8 GPUs the per-layer kernels are too short for Python to keep up otherwise."""
+        import torch
+
+        self.forward(x, residual)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            out = self.forward(x, residual)
+        return CapturedStack(graph, x, residual, out)
+
     def weight_bytes(self) -> int:
         return sum(w.nbytes() for w in self.layers)
+
+
+class CapturedStack:
+    """A captured ``MlpStack.forward``: ``replay()`` relaunches it over the captured ``x`` / ``residual`` buffers and returns ``out``."""
+
+    def __init__(self, graph, x, residual, out) -> None:
+        self.graph, self.x, self.residual, self.out = graph, x, residual, out
+
+    def replay(self):
+        self.graph.replay()
+        return self.out
