@@ -95,3 +95,38 @@ def test_sharded_weights_hold_the_bytes_of_the_full_weights():
         else:
             rel = float((y_tp - y_full.float()).norm() / y_full.float().norm())
             assert rel <= 0.08, (fmt, rel)
+
+
+def test_row_chunks_and_graph_capture_reproduce_the_plain_stack(tmp_path):
+    """The multi-GPU machinery on one rank (an NCCL group of size 1): two row chunks on two streams with the all-reduce in
+    between, and the same step captured into a CUDA graph. MXFP8 quantization is per 32-element block of a row, so cutting the
+    rows into chunks must not change a single byte."""
+    import torch.distributed as dist
+
+    from tilefish_b200 import mlp as MLP
+
+    if not dist.is_initialized():
+        dist.init_process_group("nccl", init_method=f"file://{tmp_path}/pg", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    try:
+        m, h, f = 512, 256, 384
+        layers = []
+        for i in range(3):
+            _, _, w_n, w_gu, w_d = make(m, h, f, seed=20 * i)
+            layers.append(MLP.quantize_weights(w_n.cuda(), w_gu.cuda(), w_d.cuda(), "mxfp8"))
+        x = O.randn((m, h), 5, torch.bfloat16).cuda()
+        res0 = O.randn((m, h), 6).cuda()
+        r_plain = res0.clone()
+        y_plain = MLP.MlpStack(layers)(x, r_plain)
+        stack = MLP.MlpStack(layers, group=dist.group.WORLD, chunks=2)
+        r_chunk = res0.clone()
+        y_chunk = stack(x, r_chunk)
+        torch.cuda.synchronize()
+        assert torch.equal(y_chunk, y_plain) and torch.equal(r_chunk, r_plain)
+        xg, rg = x.clone(), res0.clone()
+        cap = stack.capture(xg, rg)
+        rg.copy_(res0)
+        y_graph = cap.replay()
+        torch.cuda.synchronize()
+        assert torch.equal(y_graph, y_plain) and torch.equal(rg, r_plain)
+    finally:
+        pass  # the process group is left to the interpreter: destroying it after a graph captured its collectives blocks
