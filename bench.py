@@ -189,6 +189,17 @@ def extras(torch, K, pk):
         out["quantize"][fmt] = {"GBps": round(gbs, 1), "us": round(ms * 1e3, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 3), "shape": [m, k]}
     ms = event_ms(lambda: K.nvfp4_global_scale(x, out=gs), 10, torch, flush)
     out["quantize"]["nvfp4_amax_pass"] = {"GBps": round(m * k * 2 / ms / 1e6, 1), "us": round(ms * 1e3, 1)}
+    out["quantize"]["sweep"] = {}
+    for ms_rows in (1, 128, 8192):  # the smaller points of the sweep: launch-latency bound up to M = 128
+        xs = x[:ms_rows]
+        row = {}
+        for fmt, bpe in (("mxfp8", 2 + 1 + 1 / 32), ("mxfp4", 2 + 0.5 + 1 / 32), ("nvfp4", 2 + 0.5 + 1 / 16)):
+            fn = (lambda f=fmt: K.quantize(xs, f, global_scale=gs if f == "nvfp4" else None))
+            for _ in range(3):
+                fn()
+            t = event_ms(fn, 10, torch, flush if ms_rows >= 8192 else None)
+            row[fmt] = {"us": round(t * 1e3, 1), "GBps": round(ms_rows * k * bpe / t / 1e6, 1)}
+        out["quantize"]["sweep"][f"M={ms_rows}"] = row
     del x
     m, n, k = 4096, 6144, 2560
     a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
@@ -211,6 +222,29 @@ def extras(torch, K, pk):
         ms = s.elapsed_time(e) / iters
         tf = 2 * m * n * k / ms / 1e9
         ms_q = event_ms(lambda: K.quantize(a, fmt), 5, torch)
+        small = {}
+        for sm_rows in (1, 16, 128):  # weight-streaming regime: report time and the rate the weights are read at
+            qs = K.quantize(a[:sm_rows], fmt)
+            os_ = torch.empty((sm_rows, n), dtype=torch.bfloat16, device="cuda")
+            need = K.gemm_workspace_bytes(sm_rows, n, k, fmt)
+            ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
+            gfn = (lambda: K.gemm_blockscaled(qs, qb, out=os_, workspace=ws))
+            for _ in range(3):
+                gfn()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(20):
+                    gfn()
+            gr.replay()
+            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            s2.record()
+            gr.replay()
+            e2.record()
+            e2.synchronize()
+            us = s2.elapsed_time(e2) / 20 * 1e3
+            small[f"M={sm_rows}"] = {"us": round(us, 2), "weights_GBps": round(qb.nbytes() / us / 1e3, 1), "TFLOPs": round(2 * sm_rows * n * k / us / 1e6, 2)}
+        out["gemm"][fmt + "_small_m"] = small
         out["gemm"][fmt] = {"TFLOPs": round(tf, 1), "us": round(ms * 1e3, 1), "a_quantize_us": round(ms_q * 1e3, 1), "shape": [m, n, k],
                             "frac_of_peak": round(tf / (mult * pk["bf16_tflops"]), 3), "peak": f"{mult} x bf16 burst {pk['bf16_tflops']} ({pk['source']})",
                             "frac_of_nominal": round(tf / (2250.0 * mult), 3)}
@@ -290,7 +324,7 @@ def extras_mlp(torch, K, pk):
             roof = max(6 * 2560 * 3072 * m / (2 * pk["bf16_tflops"] * 1e12), weight_bytes / (pk["hbm_gbs"] * 1e9)) * 1e6
             out["readme_block_mxfp8"][f"M={m}"] = {"tokens_per_s": round(m / us * 1e6, 1), "us_per_step": round(us, 2), "roofline_us": round(roof, 2),
                                                    "frac_of_roofline": round(roof / us, 3)}
-        out["readme_block_mxfp8"]["note"] = ("exported plan replayed as one captured CUDA graph (4 launches: rmsnorm+quantize, gemm+SiLU gate, quantize, gemm); "
+        out["readme_block_mxfp8"]["note"] = ("exported plan replayed as one captured CUDA graph (3 launches: rmsnorm+quantize, gemm+SiLU gate+quantize, gemm); "
                                              "roofline = max(6HF*M / (2 x bf16 burst), weight bytes / HBM peak)")
     # decode: M = 64 through the 70B-shaped stack (4 layers timed)
     layers = []

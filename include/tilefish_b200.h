@@ -135,12 +135,15 @@ TF_API tf_status tf_silu_gate(const void* gate, const void* up, int64_t m, int64
  *   epilogue TF_EPI_*: with TF_EPI_SILU_GATE b has 2n rows (n % 128 == 0); with TF_EPI_RESIDUAL epilogue_arg is the f32
  *            residual [m, n] (dense)
  *   out_amax NULL, or a device f32 the caller zeroed: max(|out|) is combined into it with an atomic max
+ *   q_codes, q_scales   NULL, or (MX formats, n % 32 == 0, not with TF_EPI_RESIDUAL) the output is ALSO quantized, in the operands'
+ *            format, exactly as tf_quantize_* would quantize `out` (every epilogue thread holds whole 32-element blocks):
+ *            codes [m, n] or [m, n/2], swizzled scales. `out` may then be NULL (the bf16 copy is not written)
  *   workspace / workspace_bytes   at least tf_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when 0) */
 TF_API int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue);
 TF_API tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
                               const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
-                              int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* workspace,
-                              int64_t workspace_bytes, void* stream);
+                              int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales,
+                              void* workspace, int64_t workspace_bytes, void* stream);
 
 /* The same GEMM for callers that cannot hand over a workspace. (No counterpart in the reference.)
  *

@@ -250,3 +250,24 @@ def test_a_wait_that_runs_out_is_reported_and_the_context_survives(K):
     a, w = operands(64, 256, 256, seed=2)
     out = K.gemm_blockscaled(K.quantize(a.cuda(), "mxfp8"), K.quantize(w.cuda(), "mxfp8"))
     assert_gemm_close(out.cpu(), O.f32_to_bf16(oracle_acc(a, w, "mxfp8")), "after a timeout")
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "mxfp4"])
+@pytest.mark.parametrize("m,n,k,epi", [(256, 512, 512, "none"), (300, 384, 2560, "silu_gate"), (130, 288, 288, "none"), (32, 1536, 2560, "silu_gate"),
+                                       (16, 1024, 4096, "none")])
+def test_gemm_quantized_output_equals_quantize_of_the_bf16_output(K, fmt, m, n, k, epi):
+    """The epilogue's own MX quantization (one 32-element block per thread) against the quantizer kernel on the same bf16
+    result: codes and swizzled scale bytes (padding included) identical, with and without the bf16 copy, one-pass and split-K."""
+    rows_b = 2 * n if epi == "silu_gate" else n
+    a, w = operands(m, rows_b, k, seed=m * 3 + n)
+    qa, qb = K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt)
+    out, q = K.gemm_blockscaled(qa, qb, epilogue=epi, quantize_out=True)
+    plain = K.gemm_blockscaled(qa, qb, epilogue=epi)
+    assert torch.equal(out, plain)
+    ref = K.quantize(plain, fmt)
+    assert torch.equal(q.codes, ref.codes) and torch.equal(q.scales, ref.scales)
+    none, q2 = K.gemm_blockscaled(qa, qb, epilogue=epi, quantize_out=True, want_bf16=False)
+    assert none is None and torch.equal(q2.codes, ref.codes) and torch.equal(q2.scales, ref.scales)
+    codes, scales, _ = O.quantize(plain.cpu(), fmt)
+    assert torch.equal(q.codes.cpu(), codes) and torch.equal(q.scales.cpu(), O.swizzle_scales(scales))
+    no_device_timeout()

@@ -61,6 +61,13 @@ def test_quantize_is_bit_exact(K, fmt, m, k):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
+def test_quantize_sweep_point_8192_is_bit_exact(K, fmt):
+    """M = 8192, K = 4096 with 1 % outliers x100 (a point of the quantize sweep), every byte compared with the oracle."""
+    x = O.outlier_input(8192, 4096, seed=0)
+    check_quant(K, x, fmt, "swizzled")
+
+
+@pytest.mark.parametrize("fmt", FMTS)
 def test_quantize_adversarial_values(K, fmt):
     x = adversarial(64, 512, seed=11)
     if fmt == "nvfp4":

@@ -177,10 +177,12 @@ def test_plan_of_the_decoder_block():
     p = tilefish.plan(block)
     doc = p.doc
     assert doc["schema"] == "tilefish.plan.v1" and doc["arena_alignment"] == 256 and sorted(doc["buckets"]) == ["M=1", "M=32", "M=512"]
-    assert [s["entry"] for s in doc["steps"]] == ["rms", "gemm_gu", "quantize.mxfp8", "gemm_d"]
-    assert [s["kind"] for s in doc["steps"]] == ["kernel", "library", "kernel", "library"]
-    assert doc["steps"][1]["attrs"] == {"format": "mxfp8", "epilogue": "silu_gate", "impl": "sm100.gemm_blockscaled"}
+    # three launches: both activation quantizations are done by the kernels that produce the activations
+    assert [s["entry"] for s in doc["steps"]] == ["rms", "gemm_gu", "gemm_d"]
+    assert [s["kind"] for s in doc["steps"]] == ["kernel", "library", "library"]
+    assert doc["steps"][1]["attrs"] == {"format": "mxfp8", "epilogue": "silu_gate", "impl": "sm100.gemm_blockscaled", "q_format": "mxfp8"}
     assert doc["steps"][0]["attrs"]["q_format"] == "mxfp8" and "out" not in doc["steps"][0]["args"]  # rmsnorm emits the quantized copy only
+    assert "out" not in doc["steps"][1]["args"] and doc["steps"][2]["args"]["a"] == doc["steps"][1]["args"]["q"]  # `a` never exists in bf16
     roles = {b["name"]: b["role"] for b in doc["buffers"]}
     assert roles["x"] == "input" and roles["residual"] == "inout" and roles["w_gu"] == "weight" and roles["out0"] == "output"
     b32 = doc["buckets"]["M=32"]

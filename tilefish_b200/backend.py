@@ -186,7 +186,9 @@ def compile_graph(op: GraphOp, fuse: bool = True) -> Tuple[List[Buffer], List[St
         buffers.append(Buffer(nm, "intermediate", qtype, fmt))
         src = producer_step.get(v)
         single_use = len(users.get(v, [])) == 1 and v not in g.outputs
-        if fuse and src is not None and src.impl == "tf_residual_add_rmsnorm" and fmt != "nvfp4" and "q" not in src.args:
+        fusable = src is not None and "q" not in src.args and fmt != "nvfp4" and (
+            src.impl == "tf_residual_add_rmsnorm" or (src.impl == "tf_gemm_blockscaled" and src.attrs["format"] == fmt and src.attrs["epilogue"] != "residual"))
+        if fuse and fusable:
             src.args["q"] = nm
             src.attrs["q_format"] = fmt
             if single_use:  # nobody reads the bf16 copy: do not write it

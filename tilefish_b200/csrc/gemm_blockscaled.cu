@@ -20,7 +20,7 @@
 
 #include <cstdlib>
 
-#include "common.cuh"
+#include "quant_core.cuh"
 
 namespace tf {
 
@@ -94,6 +94,8 @@ struct GemmParams {
   unsigned int* out_amax;
   int splits, k_stages_per_split;  // split-K: every (tile, split) accumulates a K range into the f32 workspace
   float* ws;
+  uint8_t* q_codes;   // optional MX-quantized copy of the output (same format as the operands), swizzled scales
+  uint8_t* q_scales;
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------------
@@ -282,9 +284,51 @@ __global__ void bounded_wait_selftest_kernel(unsigned long long limit_ns) {
 
 // ---- epilogue helpers ------------------------------------------------------------------------------------------------------
 // Stores 32 consecutive bf16 outputs of one row (packed two per word) and applies the residual / amax side effects.
-template <int EPI>
+// The 32 outputs a thread holds are exactly one MX block of its row: amax, scale byte and codes by the quantizer's rules
+// (quant_core.cuh), written as the A operand of the next GEMM. FMT is the operands' (and the output's) format.
+template <int FMT>
+__device__ __forceinline__ void store_chunk_quantized(const GemmParams& p, const uint32_t (&packed)[16], int row, int col) {
+  if (FMT == TF_FMT_NVFP4) return;
+  const uint32_t k = 0x7FFF7FFFu;
+  uint32_t t = 0;
+#pragma unroll
+  for (int j = 0; j < 16; j += 2) t = __vimax3_u16x2(t, packed[j] & k, packed[j + 1] & k);
+  const uint32_t mx = max(t & 0xFFFFu, t >> 16);
+  const int emax = (FMT == TF_FMT_MXFP8) ? 8 : 2;
+  const int e = (int)(mx >> 7) - emax;
+  const uint32_t scale = (mx == 0) ? 127u : (uint32_t)max(e, 0);
+  const uint32_t inv1 = (254u - scale) << 7;
+  const uint32_t inv2 = inv1 | (inv1 << 16);
+  uint32_t q[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) q[j] = mul_bf16x2(packed[j], inv2);
+  if (FMT == TF_FMT_MXFP8) {
+    uint32_t c[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      c[j] = cvt_e4m3x2(bf16lo_to_f32(q[2 * j]), bf16hi_to_f32(q[2 * j])) | (cvt_e4m3x2(bf16lo_to_f32(q[2 * j + 1]), bf16hi_to_f32(q[2 * j + 1])) << 16);
+    uint4* dst = reinterpret_cast<uint4*>(p.q_codes + (int64_t)row * p.n + col);
+    dst[0] = make_uint4(c[0], c[1], c[2], c[3]);
+    dst[1] = make_uint4(c[4], c[5], c[6], c[7]);
+  } else {
+    uint32_t c[4];
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w |= cvt_e2m1x2(bf16lo_to_f32(q[4 * h + j]), bf16hi_to_f32(q[4 * h + j])) << (8 * j);
+      c[h] = w;
+    }
+    *reinterpret_cast<uint4*>(p.q_codes + (int64_t)row * (p.n >> 1) + (col >> 1)) = make_uint4(c[0], c[1], c[2], c[3]);
+  }
+  p.q_scales[swizzled_scale_offset(row, col >> 5, ((p.n >> 5) + 3) >> 2)] = (uint8_t)scale;
+}
+
+template <int EPI, int FMT>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t (&packed)[16], int row, int col, uint32_t& amax2) {
   if (row >= p.m) return;
+  if (p.q_codes && col + 32 <= p.n) store_chunk_quantized<FMT>(p, packed, row, col);
+  if (!p.out) return;
   uint16_t* orow = p.out + (int64_t)row * p.ldo + col;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
@@ -371,7 +415,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ac
       for (int j = 0; j < 16; ++j)
         packed[j] = pack_bf16x2(__fmul_rn(__uint_as_float(v[2 * j]), alpha), __fmul_rn(__uint_as_float(v[2 * j + 1]), alpha));
     }
-    store_chunk<EPI>(p, packed, row, col0 + c * 32, amax2);
+    store_chunk<EPI, FMT>(p, packed, row, col0 + c * 32, amax2);
   }
 }
 
@@ -412,22 +456,29 @@ __device__ __forceinline__ void epilogue_partial(const GemmParams& p, uint32_t t
 
 // Split-K second pass: sums the partials in split order (deterministic), then the same epilogue arithmetic as the one-pass
 // kernel. n_acc = accumulator columns (2 * n with the SiLU gate), one thread per 8 output columns.
-template <int EPI>
+template <int EPI, int QFMT>  // QFMT: -1, or the MX format of a quantized copy of the output
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int splits, int m, int n, int n_acc, const float* a_gs,
                                                             const float* b_gs, uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ residual,
-                                                            unsigned int* __restrict__ out_amax) {
+                                                            unsigned int* __restrict__ out_amax, uint8_t* __restrict__ q_codes,
+                                                            uint8_t* __restrict__ q_scales) {
   const float alpha = (a_gs && b_gs) ? __fmul_rn(__ldg(a_gs), __ldg(b_gs)) : 1.0f;
   const int nvec = n >> 3;
   const int64_t total = (int64_t)m * nvec;
   const int64_t plane = (int64_t)m * n_acc;
   uint32_t amax2 = 0;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int row = (int)(i / nvec), col = (int)(i - (int64_t)row * nvec) * 8;
+  // every thread runs the same number of rounds (the quantizer's shuffles need whole warps); n is a multiple of 32 when a
+  // quantized copy is asked for, so the 4 lanes of one block have data together
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t i0 = (int64_t)blockIdx.x * blockDim.x; i0 < total; i0 += stride) {
+    const int64_t i = i0 + threadIdx.x;
+    const bool live = i < total;
+    if (!live && QFMT < 0) continue;
+    const int row = live ? (int)(i / nvec) : 0, col = live ? (int)(i - (int64_t)row * nvec) * 8 : 0;
     float acc[8], up[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = up[j] = 0.0f;
     const float* base = ws + (int64_t)row * n_acc + col;
-    for (int sp = 0; sp < splits; ++sp) {
+    for (int sp = 0; sp < (live ? splits : 0); ++sp) {
       const float4 x0 = __ldcs(reinterpret_cast<const float4*>(base + sp * plane)), x1 = __ldcs(reinterpret_cast<const float4*>(base + sp * plane) + 1);
       acc[0] += x0.x; acc[1] += x0.y; acc[2] += x0.z; acc[3] += x0.w; acc[4] += x1.x; acc[5] += x1.y; acc[6] += x1.z; acc[7] += x1.w;
       if (EPI == TF_EPI_SILU_GATE) {
@@ -447,7 +498,13 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
       }
       amax2 = __vmaxu2(amax2, packed[j] & 0x7FFF7FFFu);
     }
-    *reinterpret_cast<uint4*>(out + (int64_t)row * ldo + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    if (QFMT >= 0) {
+      uint32_t c0, c1, sc;
+      quantize_vec8<(QFMT < 0 ? 0 : QFMT)>(make_uint4(packed[0], packed[1], packed[2], packed[3]), 0.0f, 0.0f, c0, c1, sc);
+      if (live) store_quantized<(QFMT < 0 ? 0 : QFMT)>(q_codes, q_scales, 1, row, col >> 3, n, c0, c1, sc);
+    }
+    if (!live) continue;
+    if (out) *reinterpret_cast<uint4*>(out + (int64_t)row * ldo + col) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
     if (EPI == TF_EPI_RESIDUAL) {
       float4* rp = reinterpret_cast<float4*>(residual + (int64_t)row * n + col);
       float4 r0 = rp[0], r1 = rp[1];
@@ -1097,19 +1154,31 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
     unsigned int* amax = p.out_amax;
     p.n = p.n_rows_b;
     p.out_amax = nullptr;
+    uint8_t* qc = p.q_codes;
+    p.q_codes = nullptr;  // the quantized copy is produced by the second pass
     tf_status st = sp.block_n == 128 ? launch_gemm<FMT, 128, TF_EPI_NONE, true>(ta, tb, p, stream) : launch_gemm<FMT, 256, TF_EPI_NONE, true>(ta, tb, p, stream);
     if (st != TF_OK) return st;
+    p.q_codes = qc;
     const int64_t total = (int64_t)p.m * (n_out >> 3);
     const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
     const unsigned grid = (unsigned)(need < cap ? need : cap);
     const float* ags = FMT == TF_FMT_NVFP4 ? p.a_gs : nullptr;
     const float* bgs = FMT == TF_FMT_NVFP4 ? p.b_gs : nullptr;
-    if (epilogue == TF_EPI_SILU_GATE)
-      splitk_reduce_kernel<TF_EPI_SILU_GATE><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
-    else if (epilogue == TF_EPI_RESIDUAL)
-      splitk_reduce_kernel<TF_EPI_RESIDUAL><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
-    else
-      splitk_reduce_kernel<TF_EPI_NONE><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax);
+#define TF_REDUCE(EPI_, Q_) \
+  splitk_reduce_kernel<EPI_, Q_><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax, p.q_codes, p.q_scales)
+    const int qf = p.q_codes ? FMT : -1;
+    if (epilogue == TF_EPI_SILU_GATE) {
+      if (qf == TF_FMT_MXFP8) TF_REDUCE(TF_EPI_SILU_GATE, TF_FMT_MXFP8);
+      else if (qf == TF_FMT_MXFP4) TF_REDUCE(TF_EPI_SILU_GATE, TF_FMT_MXFP4);
+      else TF_REDUCE(TF_EPI_SILU_GATE, -1);
+    } else if (epilogue == TF_EPI_RESIDUAL) {
+      TF_REDUCE(TF_EPI_RESIDUAL, -1);
+    } else {
+      if (qf == TF_FMT_MXFP8) TF_REDUCE(TF_EPI_NONE, TF_FMT_MXFP8);
+      else if (qf == TF_FMT_MXFP4) TF_REDUCE(TF_EPI_NONE, TF_FMT_MXFP4);
+      else TF_REDUCE(TF_EPI_NONE, -1);
+    }
+#undef TF_REDUCE
     TF_LAUNCH_CHECK();
     return TF_OK;
   }
@@ -1210,19 +1279,31 @@ tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, 
     if (st != TF_OK) return st;
   }
   return tf_gemm_blockscaled(a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, out, ldo, m, n, k, format, epilogue, epilogue_arg,
-                             out_amax, scratch, need > 0 ? kStaticScratchBytes : 0, stream);
+                             out_amax, nullptr, nullptr, scratch, need > 0 ? kStaticScratchBytes : 0, stream);
 }
 
 tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
                               const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
-                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* workspace, int64_t workspace_bytes, void* stream_) {
+                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales, void* workspace,
+                              int64_t workspace_bytes, void* stream_) {
   clear_error();
   cudaStream_t stream = (cudaStream_t)stream_;
   TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", __func__, format);
   TF_CHECK_ARG(epilogue >= TF_EPI_NONE && epilogue <= TF_EPI_RESIDUAL, "%s: unknown epilogue %d", __func__, epilogue);
   TF_CHECK_ARG(m >= 0 && n > 0 && k > 0, "%s: bad shape m=%lld n=%lld k=%lld", __func__, (long long)m, (long long)n, (long long)k);
   if (m == 0) return TF_OK;
-  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && out, "%s: null pointer", __func__);
+  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && (out || q_codes), "%s: null pointer", __func__);
+  TF_CHECK_ARG((q_codes == nullptr) == (q_scales == nullptr), "%s: q_codes and q_scales go together", __func__);
+  if (q_codes) {
+    if (format == TF_FMT_NVFP4)
+      return fail(TF_ERR_UNSUPPORTED, "%s: a quantized output needs the tensor's global scale first; nvfp4 outputs are quantized by tf_quantize_nvfp4_from_amax", __func__);
+    if (epilogue == TF_EPI_RESIDUAL) return fail(TF_ERR_UNSUPPORTED, "%s: the residual epilogue has no quantized output", __func__);
+    if (n % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: a quantized output needs n %% 32 == 0", __func__);
+    TF_CHECK_ALIGNED(q_codes, 16, "q_codes");
+    const int64_t cols = n / 32;
+    if ((m & 127) || (cols & 3)) TF_CUDA(cudaMemsetAsync(q_scales, 0, (size_t)tf_scale_bytes(format, m, n, TF_SCALES_SWIZZLED), stream));
+  }
+  TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || out, "%s: the residual epilogue needs out", __func__);
   TF_CHECK_ARG(format != TF_FMT_NVFP4 || (a_global_scale && b_global_scale), "%s: nvfp4 needs both global scales", __func__);
   TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || epilogue_arg, "%s: the residual epilogue needs its f32 residual", __func__);
   if (k % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: k=%lld is not a multiple of 32", __func__, (long long)k);
@@ -1233,7 +1314,7 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
   TF_CHECK_ALIGNED(b_codes, 16, "b_codes");
   TF_CHECK_ALIGNED(a_scales, 16, "a_scales");
   TF_CHECK_ALIGNED(b_scales, 16, "b_scales");
-  TF_CHECK_ALIGNED(out, 16, "out");
+  if (out) TF_CHECK_ALIGNED(out, 16, "out");
   if (epilogue == TF_EPI_RESIDUAL) TF_CHECK_ALIGNED(epilogue_arg, 16, "residual");
 
   const int64_t k_bytes = (format == TF_FMT_MXFP8) ? k : k / 2;
@@ -1264,6 +1345,8 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
   p.ldo = ldo;
   p.residual = static_cast<float*>(epilogue_arg);
   p.out_amax = reinterpret_cast<unsigned int*>(out_amax);
+  p.q_codes = static_cast<uint8_t*>(q_codes);
+  p.q_scales = static_cast<uint8_t*>(q_scales);
   const SplitPlan sp = split_plan(m, n, k_bytes, epilogue);
   p.splits = sp.splits;
   p.k_stages_per_split = sp.k_stages_per_split;

@@ -284,11 +284,14 @@ def gemm_workspace_bytes(m: int, n: int, k: int, fmt: str, epilogue: str = "none
 
 
 def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, amax_out=None,
-                     workspace=None, stream=None):
+                     quantize_out: bool = False, q_out: Optional[BlockScaledTensor] = None, want_bf16: bool = True, workspace=None, stream=None):
     """bf16 [M, N] = deq(a)[M, K] @ deq(b)[N, K]^T on tcgen05 block-scaled MMA, f32 accumulate.
 
     ``epilogue="silu_gate"``: b has 2N rows (gate rows then up rows); the result is silu(gate) * up, [M, N].
     ``epilogue="residual"``: also ``residual[M, N] += f32(out)`` (f32, in place).
+    ``quantize_out=True`` (MX formats): the epilogue also quantizes the result in the operands' format, byte for byte what
+    ``quantize(out, fmt)`` gives, and the call returns ``(out, q)``; with ``want_bf16=False`` the bf16 copy is not written
+    (``out`` is None). ``q_out`` supplies preallocated storage for it.
     """
     torch = _torch()
     _pre(isinstance(a, BlockScaledTensor) and isinstance(b, BlockScaledTensor), "a and b must be BlockScaledTensor", "dtype")
@@ -307,12 +310,27 @@ def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: st
         _dense(t, nm)
     if a.fmt == "nvfp4":
         _pre(a.global_scale is not None and b.global_scale is not None, "nvfp4 operands need their global scales", "argument")
-    if out is None:
+    quantize_out = quantize_out or q_out is not None
+    q = None
+    if quantize_out:
+        _pre(a.fmt != "nvfp4", "a quantized gemm output needs the tensor's global scale first: not available for nvfp4", "dtype", "quantize_out")
+        _pre(epilogue != "residual" and n % 32 == 0, "quantize_out needs n % 32 == 0 and is not available with the residual epilogue", "divisible", "quantize_out")
+        if q_out is not None:
+            _pre(q_out.fmt == a.fmt and q_out.shape == (m, n) and q_out.layout == "swizzled", "q_out: wrong format or shape", "shape", "q_out")
+            q = q_out
+        else:
+            q = BlockScaledTensor(a.fmt, (m, n), torch.empty((m, n // ELEMS_PER_BYTE[a.fmt]), dtype=torch.uint8, device=a.device),
+                                  torch.empty(N.scale_bytes(FORMATS[a.fmt], m, n, N.SCALES_SWIZZLED), dtype=torch.uint8, device=a.device), None, "swizzled")
+    else:
+        _pre(want_bf16, "nothing to compute: want_bf16=False without quantize_out", "argument")
+    if not want_bf16:
+        out = None
+    elif out is None:
         out = torch.empty((m, n), dtype=torch.bfloat16, device=a.device)
     else:
         _check(out, "out", torch.bfloat16, 2, a.device)
         _pre(tuple(out.shape) == (m, n) and out.stride(1) == 1 and (m <= 1 or out.stride(0) % 8 == 0), "out: wrong shape or strides", "shape", "out")
-    ldo = out.stride(0) if m > 1 else n
+    ldo = out.stride(0) if (out is not None and m > 1) else n
     res_ptr = None
     if epilogue == "residual":
         _pre(residual is not None, "epilogue='residual' needs the f32 residual", "argument", "residual")
@@ -331,11 +349,12 @@ def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: st
         N.load().tf_gemm_blockscaled(
             a.codes.data_ptr(), a.scales.data_ptr(), a.global_scale.data_ptr() if a.global_scale is not None else None,
             b.codes.data_ptr(), b.scales.data_ptr(), b.global_scale.data_ptr() if b.global_scale is not None else None,
-            out.data_ptr(), ldo, m, n, k, FORMATS[a.fmt], EPILOGUES[epilogue], res_ptr, _amax_ptr(amax_out, a.device), ws_ptr, ws_bytes,
+            out.data_ptr() if out is not None else None, ldo, m, n, k, FORMATS[a.fmt], EPILOGUES[epilogue], res_ptr, _amax_ptr(amax_out, a.device),
+            q.codes.data_ptr() if q is not None and m > 0 else None, q.scales.data_ptr() if q is not None and m > 0 else None, ws_ptr, ws_bytes,
             _stream(stream)),
         "tf_gemm_blockscaled",
     )
-    return out
+    return (out, q) if quantize_out else out
 
 
 def gemm(a, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, a_global_scale=None, a_amax=None, amax_out=None,

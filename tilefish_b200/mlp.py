@@ -6,7 +6,8 @@ executes on this backend, single-GPU or tensor-parallel:
 * activations are quantized in the weights' format at both GEMMs (the library ``gemm`` takes a bf16 ``a``);
 * the split / SiLU gate / multiply of the graph body runs as the first GEMM's epilogue (gate and up column tiles are
   accumulated side by side in tensor memory), so the [M, 2F] intermediate never reaches HBM;
-* mxfp8 / mxfp4: the rmsnorm kernel emits the quantized activation directly; nvfp4: the producing kernels also reduce
+* mxfp8 / mxfp4: the rmsnorm kernel and the first GEMM's epilogue emit the quantized activations directly (two launches
+  less, no bf16 intermediate in HBM); nvfp4: the producing kernels also reduce
   max|out| (an atomic max), from which the quantizer derives the tensor's global scale in stream order: no host sync;
 * tensor parallel: ``w_gu`` is split by columns of the output (gate rows and the matching up rows per rank), ``w_d`` by K;
   one bf16 all-reduce (NCCL, through torch.distributed) per layer sums the partial results of the second GEMM.
@@ -91,8 +92,7 @@ def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, 
         aq = K.quantize(a, fmt, amax=amax[1:2])
     else:
         _, hq = K.residual_add_rmsnorm(x, residual, w.w_n, eps, quantize_to=fmt, want_bf16=False)
-        a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate")
-        aq = K.quantize(a, fmt)
+        _, aq = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", quantize_out=True, want_bf16=False)  # `a` never exists in bf16
     y = K.gemm_blockscaled(aq, w.w_d, out=out)
     if group is not None:
         import torch.distributed as dist

@@ -173,7 +173,9 @@ class Sm100Backend(Backend):
 
         a = step["args"]
         K.gemm_blockscaled(self._resolve(a["a"], tensors), self._resolve(a["b"], tensors), epilogue=step["attrs"]["epilogue"],
-                           out=self._resolve(a["out"], tensors), amax_out=self._resolve(a["amax"], tensors) if "amax" in a else None)
+                           out=self._resolve(a["out"], tensors) if "out" in a else None, want_bf16="out" in a,
+                           q_out=self._resolve(a["q"], tensors) if "q" in a else None,
+                           amax_out=self._resolve(a["amax"], tensors) if "amax" in a else None)
 
 
 _DEFAULT_BACKEND: Optional[Backend] = None
