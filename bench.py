@@ -42,6 +42,8 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
+    ap.add_argument("--comm", default=None, choices=["all_reduce", "scatter_gather"],
+                    help="tensor-parallel exchange per block (default: scatter_gather when N > 1: reduce-scatter + all-gather of the quantized activation)")
     ap.add_argument("--chunks", type=int, default=None, help="row chunks whose all-reduces overlap the other chunk's GEMMs (default: 2 when N > 1)")
     return ap.parse_args()
 
@@ -424,7 +426,8 @@ def run_ours(args) -> None:
         blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, FMT, rank=rank, world=world))
         del w_gu, w_d
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    stack = MLP.MlpStack(blocks, group=group, chunks=chunks)
+    comm = args.comm or ("scatter_gather" if world > 1 else "all_reduce")
+    stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm)
     torch.cuda.synchronize()
 
     gx = torch.Generator().manual_seed(0)
@@ -559,7 +562,7 @@ def run_ours(args) -> None:
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp4 (e2m1 x e4m3 block scales, f32 accumulate, bf16 out)",
         "data": "synthetic", "impl": "ours",
         "config": {"workload": WORKLOAD if (layers, m) == (LAYERS, M_TOKENS) else f"REDUCED {layers} layers M={m} (development run, not the benchmark)",
-                   "parallelism": f"tp{world}" + (f", {stack.chunks} row chunks on 2 streams (all-reduce of one under the GEMMs of the other)" if stack.chunks > 1 else ""), "l2": "inputs larger than L2: every step streams all weights (>= 1.5 GB per GPU)"},
+                   "parallelism": f"tp{world}" + (f", {stack.comm}, {stack.chunks} row chunks on 2 streams (one chunk's exchange under the other's GEMMs)" if world > 1 else ""), "l2": "inputs larger than L2: every step streams all weights (>= 1.5 GB per GPU)"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "gpu_launches": launches_per_step * args.steps,

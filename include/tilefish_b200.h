@@ -138,12 +138,15 @@ TF_API tf_status tf_silu_gate(const void* gate, const void* up, int64_t m, int64
  *   q_codes, q_scales   NULL, or (MX formats, n % 32 == 0, not with TF_EPI_RESIDUAL) the output is ALSO quantized, in the operands'
  *            format, exactly as tf_quantize_* would quantize `out` (every epilogue thread holds whole 32-element blocks):
  *            codes [m, n] or [m, n/2], swizzled scales. `out` may then be NULL (the bf16 copy is not written)
+ *   a_global_scale_rows   0: a has one global scale. Else (a multiple of 128) a_global_scale is an array and rows
+ *            [i * a_global_scale_rows, (i+1) * a_global_scale_rows) of a use entry i: row blocks that were quantized separately
+ *            (each with the global scale of its own amax), e.g. activation rows gathered from the ranks of a tensor-parallel group
  *   workspace / workspace_bytes   at least tf_gemm_workspace_bytes(...) bytes, 256-byte aligned (may be NULL when 0) */
 TF_API int64_t tf_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue);
 TF_API tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
                               const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
                               int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales,
-                              void* workspace, int64_t workspace_bytes, void* stream);
+                              int64_t a_global_scale_rows, void* workspace, int64_t workspace_bytes, void* stream);
 
 /* The same GEMM for callers that cannot hand over a workspace. (No counterpart in the reference.)
  *

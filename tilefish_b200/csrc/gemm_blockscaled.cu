@@ -96,6 +96,7 @@ struct GemmParams {
   float* ws;
   uint8_t* q_codes;   // optional MX-quantized copy of the output (same format as the operands), swizzled scales
   uint8_t* q_scales;
+  int a_gs_rows;  // 0: a has one global scale; else a_gs[row / a_gs_rows] (row blocks quantized separately, e.g. gathered from ranks)
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------------
@@ -460,8 +461,8 @@ template <int EPI, int QFMT>  // QFMT: -1, or the MX format of a quantized copy 
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ ws, int splits, int m, int n, int n_acc, const float* a_gs,
                                                             const float* b_gs, uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ residual,
                                                             unsigned int* __restrict__ out_amax, uint8_t* __restrict__ q_codes,
-                                                            uint8_t* __restrict__ q_scales) {
-  const float alpha = (a_gs && b_gs) ? __fmul_rn(__ldg(a_gs), __ldg(b_gs)) : 1.0f;
+                                                            uint8_t* __restrict__ q_scales, int a_gs_rows) {
+  const float alpha0 = (a_gs && b_gs) ? __fmul_rn(__ldg(a_gs), __ldg(b_gs)) : 1.0f;
   const int nvec = n >> 3;
   const int64_t total = (int64_t)m * nvec;
   const int64_t plane = (int64_t)m * n_acc;
@@ -477,6 +478,7 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     float acc[8], up[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = up[j] = 0.0f;
+    const float alpha = (a_gs && b_gs && a_gs_rows > 0) ? __fmul_rn(__ldg(a_gs + row / a_gs_rows), __ldg(b_gs)) : alpha0;
     const float* base = ws + (int64_t)row * n_acc + col;
     for (int sp = 0; sp < (live ? splits : 0); ++sp) {
       const float4 x0 = __ldcs(reinterpret_cast<const float4*>(base + sp * plane)), x1 = __ldcs(reinterpret_cast<const float4*>(base + sp * plane) + 1);
@@ -735,6 +737,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       const int row = m_blk * kBlockM + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
       const int col0 = n_blk * kOutCols;
+      const float alpha_t = (FMT == TF_FMT_NVFP4 && p.a_gs_rows > 0) ? __fmul_rn(__ldg(p.a_gs + min(row, p.m - 1) / p.a_gs_rows), __ldg(p.b_gs)) : alpha;
       if (SPLITK) {
         float* ws_row = p.ws + ((int64_t)split * p.m + row) * p.n;
         if (acc_buf == 0)
@@ -742,9 +745,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
         else
           epilogue_partial<FMT, BLOCK_N, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, ws_row);
       } else if (acc_buf == 0) {
-        epilogue_tile<FMT, BLOCK_N, EPI, 0>(p, t_row, bar_tmem_empty, lane, row, col0, alpha, amax2);
+        epilogue_tile<FMT, BLOCK_N, EPI, 0>(p, t_row, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
       } else {
-        epilogue_tile<FMT, BLOCK_N, EPI, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha, amax2);
+        epilogue_tile<FMT, BLOCK_N, EPI, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
       }
       acc_buf ^= 1;
       tile_phase ^= 1;
@@ -974,10 +977,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_pair_kernel(
       const int row = m_blk * 256 + (int)rank * 128 + q * 32 + lane;
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16);
       const int col0 = n_blk * kOutCols;
+      const float alpha_t = (FMT == TF_FMT_NVFP4 && p.a_gs_rows > 0) ? __fmul_rn(__ldg(p.a_gs + min(row, p.m - 1) / p.a_gs_rows), __ldg(p.b_gs)) : alpha;
       if (acc_buf == 0)
-        epilogue_tile<FMT, BLOCK_N, EPI, 0, true>(p, t_row, release, lane, row, col0, alpha, amax2);
+        epilogue_tile<FMT, BLOCK_N, EPI, 0, true>(p, t_row, release, lane, row, col0, alpha_t, amax2);
       else
-        epilogue_tile<FMT, BLOCK_N, EPI, 1, true>(p, t_row + Cfg::kAccStride, release, lane, row, col0, alpha, amax2);
+        epilogue_tile<FMT, BLOCK_N, EPI, 1, true>(p, t_row + Cfg::kAccStride, release, lane, row, col0, alpha_t, amax2);
       acc_buf ^= 1;
       tile_phase ^= 1;
     }
@@ -1165,7 +1169,7 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
     const float* ags = FMT == TF_FMT_NVFP4 ? p.a_gs : nullptr;
     const float* bgs = FMT == TF_FMT_NVFP4 ? p.b_gs : nullptr;
 #define TF_REDUCE(EPI_, Q_) \
-  splitk_reduce_kernel<EPI_, Q_><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax, p.q_codes, p.q_scales)
+  splitk_reduce_kernel<EPI_, Q_><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax, p.q_codes, p.q_scales, p.a_gs_rows)
     const int qf = p.q_codes ? FMT : -1;
     if (epilogue == TF_EPI_SILU_GATE) {
       if (qf == TF_FMT_MXFP8) TF_REDUCE(TF_EPI_SILU_GATE, TF_FMT_MXFP8);
@@ -1279,13 +1283,13 @@ tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, 
     if (st != TF_OK) return st;
   }
   return tf_gemm_blockscaled(a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, out, ldo, m, n, k, format, epilogue, epilogue_arg,
-                             out_amax, nullptr, nullptr, scratch, need > 0 ? kStaticScratchBytes : 0, stream);
+                             out_amax, nullptr, nullptr, 0, scratch, need > 0 ? kStaticScratchBytes : 0, stream);
 }
 
 tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
                               const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
-                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales, void* workspace,
-                              int64_t workspace_bytes, void* stream_) {
+                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales,
+                              int64_t a_global_scale_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
   clear_error();
   cudaStream_t stream = (cudaStream_t)stream_;
   TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", __func__, format);
@@ -1304,6 +1308,7 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
     if ((m & 127) || (cols & 3)) TF_CUDA(cudaMemsetAsync(q_scales, 0, (size_t)tf_scale_bytes(format, m, n, TF_SCALES_SWIZZLED), stream));
   }
   TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || out, "%s: the residual epilogue needs out", __func__);
+  TF_CHECK_ARG(a_global_scale_rows >= 0 && a_global_scale_rows % 128 == 0, "%s: a_global_scale_rows must be 0 or a multiple of 128", __func__);
   TF_CHECK_ARG(format != TF_FMT_NVFP4 || (a_global_scale && b_global_scale), "%s: nvfp4 needs both global scales", __func__);
   TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || epilogue_arg, "%s: the residual epilogue needs its f32 residual", __func__);
   if (k % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: k=%lld is not a multiple of 32", __func__, (long long)k);
@@ -1347,6 +1352,7 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
   p.out_amax = reinterpret_cast<unsigned int*>(out_amax);
   p.q_codes = static_cast<uint8_t*>(q_codes);
   p.q_scales = static_cast<uint8_t*>(q_scales);
+  p.a_gs_rows = (int)a_global_scale_rows;
   const SplitPlan sp = split_plan(m, n, k_bytes, epilogue);
   p.splits = sp.splits;
   p.k_stages_per_split = sp.k_stages_per_split;

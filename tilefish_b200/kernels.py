@@ -60,9 +60,9 @@ class BlockScaledTensor:
     ``global_scale``  float32 [1] on the device for nvfp4, else None
     """
 
-    __slots__ = ("fmt", "shape", "codes", "scales", "global_scale", "layout")
+    __slots__ = ("fmt", "shape", "codes", "scales", "global_scale", "layout", "gs_rows")
 
-    def __init__(self, fmt: str, shape, codes, scales, global_scale=None, layout: str = "swizzled") -> None:
+    def __init__(self, fmt: str, shape, codes, scales, global_scale=None, layout: str = "swizzled", gs_rows: int = 0) -> None:
         if fmt not in FORMATS:
             raise TilefishPreconditionError(f"unknown block-scaled format {fmt!r}", kind="dtype")
         self.fmt = fmt
@@ -71,6 +71,7 @@ class BlockScaledTensor:
         self.scales = scales
         self.global_scale = global_scale
         self.layout = layout
+        self.gs_rows = gs_rows  # nvfp4: 0 = one global scale; else global_scale[i] belongs to rows [i * gs_rows, (i + 1) * gs_rows)
 
     @property
     def device(self):
@@ -350,7 +351,7 @@ def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: st
             a.codes.data_ptr(), a.scales.data_ptr(), a.global_scale.data_ptr() if a.global_scale is not None else None,
             b.codes.data_ptr(), b.scales.data_ptr(), b.global_scale.data_ptr() if b.global_scale is not None else None,
             out.data_ptr() if out is not None else None, ldo, m, n, k, FORMATS[a.fmt], EPILOGUES[epilogue], res_ptr, _amax_ptr(amax_out, a.device),
-            q.codes.data_ptr() if q is not None and m > 0 else None, q.scales.data_ptr() if q is not None and m > 0 else None, ws_ptr, ws_bytes,
+            q.codes.data_ptr() if q is not None and m > 0 else None, q.scales.data_ptr() if q is not None and m > 0 else None, a.gs_rows, ws_ptr, ws_bytes,
             _stream(stream)),
         "tf_gemm_blockscaled",
     )

@@ -101,6 +101,52 @@ def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, 
     return y
 
 
+def decoder_block_row_sharded(x_loc, res_loc, w: MlpWeights, eps: float, group, world: int, scratch: dict):
+    """One tensor-parallel block with the normalisation sharded by rows: this rank holds rows ``x_loc`` / ``res_loc`` ([R, H],
+    R a multiple of 128) of the block's input. It normalises and quantizes its rows, all-gathers the QUANTIZED activation
+    (0.56 bytes per element for nvfp4 instead of 2), runs both GEMMs on all rows against its weight shard and reduce-scatters
+    the bf16 partial results, so the next block again starts from its own rows. Compared with an all-reduce per block the
+    bytes on NVLink drop to (1 + 0.28) / 2 of the all-reduce's, and the rmsnorm work is divided by the group size. Every rank's
+    row block keeps the nvfp4 global scale of its own amax (the GEMM takes one global scale per row block)."""
+    import torch
+    import torch.distributed as dist
+
+    fmt = w.fmt
+    r, h = x_loc.shape
+    dev = x_loc.device
+    key = (r, h, fmt)
+    buf = scratch.get(key)
+    if buf is None:
+        epb = K.ELEMS_PER_BYTE[fmt]
+        sbytes = K.scale_bytes(fmt, r, h)
+        buf = scratch[key] = {
+            "codes": torch.empty((world * r, h // epb), dtype=torch.uint8, device=dev),
+            "scales": torch.empty(world * sbytes, dtype=torch.uint8, device=dev),
+            "gs": torch.empty(world, dtype=torch.float32, device=dev) if fmt == "nvfp4" else None,
+            "amax": torch.zeros(2, dtype=torch.float32, device=dev),
+        }
+    if fmt == "nvfp4":
+        amax = buf["amax"]
+        amax.zero_()
+        hl = K.residual_add_rmsnorm(x_loc, res_loc, w.w_n, eps, amax_out=amax[0:1])
+        hq = K.quantize(hl, fmt, amax=amax[0:1])
+        dist.all_gather_into_tensor(buf["gs"], hq.global_scale, group=group)
+    else:
+        _, hq = K.residual_add_rmsnorm(x_loc, res_loc, w.w_n, eps, quantize_to=fmt, want_bf16=False)
+    dist.all_gather_into_tensor(buf["codes"], hq.codes, group=group)
+    dist.all_gather_into_tensor(buf["scales"], hq.scales, group=group)
+    hq_all = K.BlockScaledTensor(fmt, (world * r, h), buf["codes"], buf["scales"], buf["gs"], "swizzled", gs_rows=r if fmt == "nvfp4" else 0)
+    if fmt == "nvfp4":
+        a = K.gemm_blockscaled(hq_all, w.w_gu, epilogue="silu_gate", amax_out=amax[1:2])
+        aq = K.quantize(a, fmt, amax=amax[1:2])
+    else:
+        _, aq = K.gemm_blockscaled(hq_all, w.w_gu, epilogue="silu_gate", quantize_out=True, want_bf16=False)
+    y = K.gemm_blockscaled(aq, w.w_d)
+    out = torch.empty((r, h), dtype=torch.bfloat16, device=dev)
+    dist.reduce_scatter_tensor(out, y, group=group)
+    return out
+
+
 class MlpStack:
     """``layers`` decoder blocks applied in sequence: the output of block l is the ``x`` of block l + 1, the f32 residual
     stream is carried in place.
@@ -111,16 +157,25 @@ class MlpStack:
     global scales.
     """
 
-    def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16) -> None:
+    def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16,
+                 comm: str = "all_reduce") -> None:
+        """``comm``: "all_reduce" (one bf16 all-reduce per block) or "scatter_gather" (rows of the normalisation sharded over
+        the ranks: reduce-scatter of the partial results + all-gather of the quantized activations; see
+        ``decoder_block_row_sharded``)."""
         self.layers = layers
         self.eps = eps
         self.group = group
         self.chunks = chunks if group is not None else 1
         self.sm_margin = sm_margin
+        self.comm = comm if group is not None else "all_reduce"
+        if self.comm not in ("all_reduce", "scatter_gather"):
+            raise TilefishPreconditionError(f"unknown comm mode {comm!r}", kind="argument", arg="comm")
         self._scratch: List[dict] = [{} for _ in range(max(1, self.chunks))]
         self._streams = None
 
     def forward(self, x, residual):
+        if self.comm == "scatter_gather":
+            return self._forward_row_sharded(x, residual)
         if self.chunks <= 1:
             for w in self.layers:
                 x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
@@ -160,6 +215,57 @@ class MlpStack:
                 main.wait_stream(s)
         finally:
             N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
+        return out
+
+    def _forward_row_sharded(self, x, residual):
+        import torch
+        import torch.distributed as dist
+
+        from . import _native as N
+
+        world = dist.get_world_size(self.group)
+        rank = dist.get_rank(self.group)
+        m, h = x.shape
+        c = max(1, self.chunks)
+        unit = 128 * world
+        if m % (unit * c):
+            c = 1
+        if m % unit:
+            raise TilefishPreconditionError(f"scatter_gather needs M={m} to be a multiple of 128 x group size ({unit})", kind="divisible", arg="x")
+        rows = m // c       # rows of a chunk
+        r = rows // world   # rows of a chunk this rank normalises
+        if self._streams is None or len(self._streams) < c:
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in range(c)]
+        while len(self._scratch) < c:
+            self._scratch.append({})
+        main = torch.cuda.current_stream()
+        out = torch.empty_like(x)
+        if c > 1:
+            N.check(N.load().tf_set_sm_margin(self.sm_margin), "tf_set_sm_margin")
+        try:
+            xs, rs = [], []
+            for ci in range(c):
+                lo = ci * rows + rank * r
+                xs.append(x[lo:lo + r])
+                rs.append(residual[lo:lo + r])  # this rank's rows are updated in place; the others arrive with the final all-gather
+            streams = self._streams[:c] if c > 1 else [main]
+            for st in streams:
+                if st is not main:
+                    st.wait_stream(main)
+            for w in self.layers:
+                for ci in range(c):
+                    with torch.cuda.stream(streams[ci]):
+                        xs[ci] = decoder_block_row_sharded(xs[ci], rs[ci], w, self.eps, self.group, world, self._scratch[ci])
+            for ci in range(c):
+                with torch.cuda.stream(streams[ci]):
+                    dist.all_gather_into_tensor(out[ci * rows:(ci + 1) * rows], xs[ci], group=self.group)
+                    dist.all_gather_into_tensor(residual[ci * rows:(ci + 1) * rows], rs[ci].clone(), group=self.group)
+            for st in streams:
+                if st is not main:
+                    main.wait_stream(st)
+        finally:
+            if c > 1:
+                N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
         return out
 
     __call__ = forward
