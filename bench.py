@@ -43,7 +43,8 @@ def parse_args():
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "scatter_gather"],
-                    help="tensor-parallel exchange per block (default: scatter_gather when N > 1: reduce-scatter + all-gather of the quantized activation)")
+                    help="tensor-parallel exchange per block (default all_reduce; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
+                         "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
     ap.add_argument("--chunks", type=int, default=None, help="row chunks whose all-reduces overlap the other chunk's GEMMs (default: 2 when N > 1)")
     return ap.parse_args()
 
@@ -426,15 +427,20 @@ def run_ours(args) -> None:
         blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, FMT, rank=rank, world=world))
         del w_gu, w_d
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    comm = args.comm or ("scatter_gather" if world > 1 else "all_reduce")
+    comm = args.comm or "all_reduce"
     stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm)
     torch.cuda.synchronize()
 
     gx = torch.Generator().manual_seed(0)
-    x_host = torch.randn((m, H), generator=gx).to(torch.bfloat16).pin_memory()
-    out_host = torch.empty((m, H), dtype=torch.bfloat16).pin_memory()
+    x_all = torch.randn((m, H), generator=gx).to(torch.bfloat16)
+    # scatter_gather keeps every token on one rank outside the GEMMs: each rank uploads, normalises and downloads only its own
+    # rows, so the job's input and output cross PCIe once in total (m * H * 2 bytes each way over all ranks)
+    rows_local = world > 1 and stack.comm == "scatter_gather"
+    m_io = m // world if rows_local else m
+    x_host = (x_all[rank * m_io:(rank + 1) * m_io] if rows_local else x_all).contiguous().pin_memory()
+    out_host = torch.empty((m_io, H), dtype=torch.bfloat16).pin_memory()
     x_dev = x_host.to(dev)
-    residual = torch.zeros((m, H), dtype=torch.float32, device=dev)
+    residual = torch.zeros((m_io, H), dtype=torch.float32, device=dev)
 
     # per-launch events around the dominant kernel (the first GEMM of every block) inside the timed region
     gemm_events = []
@@ -456,15 +462,18 @@ def run_ours(args) -> None:
 
     def step():
         residual.zero_()
-        return stack(x_dev, residual)
+        return stack(x_dev, residual, rows_local=True) if rows_local else stack(x_dev, residual)
 
     def step_e2e():
         x_dev.copy_(x_host, non_blocking=True)
         residual.zero_()
-        y = stack(x_dev, residual)
+        y = step_inner()
         out_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return out_host
+
+    def step_inner():
+        return stack(x_dev, residual, rows_local=True) if rows_local else stack(x_dev, residual)
 
     def barrier():
         if world > 1:
@@ -563,7 +572,9 @@ def run_ours(args) -> None:
         "data": "synthetic", "impl": "ours",
         "config": {"workload": WORKLOAD if (layers, m) == (LAYERS, M_TOKENS) else f"REDUCED {layers} layers M={m} (development run, not the benchmark)",
                    "parallelism": f"tp{world}" + (f", {stack.comm}, {stack.chunks} row chunks on 2 streams (one chunk's exchange under the other's GEMMs)" if world > 1 else ""), "l2": "inputs larger than L2: every step streams all weights (>= 1.5 GB per GPU)"},
-        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2, "d2h_bytes_per_step": out_host.numel() * 2,
+        "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2 * (world if rows_local else 1),
+                "d2h_bytes_per_step": out_host.numel() * 2 * (world if rows_local else 1),
+                "io": (f"each rank copies its own {m_io} rows; bytes are the job's total" if rows_local else "every rank copies the full tensors; bytes are per rank"),
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "gpu_launches": launches_per_step * args.steps,
         "roofline": roofline,

@@ -122,6 +122,16 @@ def test_row_chunks_and_graph_capture_reproduce_the_plain_stack(tmp_path):
         y_chunk = stack(x, r_chunk)
         torch.cuda.synchronize()
         assert torch.equal(y_chunk, y_plain) and torch.equal(r_chunk, r_plain)
+        for chunks in (1, 2):  # the row-sharded exchange (reduce-scatter + all-gather of the quantized rows), full and rank-local I/O
+            sg = MLP.MlpStack(layers, group=dist.group.WORLD, chunks=chunks, comm="scatter_gather")
+            r_sg = res0.clone()
+            y_sg = sg(x, r_sg)
+            torch.cuda.synchronize()
+            assert torch.equal(y_sg, y_plain) and torch.equal(r_sg, r_plain), chunks
+            r_loc = res0.clone()
+            y_loc = sg(x, r_loc, rows_local=True)
+            torch.cuda.synchronize()
+            assert torch.equal(y_loc, y_plain) and torch.equal(r_loc, r_plain), chunks
         xg, rg = x.clone(), res0.clone()
         cap = stack.capture(xg, rg)
         rg.copy_(res0)

@@ -173,9 +173,13 @@ class MlpStack:
         self._scratch: List[dict] = [{} for _ in range(max(1, self.chunks))]
         self._streams = None
 
-    def forward(self, x, residual):
+    def forward(self, x, residual, rows_local: bool = False):
+        """``rows_local`` (scatter_gather only): ``x`` and ``residual`` are THIS RANK'S rows ([M / n, H]) and so is the result: no
+        rank ever holds the other ranks' tokens outside the GEMMs, and the job's input and output cross PCIe once in total."""
         if self.comm == "scatter_gather":
-            return self._forward_row_sharded(x, residual)
+            return self._forward_row_sharded(x, residual, rows_local)
+        if rows_local:
+            raise TilefishPreconditionError("rows_local needs comm='scatter_gather'", kind="argument", arg="rows_local")
         if self.chunks <= 1:
             for w in self.layers:
                 x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
@@ -217,7 +221,7 @@ class MlpStack:
             N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
         return out
 
-    def _forward_row_sharded(self, x, residual):
+    def _forward_row_sharded(self, x, residual, rows_local: bool = False):
         import torch
         import torch.distributed as dist
 
@@ -226,6 +230,8 @@ class MlpStack:
         world = dist.get_world_size(self.group)
         rank = dist.get_rank(self.group)
         m, h = x.shape
+        if rows_local:
+            m *= world
         c = max(1, self.chunks)
         unit = 128 * world
         if m % (unit * c):
@@ -245,7 +251,7 @@ class MlpStack:
         try:
             xs, rs = [], []
             for ci in range(c):
-                lo = ci * rows + rank * r
+                lo = ci * r if rows_local else ci * rows + rank * r
                 xs.append(x[lo:lo + r])
                 rs.append(residual[lo:lo + r])  # this rank's rows are updated in place; the others arrive with the final all-gather
             streams = self._streams[:c] if c > 1 else [main]
@@ -258,8 +264,11 @@ class MlpStack:
                         xs[ci] = decoder_block_row_sharded(xs[ci], rs[ci], w, self.eps, self.group, world, self._scratch[ci])
             for ci in range(c):
                 with torch.cuda.stream(streams[ci]):
-                    dist.all_gather_into_tensor(out[ci * rows:(ci + 1) * rows], xs[ci], group=self.group)
-                    dist.all_gather_into_tensor(residual[ci * rows:(ci + 1) * rows], rs[ci].clone(), group=self.group)
+                    if rows_local:
+                        out[ci * r:(ci + 1) * r].copy_(xs[ci])
+                    else:
+                        dist.all_gather_into_tensor(out[ci * rows:(ci + 1) * rows], xs[ci], group=self.group)
+                        dist.all_gather_into_tensor(residual[ci * rows:(ci + 1) * rows], rs[ci].clone(), group=self.group)
             for st in streams:
                 if st is not main:
                     main.wait_stream(st)
@@ -270,18 +279,18 @@ class MlpStack:
 
     __call__ = forward
 
-    def capture(self, x, residual):
+    def capture(self, x, residual, rows_local: bool = False):
         """Captures one ``forward(x, residual)`` into a CUDA graph (after one eager warm-up run, which also sets the kernels'
         attributes). ``x`` and ``residual`` are the graph's fixed input buffers: write new inputs into them, then
         ``replay()``. With tensor parallelism the all-reduces and both row-chunk streams are part of the graph, so a step
         costs one launch on the host: at 4-8 GPUs the per-layer kernels are too short for Python to keep up otherwise."""
         import torch
 
-        self.forward(x, residual)
+        self.forward(x, residual, rows_local) if rows_local else self.forward(x, residual)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            out = self.forward(x, residual)
+            out = self.forward(x, residual, rows_local) if rows_local else self.forward(x, residual)
         return CapturedStack(graph, x, residual, out)
 
     def weight_bytes(self) -> int:
