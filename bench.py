@@ -42,9 +42,15 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
-    ap.add_argument("--comm", default=None, choices=["all_reduce", "scatter_gather"],
+    ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "scatter_gather"],
                     help="tensor-parallel exchange per block (default all_reduce; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
                          "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
+    ap.add_argument("--ar-ctas", type=int, default=16, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce also the all-reduce kernel's CTAs")
+    ap.add_argument("--peer-path", default="multicast_store", choices=["multicast_store", "switch_reduce", "peer_loads"],
+                    help="data path of peer_all_reduce: f32 sum over peer loads + multicast store (default), the switch's own reduction, or peer loads only")
+    ap.add_argument("--sweep-exchange", action="store_true",
+                    help="N > 1, instead of the benchmark: time the step (one CUDA graph) for every exchange mode / row-chunk count / CTA count over the "
+                         "same weights, and a bare 64 MiB all-reduce by NCCL and by the peer kernel's three paths; one JSON line (profiles/tp_exchange_modes_*)")
     ap.add_argument("--chunks", type=int, default=None, help="row chunks whose all-reduces overlap the other chunk's GEMMs (default: 2 when N > 1)")
     return ap.parse_args()
 
@@ -391,6 +397,66 @@ def run_single_kernel(name: str) -> None:
     print(json.dumps({"kernel": name, "launches": 3}))
 
 
+def exchange_sweep(args, torch, MLP, blocks, group, dev, rank, world, layers, m) -> None:
+    """Every exchange variant of the tensor-parallel step over the same weights: per variant the step is captured into one CUDA
+    graph and `--steps` replays are timed with CUDA events (max over ranks). Also the bare all-reduce of one [M, H] bf16 tensor."""
+    import torch.distributed as dist
+
+    from tilefish_b200.collective import PeerAllReduce
+
+    def timed(fn, n):
+        for _ in range(3):
+            fn()
+        dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            fn()
+        e.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / n], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t.item()), 4)
+
+    out = {"sweep": "tp exchange", "n_gpus": world, "layers": layers, "tokens": m, "bare_allreduce_ms": {}, "step_ms": {}}
+    n = m * H
+    x = torch.randn(n, device=dev).to(torch.bfloat16)
+    out["bare_allreduce_ms"]["nccl"] = timed(lambda: dist.all_reduce(x), 20)
+    for path in ("switch_reduce", "multicast_store", "peer_loads"):
+        for ctas in (16, 32, 64, 128):
+            peer = PeerAllReduce(2 * n, group, dev, channels=1, num_ctas=ctas, multicast=path != "peer_loads", reduce_in_switch=path == "switch_reduce")
+            v = peer.view(0, (n,))
+            v.copy_(x)
+            out["bare_allreduce_ms"][f"{peer.mode}/{ctas} CTAs"] = timed(lambda: peer.allreduce_(v), 20)
+            if peer.status():
+                out["bare_allreduce_ms"][f"{peer.mode}/{ctas} CTAs"] = "bounded wait gave up"
+            del peer, v
+    del x
+    g = torch.Generator().manual_seed(0)
+    x_dev = torch.randn((m, H), generator=g).to(torch.bfloat16).to(dev)
+    residual = torch.zeros((m, H), dtype=torch.float32, device=dev)
+    variants = [("all_reduce", 1, None, 16), ("all_reduce", 2, None, 16)]
+    for path in ("switch_reduce", "multicast_store"):
+        variants += [("peer_all_reduce", 1, path, 148), ("peer_all_reduce", 1, path, 64), ("peer_all_reduce", 2, path, 16), ("peer_all_reduce", 2, path, 32),
+                     ("peer_all_reduce", 2, path, 48)]
+    for comm, chunks, path, ctas in variants:
+        stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=ctas, peer_path=path or "multicast_store")
+        cap = stack.capture(x_dev, residual)
+
+        def step():
+            residual.zero_()
+            cap.replay()
+
+        key = f"{comm}" + (f"/{path}" if path else "") + f", {chunks} chunk(s), {ctas} CTAs left to the exchange"
+        out["step_ms"][key] = timed(step, args.steps)
+        if getattr(stack, "_peer", None) is not None and stack._peer.status():
+            out["step_ms"][key] = "bounded wait gave up"
+        del cap, stack
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+
+
 def run_ours(args) -> None:
     import torch
 
@@ -426,9 +492,15 @@ def run_ours(args) -> None:
         w_n = (1 + 0.1 * torch.randn(H, generator=g, device=dev)).to(torch.bfloat16)
         blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, FMT, rank=rank, world=world))
         del w_gu, w_d
+    if args.sweep_exchange:
+        if world < 2:
+            raise SystemExit("bench.py: --sweep-exchange needs --gpus >= 2")
+        exchange_sweep(args, torch, MLP, blocks, group, dev, rank, world, layers, m)
+        finish_ranks(world)
+        return
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
     comm = args.comm or "all_reduce"
-    stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm)
+    stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=args.ar_ctas, peer_path=args.peer_path)
     torch.cuda.synchronize()
 
     gx = torch.Generator().manual_seed(0)
@@ -458,7 +530,8 @@ def run_ours(args) -> None:
 
     gemm_events_enabled = [False]
     K.gemm_blockscaled = timed_gemm
-    launches_per_step = layers * 5 * stack.chunks  # rmsnorm, 2 x quantize, 2 x gemm per block and row chunk (nvfp4)
+    # rmsnorm, 2 x quantize, 2 x gemm per block and row chunk (nvfp4); with peer_all_reduce the exchange is this library's kernel too
+    launches_per_step = layers * (6 if (world > 1 and stack.comm == "peer_all_reduce") else 5) * stack.chunks
 
     def step():
         residual.zero_()
@@ -577,6 +650,8 @@ def run_ours(args) -> None:
                 "io": (f"each rank copies its own {m_io} rows; bytes are the job's total" if rows_local else "every rank copies the full tensors; bytes are per rank"),
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "gpu_launches": launches_per_step * args.steps,
+        "exchange": ({"kernel": "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas, "error_word": stack._peer.status()}
+                     if getattr(stack, "_peer", None) is not None else None),
         "roofline": roofline,
         "clocks": clocks,
     }

@@ -170,6 +170,28 @@ TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_s
                                      const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
                                      int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* stream);
 
+/* In-place bf16 sum all-reduce over the ranks of a tensor-parallel group, one call (one kernel) per rank, each on its own GPU.
+ * Replaces the cross-rank sum the reference leaves to the caller's framework; the MLP path's only exchange: partial results of
+ * the second GEMM (w_d split along K) summed over the ranks.
+ *   buffer_ptrs[world]  device addresses, valid ON THIS GPU, of every rank's data buffer (peer-mapped; entry `rank` is this
+ *            rank's own). All ranks use the same offset and count: symmetric memory.
+ *   state_ptrs[world]   the same for every rank's 128-byte state block, zeroed once by the host before the first call and
+ *            never touched by it again. Calls that may run at the same time on one GPU need separate state blocks.
+ *   multicast_ptr   0, or the address of a multicast (NVSwitch) mapping of the data buffers. With 0: plain peer loads,
+ *            reduce-scatter then all-gather. Else each rank sums its slice over peer loads and multimem.st writes the result to all
+ *            ranks, or, with
+ *   reduce_in_switch   nonzero, the switch itself sums (multimem.ld_reduce): half the bytes received per GPU, but the switch's
+ *            bf16 result is only within one bf16 step of the exact sum, not always the nearest value. The other two paths sum
+ *            in f32 in rank order and round to nearest even once.
+ *   offset_bytes (multiple of 16), count (bf16 elements, multiple of 8 * world)   the range of the buffers that is summed
+ *   num_ctas   CTAs of the kernel (1..148); they must all be resident at once, so leave that many SMs to it when other
+ *            kernels run beside it (tf_set_sm_margin)
+ * Every rank must make the same sequence of calls on a state block. The
+ * waits on the peers are bounded (two seconds): a rank that never arrives makes the kernel return with a nonzero error word
+ * (the 64-bit word at byte 88 of the state block; the state blocks must then be zeroed again on all ranks). */
+TF_API tf_status tf_allreduce_bf16(const uint64_t* buffer_ptrs, const uint64_t* state_ptrs, uint64_t multicast_ptr, int32_t reduce_in_switch,
+                                   int32_t rank, int32_t world, int64_t offset_bytes, int64_t count, int32_t num_ctas, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -70,10 +70,12 @@ def quantize_weights(w_n, w_gu, w_d, fmt: str, *, rank: int = 0, world: int = 1)
     return MlpWeights(w_n, gu, d)
 
 
-def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, scratch: Optional[dict] = None, out=None):
+def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, scratch: Optional[dict] = None, out=None, reduce=None):
     """One block: ``residual += x`` (f32, in place), returns bf16 [M, H] = mlp(rmsnorm(residual) * w_n).
 
     ``group``: a torch.distributed process group for the tensor-parallel all-reduce (None = single GPU).
+    ``reduce``: instead of ``group``, a callable that sums the second GEMM's partial result over the ranks in place
+    (``PeerAllReduce.allreduce_`` with ``out`` a view of its symmetric buffer).
     ``scratch``: a dict reused between calls for the two-float amax buffer (nvfp4).
     """
     import torch
@@ -94,7 +96,9 @@ def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, 
         _, hq = K.residual_add_rmsnorm(x, residual, w.w_n, eps, quantize_to=fmt, want_bf16=False)
         _, aq = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", quantize_out=True, want_bf16=False)  # `a` never exists in bf16
     y = K.gemm_blockscaled(aq, w.w_d, out=out)
-    if group is not None:
+    if reduce is not None:
+        reduce(y)
+    elif group is not None:
         import torch.distributed as dist
 
         dist.all_reduce(y, group=group)
@@ -158,18 +162,26 @@ class MlpStack:
     """
 
     def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16,
-                 comm: str = "all_reduce") -> None:
-        """``comm``: "all_reduce" (one bf16 all-reduce per block) or "scatter_gather" (rows of the normalisation sharded over
-        the ranks: reduce-scatter of the partial results + all-gather of the quantized activations; see
-        ``decoder_block_row_sharded``)."""
+                 comm: str = "all_reduce", peer_path: str = "multicast_store") -> None:
+        """``comm``: "all_reduce" (one NCCL bf16 all-reduce per block), "peer_all_reduce" (the same exchange by this package's
+        own kernel over symmetric memory, see ``collective.PeerAllReduce``; ``sm_margin`` is also its CTA count) or
+        "scatter_gather" (rows of the normalisation sharded over the ranks: reduce-scatter of the partial results +
+        all-gather of the quantized activations; see ``decoder_block_row_sharded``)."""
         self.layers = layers
         self.eps = eps
         self.group = group
         self.chunks = chunks if group is not None else 1
         self.sm_margin = sm_margin
         self.comm = comm if group is not None else "all_reduce"
-        if self.comm not in ("all_reduce", "scatter_gather"):
+        if self.comm not in ("all_reduce", "peer_all_reduce", "scatter_gather"):
             raise TilefishPreconditionError(f"unknown comm mode {comm!r}", kind="argument", arg="comm")
+        self._peer = None
+        # how the peer all-reduce moves data: "multicast_store" (sum over peer loads, result written through the switch),
+        # "switch_reduce" (the switch also sums: fewer bytes, last bit not always nearest) or "peer_loads" (no multicast at all)
+        if peer_path not in ("multicast_store", "switch_reduce", "peer_loads"):
+            raise TilefishPreconditionError(f"unknown peer_path {peer_path!r}", kind="argument", arg="peer_path")
+        self._peer_path = peer_path
+        self._last_reduce = None
         self._scratch: List[dict] = [{} for _ in range(max(1, self.chunks))]
         self._streams = None
 
@@ -180,6 +192,8 @@ class MlpStack:
             return self._forward_row_sharded(x, residual, rows_local)
         if rows_local:
             raise TilefishPreconditionError("rows_local needs comm='scatter_gather'", kind="argument", arg="rows_local")
+        if self.comm == "peer_all_reduce" and self._peer_for(x) is not None:
+            return self._forward_peer(x, residual)
         if self.chunks <= 1:
             for w in self.layers:
                 x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
@@ -219,6 +233,84 @@ class MlpStack:
                 main.wait_stream(s)
         finally:
             N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
+        return out
+
+    def _peer_for(self, x):
+        """The symmetric buffer for activations of ``x``'s size (collective on first use; None for a single-rank group)."""
+        import torch.distributed as dist
+
+        if dist.get_world_size(self.group) < 2:
+            return None
+        need = x.numel() * 2
+        if self._peer is None or self._peer.nbytes < need:
+            from .collective import PeerAllReduce
+
+            self._peer = PeerAllReduce(need, self.group, x.device, channels=max(1, self.chunks), num_ctas=max(1, self.sm_margin), multicast=self._peer_path != "peer_loads",
+                                       reduce_in_switch=self._peer_path == "switch_reduce")
+        return self._peer
+
+    def _forward_peer(self, x, residual):
+        """All-reduce by this package's kernel: every chunk's second GEMM writes into the chunk's rows of the symmetric buffer,
+        the kernel sums them in place and the next block reads them there. The all-reduce kernels of the chunks are chained by
+        events into one order that is the same on every rank, so two of them never wait for each other crosswise."""
+        import torch
+
+        from . import _native as N
+
+        peer = self._peer
+        m, h = x.shape
+        c = max(1, self.chunks)
+        world = peer.world
+        unit = 128
+        while (unit * h) % (8 * world):
+            unit *= 2
+        bounds = [min(m, (m * i // c + unit - 1) // unit * unit) if 0 < i < c else m * i // c for i in range(c + 1)]
+        spans = [(bounds[i], bounds[i + 1]) for i in range(c) if bounds[i + 1] > bounds[i]]
+        if any(((b - a) * h) % (8 * world) for a, b in spans):
+            raise TilefishPreconditionError(f"peer_all_reduce: a chunk of [{m}, {h}] is not a multiple of {8 * world} elements", kind="divisible", arg="x")
+        multi = len(spans) > 1
+        if multi and (self._streams is None or len(self._streams) < len(spans)):
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in spans]
+        main = torch.cuda.current_stream()
+        streams = self._streams[:len(spans)] if multi else [main]
+        out = torch.empty_like(x)
+        views = [peer.view(a * h * 2, (b - a, h)) for a, b in spans]
+        self._last_reduce = None
+
+        def reducer(ci):
+            def reduce(y):
+                st = torch.cuda.current_stream()
+                if self._last_reduce is not None:
+                    st.wait_event(self._last_reduce)
+                peer.allreduce_(y, channel=ci)
+                ev = torch.cuda.Event()
+                ev.record(st)
+                self._last_reduce = ev
+
+            return reduce
+
+        if multi:
+            N.check(N.load().tf_set_sm_margin(self.sm_margin), "tf_set_sm_margin")
+        try:
+            xs = [x[a:b] for a, b in spans]
+            rs = [residual[a:b] for a, b in spans]
+            for s in streams:
+                if s is not main:
+                    s.wait_stream(main)
+            for w in self.layers:
+                for ci in range(len(spans)):
+                    with torch.cuda.stream(streams[ci]):
+                        xs[ci] = decoder_block(xs[ci], rs[ci], w, self.eps, scratch=self._scratch[ci], out=views[ci], reduce=reducer(ci))
+            for ci, (a, b) in enumerate(spans):
+                with torch.cuda.stream(streams[ci]):
+                    out[a:b].copy_(xs[ci])
+            for s in streams:
+                if s is not main:
+                    main.wait_stream(s)
+        finally:
+            if multi:
+                N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
+            self._last_reduce = None
         return out
 
     def _forward_row_sharded(self, x, residual, rows_local: bool = False):
