@@ -40,7 +40,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=LAYERS, help="development only: fewer layers (the line then says so)")
     ap.add_argument("--tokens", type=int, default=M_TOKENS, help="development only")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
-    ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm"],
+    ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "scatter_gather"],
                     help="tensor-parallel exchange per block (default all_reduce; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
@@ -380,6 +380,19 @@ def run_single_kernel(name: str) -> None:
         out = torch.empty((m, f), dtype=torch.bfloat16, device="cuda")
         amax = torch.zeros(1, device="cuda")
         fn = lambda: K.gemm_blockscaled(qa, qb, epilogue="silu_gate", out=out, amax_out=amax)  # noqa: E731
+    elif name == "decode":  # two blocks of the stack at M = 64 (weights stream once per block): the launch list of the decode path
+        from tilefish_b200 import mlp as MLP
+
+        blocks = []
+        for layer in range(2):
+            w_gu = (torch.randn((2 * F, H), generator=g, device="cuda") * H**-0.5).to(torch.bfloat16)
+            w_d = (torch.randn((H, F), generator=g, device="cuda") * F**-0.5).to(torch.bfloat16)
+            blocks.append(MLP.quantize_weights(torch.ones(H, dtype=torch.bfloat16, device="cuda"), w_gu, w_d, FMT))
+            del w_gu, w_d
+        stack = MLP.MlpStack(blocks)
+        x = torch.randn((64, H), generator=g, device="cuda").to(torch.bfloat16)
+        res = torch.zeros((64, H), device="cuda")
+        fn = lambda: stack(x, res)  # noqa: E731
     elif name == "rmsnorm":
         x = torch.randn((8192, H), generator=g, device="cuda").to(torch.bfloat16)
         res = torch.zeros((8192, H), device="cuda")

@@ -54,3 +54,25 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
     monkeypatch.setattr(_native, "LIB_PATH", str(tmp_path / "nope.so"))
     with pytest.raises(TilefishRuntimeError, match="no CPU or Triton fallback"):
         _native.load()
+
+
+def test_allreduce_refuses_bad_arguments_before_any_launch():
+    """tf_allreduce_bf16 decides its argument errors on the host: this runs without a GPU."""
+    import ctypes
+
+    from tilefish_b200 import _native
+
+    if not os.path.exists(_native.LIB_PATH):
+        pytest.skip("library not built here (python tilefish_b200/csrc/build.py)")
+    lib = _native.load()
+    ptrs = (ctypes.c_uint64 * 2)(0x1000, 0x2000)
+    call = lambda *a: lib.tf_allreduce_bf16(*a)  # noqa: E731
+    assert call(None, ptrs, 0, 0, 0, 2, 0, 16, 8, None) != 0                 # no buffer table
+    assert call(ptrs, ptrs, 0, 0, 0, 1, 0, 16, 8, None) != 0                 # a single rank has nothing to exchange
+    assert call(ptrs, ptrs, 0, 0, 2, 2, 0, 16, 8, None) != 0                 # rank outside the group
+    assert call(ptrs, ptrs, 0, 0, 0, 2, 0, 24, 8, None) != 0                 # count not a multiple of 8 x world
+    assert call(ptrs, ptrs, 0, 0, 0, 2, 8, 16, 8, None) != 0                 # offset not a multiple of 16
+    assert call(ptrs, ptrs, 0, 0, 0, 2, 0, 16, 0, None) != 0                 # no CTAs
+    assert b"num_ctas" in lib.tf_last_error()
+    bad = (ctypes.c_uint64 * 2)(0x1000, 0x2004)
+    assert call(bad, ptrs, 0, 0, 0, 2, 0, 16, 8, None) != 0                  # unaligned peer pointer

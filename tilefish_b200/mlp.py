@@ -70,24 +70,26 @@ def quantize_weights(w_n, w_gu, w_d, fmt: str, *, rank: int = 0, world: int = 1)
     return MlpWeights(w_n, gu, d)
 
 
-def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, scratch: Optional[dict] = None, out=None, reduce=None):
+def decoder_block(x, residual, w: MlpWeights, eps: float = 1e-6, *, group=None, scratch: Optional[dict] = None, out=None, reduce=None, amax=None):
     """One block: ``residual += x`` (f32, in place), returns bf16 [M, H] = mlp(rmsnorm(residual) * w_n).
 
     ``group``: a torch.distributed process group for the tensor-parallel all-reduce (None = single GPU).
     ``reduce``: instead of ``group``, a callable that sums the second GEMM's partial result over the ranks in place
     (``PeerAllReduce.allreduce_`` with ``out`` a view of its symmetric buffer).
     ``scratch``: a dict reused between calls for the two-float amax buffer (nvfp4).
+    ``amax``: instead, two f32 on the device that the caller has zeroed (a stack zeroes one buffer for all its blocks at once).
     """
     import torch
 
     fmt = w.fmt
     if fmt == "nvfp4":
-        if scratch is None:
-            scratch = {}
-        amax = scratch.get("amax")
-        if amax is None or amax.device != x.device:
-            amax = scratch["amax"] = torch.zeros(2, dtype=torch.float32, device=x.device)
-        amax.zero_()
+        if amax is None:
+            if scratch is None:
+                scratch = {}
+            amax = scratch.get("amax")
+            if amax is None or amax.device != x.device:
+                amax = scratch["amax"] = torch.zeros(2, dtype=torch.float32, device=x.device)
+            amax.zero_()
         h = K.residual_add_rmsnorm(x, residual, w.w_n, eps, amax_out=amax[0:1])
         hq = K.quantize(h, fmt, amax=amax[0:1])
         a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", amax_out=amax[1:2])
@@ -185,6 +187,18 @@ class MlpStack:
         self._scratch: List[dict] = [{} for _ in range(max(1, self.chunks))]
         self._streams = None
 
+    def _amax_slots(self, ci: int, device):
+        """Two zeroed f32 per block for chunk ``ci`` (nvfp4 global scales): one buffer, one memset per forward."""
+        import torch
+
+        if not self.layers or self.layers[0].fmt != "nvfp4":
+            return [None] * len(self.layers)
+        buf = self._scratch[ci].get("amax_all")
+        if buf is None or buf.device != device or buf.numel() != 2 * len(self.layers):
+            buf = self._scratch[ci]["amax_all"] = torch.zeros(2 * len(self.layers), dtype=torch.float32, device=device)
+        buf.zero_()
+        return [buf[2 * i:2 * i + 2] for i in range(len(self.layers))]
+
     def forward(self, x, residual, rows_local: bool = False):
         """``rows_local`` (scatter_gather only): ``x`` and ``residual`` are THIS RANK'S rows ([M / n, H]) and so is the result: no
         rank ever holds the other ranks' tokens outside the GEMMs, and the job's input and output cross PCIe once in total."""
@@ -195,8 +209,9 @@ class MlpStack:
         if self.comm == "peer_all_reduce" and self._peer_for(x) is not None:
             return self._forward_peer(x, residual)
         if self.chunks <= 1:
-            for w in self.layers:
-                x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
+            slots = self._amax_slots(0, x.device)
+            for w, am in zip(self.layers, slots):
+                x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0], amax=am)
             return x
         return self._forward_chunked(x, residual)
 
@@ -211,8 +226,9 @@ class MlpStack:
         bounds = [min(b, m) for b in bounds]
         spans = [(bounds[i], bounds[i + 1]) for i in range(c) if bounds[i + 1] > bounds[i]]
         if len(spans) < 2:
-            for w in self.layers:
-                x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0])
+            slots = self._amax_slots(0, x.device)
+            for w, am in zip(self.layers, slots):
+                x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0], amax=am)
             return x
         if self._streams is None or len(self._streams) < len(spans):
             self._streams = [torch.cuda.Stream(device=x.device) for _ in spans]
@@ -225,10 +241,15 @@ class MlpStack:
             for s in self._streams[:len(spans)]:
                 s.wait_stream(main)
             last = len(self.layers) - 1
+            slots = []
+            for ci in range(len(spans)):
+                with torch.cuda.stream(self._streams[ci]):
+                    slots.append(self._amax_slots(ci, x.device))
             for li, w in enumerate(self.layers):
                 for ci, (a, b) in enumerate(spans):
                     with torch.cuda.stream(self._streams[ci]):
-                        xs[ci] = decoder_block(xs[ci], rs[ci], w, self.eps, group=self.group, scratch=self._scratch[ci], out=out[a:b] if li == last else None)
+                        xs[ci] = decoder_block(xs[ci], rs[ci], w, self.eps, group=self.group, scratch=self._scratch[ci], out=out[a:b] if li == last else None,
+                                               amax=slots[ci][li])
             for s in self._streams[:len(spans)]:
                 main.wait_stream(s)
         finally:
@@ -297,10 +318,14 @@ class MlpStack:
             for s in streams:
                 if s is not main:
                     s.wait_stream(main)
-            for w in self.layers:
+            slots = []
+            for ci in range(len(spans)):
+                with torch.cuda.stream(streams[ci]):
+                    slots.append(self._amax_slots(ci, x.device))
+            for li, w in enumerate(self.layers):
                 for ci in range(len(spans)):
                     with torch.cuda.stream(streams[ci]):
-                        xs[ci] = decoder_block(xs[ci], rs[ci], w, self.eps, scratch=self._scratch[ci], out=views[ci], reduce=reducer(ci))
+                        xs[ci] = decoder_block(xs[ci], rs[ci], w, self.eps, scratch=self._scratch[ci], out=views[ci], reduce=reducer(ci), amax=slots[ci][li])
             for ci, (a, b) in enumerate(spans):
                 with torch.cuda.stream(streams[ci]):
                     out[a:b].copy_(xs[ci])
