@@ -51,6 +51,8 @@ def parse_args():
     ap.add_argument("--sweep-exchange", action="store_true",
                     help="N > 1, instead of the benchmark: time the step (one CUDA graph) for every exchange mode / row-chunk count / CTA count over the "
                          "same weights, and a bare 64 MiB all-reduce by NCCL and by the peer kernel's three paths; one JSON line (profiles/tp_exchange_modes_*)")
+    ap.add_argument("--pdl", type=int, default=None, choices=[0, 1],
+                    help="programmatic dependent launch of this library's kernels (tf_set_programmatic_launch); default: the library's default")
     ap.add_argument("--chunks", type=int, default=None, help="row chunks whose all-reduces overlap the other chunk's GEMMs (default: 2 when N > 1)")
     return ap.parse_args()
 
@@ -365,13 +367,15 @@ def extras_mlp(torch, K, pk):
     return out
 
 
-def run_single_kernel(name: str) -> None:
+def run_single_kernel(name: str, pdl=None) -> None:
     """Three launches of one kernel on a case of a few hundred MB (larger than L2, small enough for a multi-pass ncu capture)."""
     import torch
 
     from tilefish_b200 import kernels as K
 
     K.require_cuda()
+    if pdl is not None:
+        K.set_programmatic_launch(bool(pdl))
     g = torch.Generator(device="cuda").manual_seed(0)
     if name == "gemm1":  # the dominant kernel at half the benchmark's width: M = 4096, F = 14336, K = 8192, nvfp4, SiLU-gate epilogue
         m, f, k = 4096, F // 2, H
@@ -493,6 +497,8 @@ def run_ours(args) -> None:
     from tilefish_b200 import mlp as MLP
 
     K.require_cuda()
+    if args.pdl is not None:
+        K.set_programmatic_launch(bool(args.pdl))
     pk = peaks()
     layers, m = args.layers, args.tokens
 
@@ -691,7 +697,7 @@ def main() -> None:
         run_reference(args, rank)
         return
     if args.kernel:
-        run_single_kernel(args.kernel)
+        run_single_kernel(args.kernel, args.pdl)
         return
     run_ours(args)
 

@@ -75,6 +75,13 @@ TF_API tf_status tf_device_status(int32_t* status, int32_t* detail);
  * 0 restores the default. No counterpart in the reference (its GEMM is cuBLASLt's `sm_count_target`, python/src/tilefish/_cublaslt.py). */
 TF_API tf_status tf_set_sm_margin(int32_t sms);
 
+/* Programmatic dependent launch for this library's kernels (off by default; process-wide). On: the quantize, rmsnorm, GEMM and
+ * split-K reduction kernels are launched so that each may be scheduled while the kernel before it on the stream is still
+ * draining; each waits (griddepcontrol.wait) for that kernel to complete before its first access to global memory, so results
+ * are unchanged. It hides launch latency and kernel set-up in chains of short kernels (small M, decode, many GPUs). No
+ * counterpart in the reference. */
+TF_API tf_status tf_set_programmatic_launch(int32_t enabled);
+
 /* Failure-detection self-test (no counterpart in the reference): launches one thread that waits on a barrier nothing will ever
  * signal, with the given limit. The wait gives up, records TF_ERR_DEVICE_TIMEOUT (detail 9 * 65536) in the device status word
  * and the kernel returns normally; the context stays usable. Exercises the mechanism every wait of the GEMM relies on. */

@@ -32,11 +32,21 @@ int sm_count() {
   return cached;
 }
 
+static int g_programmatic_launch = 0;
+bool programmatic_launch_enabled() { return g_programmatic_launch != 0; }
+void set_programmatic_launch(bool on) { g_programmatic_launch = on ? 1 : 0; }
+
 }  // namespace tf
 
 using namespace tf;
 
 extern "C" {
+
+tf_status tf_set_programmatic_launch(int32_t enabled) {
+  tf::clear_error();
+  tf::set_programmatic_launch(enabled != 0);
+  return TF_OK;
+}
 
 const char* tf_version(void) { return "tilefish_b200 0.1.0 (sm_100a)"; }
 const char* tf_last_error(void) { return g_last_error.c_str(); }

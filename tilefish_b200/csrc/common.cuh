@@ -32,8 +32,36 @@ int sm_count();
   } while (0)
 #define TF_LAUNCH_CHECK() TF_CUDA(cudaGetLastError())
 
+// Programmatic dependent launch (tf_set_programmatic_launch): a kernel launched through launch_dependent() may be scheduled
+// while the kernel before it on the stream is still draining, so that its launch latency and set-up overlap that tail. Every
+// kernel launched this way executes griddep_wait() before its first access to global memory, which blocks until the previous
+// kernel has completed and its writes are visible. Off: a plain stream-ordered launch.
+bool programmatic_launch_enabled();
+void set_programmatic_launch(bool on);
+
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = programmatic_launch_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // ---- device: bit-level conversions -----------------------------------------------------------------------------------
 #ifdef __CUDACC__
+
+// Wait for the previous kernel on the stream (returns at once in a plain launch); let the next one be scheduled early.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 __device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
 __device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }

@@ -462,6 +462,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
                                                             const float* b_gs, uint16_t* __restrict__ out, int64_t ldo, float* __restrict__ residual,
                                                             unsigned int* __restrict__ out_amax, uint8_t* __restrict__ q_codes,
                                                             uint8_t* __restrict__ q_scales, int a_gs_rows) {
+  griddep_launch_dependents();
+  griddep_wait();
   const float alpha0 = (a_gs && b_gs) ? __fmul_rn(__ldg(a_gs), __ldg(b_gs)) : 1.0f;
   const int nvec = n >> 3;
   const int64_t total = (int64_t)m * nvec;
@@ -551,6 +553,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
   volatile int* abort_flag = reinterpret_cast<volatile int*>(smem_gen + (abort_slot - smem_base));
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  griddep_launch_dependents();  // the next kernel on the stream may be scheduled; it waits for this one before touching memory
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -570,6 +573,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  griddep_wait();  // barriers and tensor memory are set up; nothing of global memory was touched before the previous kernel is done
 
   if (warp == 0) {
     // ---------------- producer ----------------
@@ -1085,8 +1089,7 @@ static tf_status launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmP
   p.n_blocks = (p.n + out_cols - 1) / out_cols;
   p.num_tiles = p.m_blocks * p.n_blocks * p.splits;
   const int grid = p.num_tiles < gemm_sms() ? p.num_tiles : gemm_sms();
-  kernel<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(ta, tb, p);
-  TF_LAUNCH_CHECK();
+  TF_CUDA(launch_dependent(kernel, dim3(grid), dim3(kGemmThreads), (size_t)Cfg::kSmemBytes, stream, ta, tb, p));
   return TF_OK;
 }
 
@@ -1169,7 +1172,8 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
     const float* ags = FMT == TF_FMT_NVFP4 ? p.a_gs : nullptr;
     const float* bgs = FMT == TF_FMT_NVFP4 ? p.b_gs : nullptr;
 #define TF_REDUCE(EPI_, Q_) \
-  splitk_reduce_kernel<EPI_, Q_><<<grid, 256, 0, stream>>>(p.ws, sp.splits, p.m, n_out, p.n_rows_b, ags, bgs, p.out, p.ldo, residual, amax, p.q_codes, p.q_scales, p.a_gs_rows)
+  launch_dependent(splitk_reduce_kernel<EPI_, Q_>, dim3(grid), dim3(256), 0, stream, (const float*)p.ws, (int)sp.splits, (int)p.m, (int)n_out, (int)p.n_rows_b, ags, bgs, \
+                   p.out, p.ldo, residual, amax, p.q_codes, p.q_scales, (int)p.a_gs_rows)
     const int qf = p.q_codes ? FMT : -1;
     if (epilogue == TF_EPI_SILU_GATE) {
       if (qf == TF_FMT_MXFP8) TF_REDUCE(TF_EPI_SILU_GATE, TF_FMT_MXFP8);

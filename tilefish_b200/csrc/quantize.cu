@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
                                                                       int swizzled, const float* __restrict__ gs_ptr, float* __restrict__ gs_out) {
   const int tpr = blockDim.x;
   const int nvec = (int)(k >> 4);
+  griddep_launch_dependents();
+  griddep_wait();
   float gs = (FMT == TF_FMT_NVFP4) ? __ldg(gs_ptr) : 0.0f;
   if (FMT == TF_FMT_NVFP4 && gs_out != nullptr) {
     gs = __fdiv_rn(gs, 2688.0f);
@@ -155,9 +157,8 @@ static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64
   const int64_t cap = (int64_t)sm_count() * 8;
   dim3 block(tpr, rpb);
   dim3 grid((unsigned)(blocks_needed < cap ? blocks_needed : cap));
-  quantize_rows_kernel<FMT><<<grid, block, 0, stream>>>(static_cast<const uint8_t*>(x), m, k, ldx, static_cast<uint8_t*>(codes),
-                                                        static_cast<uint8_t*>(scales), layout == TF_SCALES_SWIZZLED, gs, gs_out);
-  TF_LAUNCH_CHECK();
+  TF_CUDA(launch_dependent(quantize_rows_kernel<FMT>, grid, block, 0, stream, static_cast<const uint8_t*>(x), m, k, ldx, static_cast<uint8_t*>(codes),
+                           static_cast<uint8_t*>(scales), (int)(layout == TF_SCALES_SWIZZLED), gs, gs_out));
   return TF_OK;
 }
 

@@ -22,6 +22,8 @@ __global__ void __launch_bounds__(512) residual_add_rmsnorm_kernel(const uint4* 
   __shared__ float row_rstd;
   const int nvec = d >> 3;
   const int tid = threadIdx.x, nthreads = blockDim.x;
+  griddep_launch_dependents();
+  griddep_wait();
   const float gs = (QFMT == TF_FMT_NVFP4) ? __ldg(q_gs_ptr) : 0.0f;
   const float inv_t = (QFMT == TF_FMT_NVFP4 && gs != 0.0f) ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
 
@@ -104,10 +106,10 @@ template <int VPT>
 static void launch_vpt(int qfmt, dim3 grid, dim3 block, cudaStream_t s, const uint4* x, float4* res, const uint4* w, uint4* out, int64_t m, int d,
                        float eps, float inv_d, uint8_t* qc, uint8_t* qs, int qsw, const float* qgs, unsigned int* amax) {
   switch (qfmt) {
-    case TF_FMT_MXFP8: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP8><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
-    case TF_FMT_MXFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
-    case TF_FMT_NVFP4: residual_add_rmsnorm_kernel<VPT, TF_FMT_NVFP4><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
-    default: residual_add_rmsnorm_kernel<VPT, -1><<<grid, block, 0, s>>>(x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    case TF_FMT_MXFP8: launch_dependent(residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP8>, grid, block, 0, s, x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    case TF_FMT_MXFP4: launch_dependent(residual_add_rmsnorm_kernel<VPT, TF_FMT_MXFP4>, grid, block, 0, s, x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    case TF_FMT_NVFP4: launch_dependent(residual_add_rmsnorm_kernel<VPT, TF_FMT_NVFP4>, grid, block, 0, s, x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
+    default: launch_dependent(residual_add_rmsnorm_kernel<VPT, -1>, grid, block, 0, s, x, res, w, out, m, d, eps, inv_d, qc, qs, qsw, qgs, amax); break;
   }
 }
 

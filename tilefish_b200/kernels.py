@@ -280,6 +280,12 @@ def silu_gate(t, up=None, *, out=None, stream=None):
     return out
 
 
+def set_programmatic_launch(enabled: bool) -> None:
+    """Process-wide: launch this library's kernels as programmatic dependents (each may be scheduled while its predecessor on
+    the stream drains, and waits for it before touching memory). Same results; hides launch latency in chains of short kernels."""
+    N.check(N.load().tf_set_programmatic_launch(1 if enabled else 0), "tf_set_programmatic_launch")
+
+
 def gemm_workspace_bytes(m: int, n: int, k: int, fmt: str, epilogue: str = "none") -> int:
     return int(N.load().tf_gemm_workspace_bytes(m, n, k, FORMATS[fmt], EPILOGUES[epilogue]))
 
