@@ -94,7 +94,13 @@ def test_gemm_silu_gate_epilogue(K, fmt, m, f, k):
     assert frac == 0.0
     # and it equals the unfused pair of kernels on the same GEMM result up to that result's own rounding
     unfused = K.silu_gate(K.gemm_blockscaled(K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt)))
-    assert torch.equal(unfused, out), "fused epilogue must reproduce gemm -> bf16 -> silu_gate bit for bit"
+    if K.gemm_workspace_bytes(m, f, k, fmt, "silu_gate") == 0 and K.gemm_workspace_bytes(m, 2 * f, k, fmt) == 0:
+        assert torch.equal(unfused, out), "fused epilogue must reproduce gemm -> bf16 -> silu_gate bit for bit"
+    else:
+        # small M: either call may cut K into ranges (its own choice per epilogue), which changes the order of the f32 sums
+        d = (unfused.float() - out.float()).abs()
+        assert float(d.max()) <= TOL * float(t.float().abs().max()) * gain
+        assert float((d > 0).float().mean()) < 0.02
     no_device_timeout()
 
 
@@ -156,8 +162,8 @@ def test_gemm_refusals(K):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
-@pytest.mark.parametrize("m,n,k,epi", [(1, 2560, 3072, "none"), (16, 6144, 2560, "none"), (64, 1024, 8192, "none"), (32, 1536, 2560, "silu_gate"),
-                                       (40, 512, 4096, "residual")])
+@pytest.mark.parametrize("m,n,k,epi", [(1, 2560, 8192, "none"), (16, 6144, 8192, "none"), (64, 1024, 8192, "none"), (32, 1536, 2560, "silu_gate"),
+                                       (40, 512, 4096, "residual"), (130, 1024, 4096, "residual"), (200, 512, 8192, "silu_gate")])
 def test_gemm_small_m_takes_the_split_k_path(K, fmt, m, n, k, epi):
     """Few output tiles and a long K: the problem is cut along K into an f32 workspace and reduced by a second kernel. Same
     oracle, same bound; the partial sums are added in split order, so two runs give identical bytes."""

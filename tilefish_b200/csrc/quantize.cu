@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
   float gs = (FMT == TF_FMT_NVFP4) ? __ldg(gs_ptr) : 0.0f;
   if (FMT == TF_FMT_NVFP4 && gs_out != nullptr) {
     gs = __fdiv_rn(gs, 2688.0f);
-    if (blockIdx.x == 0 && threadIdx.x == 0 && threadIdx.y == 0) gs_out[0] = gs;
+    if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && threadIdx.y == 0) gs_out[0] = gs;
   }
   const float inv_t = (FMT == TF_FMT_NVFP4 && gs != 0.0f) ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
   const int64_t row_stride = (int64_t)gridDim.x * blockDim.y;
@@ -41,7 +41,12 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
     const int64_t row = row_base + threadIdx.y;
     const bool row_ok = row < m;
     const uint8_t* xr = x + (row_ok ? row : 0) * ldx * 2;
-    for (int base = 0; base < nvec; base += kQuantUnroll * tpr) {  // kQuantUnroll 256-bit loads in flight per thread
+    // gridDim.y cuts the row into segments of whole rounds (few, long rows: more CTAs than row blocks)
+    const int rounds = (nvec + kQuantUnroll * tpr - 1) / (kQuantUnroll * tpr);
+    const int rounds_per_seg = (rounds + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int base_begin = (int)blockIdx.y * rounds_per_seg * kQuantUnroll * tpr;
+    const int base_end = min(nvec, base_begin + rounds_per_seg * kQuantUnroll * tpr);
+    for (int base = base_begin; base < base_end; base += kQuantUnroll * tpr) {  // kQuantUnroll 256-bit loads in flight per thread
       uint32_t v[kQuantUnroll][8];
       bool has[kQuantUnroll];
 #pragma unroll
@@ -157,6 +162,11 @@ static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64
   const int64_t cap = (int64_t)sm_count() * 8;
   dim3 block(tpr, rpb);
   dim3 grid((unsigned)(blocks_needed < cap ? blocks_needed : cap));
+  const int64_t rounds = ((k >> 4) + kQuantUnroll * tpr - 1) / (kQuantUnroll * tpr);
+  if (blocks_needed < 2 * sm_count() && rounds > 1) {  // few long rows: cut them into segments so that every SM gets work
+    const int64_t want = (2 * sm_count() + blocks_needed - 1) / blocks_needed;
+    grid.y = (unsigned)(want < rounds ? want : rounds);
+  }
   TF_CUDA(launch_dependent(quantize_rows_kernel<FMT>, grid, block, 0, stream, static_cast<const uint8_t*>(x), m, k, ldx, static_cast<uint8_t*>(codes),
                            static_cast<uint8_t*>(scales), (int)(layout == TF_SCALES_SWIZZLED), gs, gs_out));
   return TF_OK;
