@@ -43,11 +43,12 @@ def parse_args():
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "scatter_gather"],
-                    help="tensor-parallel exchange per block (default all_reduce; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
+                    help="tensor-parallel exchange per block (default: peer_all_reduce, this library's kernel, at 2 GPUs, NCCL all_reduce otherwise; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
                          "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
     ap.add_argument("--ar-ctas", type=int, default=16, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce also the all-reduce kernel's CTAs")
-    ap.add_argument("--peer-path", default="multicast_store", choices=["multicast_store", "switch_reduce", "peer_loads"],
-                    help="data path of peer_all_reduce: f32 sum over peer loads + multicast store (default), the switch's own reduction, or peer loads only")
+    ap.add_argument("--peer-path", default="switch_reduce", choices=["multicast_store", "switch_reduce", "peer_loads"],
+                    help="data path of peer_all_reduce: the switch's own reduction (default: fewest bytes; its bf16 sum is within one bf16 step of the exact sum, as "
+                         "NCCL's NVLS all-reduce), f32 sum over peer loads + multicast store (exact, rounded once), or peer loads only")
     ap.add_argument("--sweep-exchange", action="store_true",
                     help="N > 1, instead of the benchmark: time the step (one CUDA graph) for every exchange mode / row-chunk count / CTA count over the "
                          "same weights, and a bare 64 MiB all-reduce by NCCL and by the peer kernel's three paths; one JSON line (profiles/tp_exchange_modes_*)")
@@ -518,7 +519,9 @@ def run_ours(args) -> None:
         finish_ranks(world)
         return
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    comm = args.comm or "all_reduce"
+    # default exchange: this library's all-reduce kernel where it was measured faster than NCCL's (2 GPUs: 156.5 k against 148.5 k
+    # tokens/s), NCCL elsewhere (the kernel is tested on 2 GPUs only; pass --comm peer_all_reduce to use it at any N)
+    comm = args.comm or ("peer_all_reduce" if world == 2 else "all_reduce")
     stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=args.ar_ctas, peer_path=args.peer_path)
     torch.cuda.synchronize()
 
@@ -591,6 +594,16 @@ def run_ours(args) -> None:
             ms = float(t.item())
         return ms
 
+    exchange_note = None
+    if world > 1 and args.comm is None and stack.comm == "peer_all_reduce":
+        # the default picked this library's all-reduce: if its symmetric memory cannot be set up on this machine (every rank sees
+        # the same refusal), run the NCCL exchange instead and say so in the line
+        try:
+            step()
+        except Exception as e:  # noqa: BLE001
+            exchange_note = f"peer_all_reduce unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL all_reduce used"
+            stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm="all_reduce", sm_margin=args.ar_ctas)
+            launches_per_step = layers * 5 * stack.chunks
     for _ in range(max(args.warmup, 3)):
         step()
     use_graph = world > 1
@@ -669,6 +682,7 @@ def run_ours(args) -> None:
                 "io": (f"each rank copies its own {m_io} rows; bytes are the job's total" if rows_local else "every rank copies the full tensors; bytes are per rank"),
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "gpu_launches": launches_per_step * args.steps,
+        "exchange_note": exchange_note,
         "exchange": ({"kernel": "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas, "error_word": stack._peer.status()}
                      if getattr(stack, "_peer", None) is not None else None),
         "roofline": roofline,
