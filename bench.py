@@ -42,7 +42,7 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
-    ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "scatter_gather"],
+    ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "fused_exchange", "scatter_gather"],
                     help="tensor-parallel exchange per block (default: peer_all_reduce, this library's kernel, at 2 GPUs, NCCL all_reduce otherwise; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
                          "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
     ap.add_argument("--ar-ctas", type=int, default=16, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce also the all-reduce kernel's CTAs")
@@ -458,6 +458,8 @@ def exchange_sweep(args, torch, MLP, blocks, group, dev, rank, world, layers, m)
     for path in ("switch_reduce", "multicast_store"):
         variants += [("peer_all_reduce", 1, path, 148), ("peer_all_reduce", 1, path, 64), ("peer_all_reduce", 2, path, 16), ("peer_all_reduce", 2, path, 32),
                      ("peer_all_reduce", 2, path, 48)]
+        variants += [("fused_exchange", 1, path, 148), ("fused_exchange", 1, path, 64), ("fused_exchange", 2, path, 16), ("fused_exchange", 2, path, 32),
+                     ("fused_exchange", 2, path, 48)]
     for comm, chunks, path, ctas in variants:
         stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=ctas, peer_path=path or "multicast_store")
         cap = stack.capture(x_dev, residual)
@@ -553,7 +555,9 @@ def run_ours(args) -> None:
     gemm_events_enabled = [False]
     K.gemm_blockscaled = timed_gemm
     # rmsnorm, 2 x quantize, 2 x gemm per block and row chunk (nvfp4); with peer_all_reduce the exchange is this library's kernel too
-    launches_per_step = layers * (6 if (world > 1 and stack.comm == "peer_all_reduce") else 5) * stack.chunks
+    launches_per_step = layers * (6 if (world > 1 and stack.comm == "peer_all_reduce") else 4 if stack.comm == "fused_exchange" else 5) * stack.chunks
+    if stack.comm == "fused_exchange":  # per block and chunk: exchange (sum + rmsnorm + quantize + gather), gemm, quantize, gemm; one all-reduce at the end
+        launches_per_step += stack.chunks
 
     def step():
         residual.zero_()
@@ -683,7 +687,7 @@ def run_ours(args) -> None:
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "gpu_launches": launches_per_step * args.steps,
         "exchange_note": exchange_note,
-        "exchange": ({"kernel": "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas, "error_word": stack._peer.status()}
+        "exchange": ({"kernel": "tp_norm_exchange_kernel" if stack.comm == "fused_exchange" else "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas, "error_word": stack._peer.status()}
                      if getattr(stack, "_peer", None) is not None else None),
         "roofline": roofline,
         "clocks": clocks,

@@ -199,6 +199,27 @@ TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_s
 TF_API tf_status tf_allreduce_bf16(const uint64_t* buffer_ptrs, const uint64_t* state_ptrs, uint64_t multicast_ptr, int32_t reduce_in_switch,
                                    int32_t rank, int32_t world, int64_t offset_bytes, int64_t count, int32_t num_ctas, void* stream);
 
+/* The tensor-parallel exchange between two blocks of the MLP stack fused with the next block's residual_add_rmsnorm and the
+ * quantization of its output; one call (one kernel) per rank. With the normalisation sharded by rows, rank r sums ITS rows
+ * of the second GEMM's partial results over the ranks (f32 over peer loads in rank order, rounded to bf16 once; or in the
+ * switch with reduce_in_switch), adds them into its rows of the f32 residual stream, normalises them exactly as
+ * tf_residual_add_rmsnorm does, quantizes them exactly as tf_quantize_* does (nvfp4: with the global scale of the row
+ * block's own amax) and writes codes, swizzled scales and the global scale into EVERY rank's buffers, so that each rank
+ * holds the quantized activation of all rows for its first GEMM (tf_gemm_blockscaled with a_global_scale_rows = rows / world).
+ * No counterpart in the reference.
+ *   buffer_ptrs / state_ptrs / multicast_ptr / reduce_in_switch / rank / world / num_ctas   as tf_allreduce_bf16 (world may be 1)
+ *   partial_offset   byte offset, inside every rank's buffer, of the bf16 [rows_total, d] partial results
+ *   codes_offset, scales_offset, gs_offset   byte offsets of the outputs: codes [rows_total, d] (e4m3) or [rows_total, d/2]
+ *            (e2m1), swizzled scales of a [rows_total, d] tensor, f32 [world] global scales (nvfp4; 16-byte aligned)
+ *   rows_total (a multiple of 128 * world), d (a multiple of 128)
+ *   sum_peers   0: the partial region already holds complete values on this rank (the input of the first block)
+ *   residual_rows   this rank's rows [rank * rows_total / world, ...) of the residual stream, f32, updated in place
+ *   w bf16 [d]; h_scratch bf16 [rows_total / world, d] (scratch); amax one zeroed f32 (nvfp4) */
+TF_API tf_status tf_tp_norm_exchange(const uint64_t* buffer_ptrs, const uint64_t* state_ptrs, uint64_t multicast_ptr, int32_t reduce_in_switch,
+                                     int32_t rank, int32_t world, int64_t partial_offset, int64_t codes_offset, int64_t scales_offset,
+                                     int64_t gs_offset, int64_t rows_total, int64_t d, int32_t sum_peers, void* residual_rows, const void* w,
+                                     void* h_scratch, float* amax, float eps, int32_t q_format, int32_t num_ctas, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -176,3 +176,44 @@ def test_programmatic_launch_gives_the_same_bytes(fmt, m):
     finally:
         K.set_programmatic_launch(False)
     assert _native.device_status() == (0, 0)
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "mxfp4", "nvfp4"])
+@pytest.mark.parametrize("chunks", [1, 2])
+def test_fused_exchange_kernel_reproduces_the_unfused_kernels(fmt, chunks):
+    """comm="fused_exchange" replaces all-reduce + residual_add_rmsnorm + quantize by one kernel (tf_tp_norm_exchange). On a
+    single-rank group there is nothing to sum, so it must give the bytes of the stack built from the separate kernels with the
+    same row chunks (same normalisation arithmetic, same quantizer, per-row-block nvfp4 global scales in the GEMM)."""
+    import os
+
+    import torch.distributed as dist
+
+    from tilefish_b200 import mlp as MLP
+
+    if not dist.is_initialized():
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29517")
+        dist.init_process_group("nccl", rank=0, world_size=1, device_id=torch.device("cuda", 0))
+    m, h, f = 512, 1024, 1536
+    layers = []
+    for i in range(3):
+        _, _, w_n, w_gu, w_d = make(m, h, f, seed=11 * i)
+        layers.append(MLP.quantize_weights(w_n.cuda(), w_gu.cuda(), w_d.cuda(), fmt))
+    x = O.randn((m, h), 5, torch.bfloat16).cuda()
+    res0 = O.randn((m, h), 6).cuda()
+    ref_res = res0.clone()
+    ref = MLP.MlpStack(layers, group=dist.group.WORLD, chunks=chunks, comm="all_reduce")(x, ref_res)
+    stack = MLP.MlpStack(layers, group=dist.group.WORLD, chunks=chunks, comm="fused_exchange", sm_margin=24)
+    for _ in range(2):  # twice: the kernel's call counter and barriers carry over
+        res = res0.clone()
+        y = stack(x, res)
+        torch.cuda.synchronize()
+        assert torch.equal(res, ref_res)
+        assert torch.equal(y, ref)
+    res = res0.clone()
+    cap = stack.capture(x, res)
+    res.copy_(res0)
+    y = cap.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(y, ref) and torch.equal(res, ref_res)
+    assert stack._peer.status() == 0

@@ -21,6 +21,6 @@ def test_peer_allreduce_two_gpus():
     env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1", "--master-port", "29533",
            os.path.join(HERE, "workers", "peer_allreduce_worker.py")]
-    r = subprocess.run(cmd, capture_output=True, text=True, timeout=240, env=env)
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=400, env=env)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "rank 0 ok" in r.stdout and "rank 1 ok" in r.stdout

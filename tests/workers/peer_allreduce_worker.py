@@ -99,6 +99,44 @@ def main() -> int:
             y = outs[("peer_all_reduce", chunks, "switch_reduce")]
             rel = float((y - ref).norm() / ref.norm())
             expect(rel < (0.04 if fmt == "mxfp8" else 0.15), f"{fmt} chunks={chunks} switch_reduce: rel {rel}")
+    # the fused exchange kernel (sum + residual add + rmsnorm + quantize + gather in one launch per block and chunk) against the
+    # all-reduce stack: mxfp8 has no tensor-wide scale, so sharding the normalisation by rows must not change a byte (peer loads
+    # sum in f32 and round once, as NCCL does for two ranks); nvfp4 row blocks get their own global scales: quantization noise
+    h, f, m = 1024, 2048, 1024
+    for fmt in ("mxfp8", "nvfp4"):
+        blocks = []
+        for layer in range(3):
+            g = torch.Generator(device=dev).manual_seed(200 + layer)
+            w_gu = (torch.randn((2 * f, h), generator=g, device=dev) * h**-0.5).to(torch.bfloat16)
+            w_d = (torch.randn((h, f), generator=g, device=dev) * f**-0.5).to(torch.bfloat16)
+            w_n = (1 + 0.1 * torch.randn(h, generator=g, device=dev)).to(torch.bfloat16)
+            blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, fmt, rank=rank, world=world))
+        g = torch.Generator(device=dev).manual_seed(9)
+        x = torch.randn((m, h), generator=g, device=dev).to(torch.bfloat16)
+        for chunks in (1, 2):
+            # the reference with the same row sharding: mxfp8 = the all-reduce stack (no tensor-wide scale); nvfp4 = the row-sharded
+            # stack over NCCL collectives (every rank's row block has the global scale of its own amax there too)
+            res_ref = torch.zeros((m, h), dtype=torch.float32, device=dev)
+            ref = MLP.MlpStack(blocks, group=dist.group.WORLD, chunks=chunks, comm="all_reduce" if fmt == "mxfp8" else "scatter_gather")(x, res_ref).float()
+            for path in ("multicast_store", "peer_loads", "switch_reduce"):
+                stack = MLP.MlpStack(blocks, group=dist.group.WORLD, chunks=chunks, comm="fused_exchange", sm_margin=16, peer_path=path)
+                res = torch.zeros((m, h), dtype=torch.float32, device=dev)
+                y = stack(x, res).float()
+                torch.cuda.synchronize()
+                rel = float((y - ref).norm() / ref.norm())
+                if path != "switch_reduce" and world == 2:
+                    expect(torch.equal(y, ref) and torch.equal(res, res_ref), f"fused {fmt} chunks={chunks} {path}: differs from the all-reduce stack (rel {rel})")
+                else:
+                    # the switch's sums differ in the last bit, which requantizes everything downstream: quantization noise
+                    expect(rel < (0.1 if fmt == "mxfp8" else 0.35), f"fused {fmt} chunks={chunks} {path}: rel {rel}")
+                if chunks == 2 and path == "multicast_store":
+                    res2 = torch.zeros((m, h), dtype=torch.float32, device=dev)
+                    cap = stack.capture(x.clone(), res2)
+                    res2.zero_()
+                    y2 = cap.replay().float()
+                    torch.cuda.synchronize()
+                    expect(torch.equal(y2, y), f"fused {fmt}: captured stack differs from eager")
+                expect(stack._peer.status() == 0, f"fused {fmt} {path}: error word")
     if failures:
         print(f"rank {rank} FAILED: " + "; ".join(failures), flush=True)
     else:

@@ -36,15 +36,24 @@ class PeerAllReduce:
         import torch.distributed._symmetric_memory as symm
 
         self.lib = N.load()
-        self.group = group if group is not None else dist.group.WORLD
-        self.world = dist.get_world_size(self.group)
-        self.rank = dist.get_rank(self.group)
-        if not 2 <= self.world <= 8:
-            raise TilefishPreconditionError(f"PeerAllReduce: {self.world} ranks (2..8 supported)", kind="argument", arg="group")
+        self.group = group if group is not None else (dist.group.WORLD if dist.is_initialized() else None)
+        self.world = dist.get_world_size(self.group) if self.group is not None else 1
+        self.rank = dist.get_rank(self.group) if self.group is not None else 0
+        if not 1 <= self.world <= 8:
+            raise TilefishPreconditionError(f"PeerAllReduce: {self.world} ranks (1..8 supported)", kind="argument", arg="group")
         self.num_ctas = int(num_ctas)
         self.reduce_in_switch = bool(reduce_in_switch)
         self.channels = int(channels)
         self.nbytes = (int(nbytes) + 255) // 256 * 256
+        if self.world == 1:
+            # a single rank has no peers: ordinary device memory, the same kernels (their barriers then only meet themselves)
+            self.buffer = torch.empty(self.nbytes, dtype=torch.uint8, device=device)
+            self.state = torch.zeros(self.channels * STATE_BYTES, dtype=torch.uint8, device=device)
+            self.multicast_ptr = 0
+            u64s = ctypes.c_uint64 * 1
+            self._bufs = u64s(self.buffer.data_ptr())
+            self._states = [u64s(self.state.data_ptr() + c * STATE_BYTES) for c in range(self.channels)]
+            return
         self.buffer = symm.empty(self.nbytes, dtype=torch.uint8, device=device)
         self.state = symm.empty(self.channels * STATE_BYTES, dtype=torch.uint8, device=device)
         self.state.zero_()
@@ -91,6 +100,8 @@ class PeerAllReduce:
         current stream. Calls on one channel must be stream-ordered; all ranks issue the same calls in the same order."""
         import torch
 
+        if self.world == 1:
+            return t  # nothing to sum
         off = t.data_ptr() - self.buffer.data_ptr()
         n = t.numel()
         if t.dtype != torch.bfloat16 or not t.is_contiguous() or off < 0 or off + 2 * n > self.nbytes:
@@ -100,6 +111,30 @@ class PeerAllReduce:
         N.check(self.lib.tf_allreduce_bf16(self._bufs, self._states[channel], ctypes.c_uint64(self.multicast_ptr), int(self.reduce_in_switch), self.rank, self.world, off, n,
                                           self.num_ctas, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "tf_allreduce_bf16")
         return t
+
+    def norm_exchange_(self, *, partial_offset: int, codes_offset: int, scales_offset: int, gs_offset: int, rows_total: int, d: int, sum_peers: bool,
+                       residual_rows, w, h_scratch, amax, eps: float, fmt: str, channel: int = 0) -> None:
+        """``tf_tp_norm_exchange`` on the current stream: this rank sums its rows of the partial results at ``partial_offset`` over
+        the ranks, adds them into ``residual_rows`` (f32, its rows of the residual stream), normalises with ``w`` and writes the
+        quantized rows (codes, swizzled scales, nvfp4 global scale) at the given offsets of EVERY rank's buffer."""
+        import torch
+
+        from . import kernels as K
+
+        if not 0 <= channel < self.channels:
+            raise TilefishPreconditionError(f"PeerAllReduce.norm_exchange_: channel {channel} of {self.channels}", kind="argument", arg="channel")
+        for name, t, dt in (("residual_rows", residual_rows, torch.float32), ("w", w, torch.bfloat16), ("h_scratch", h_scratch, torch.bfloat16)):
+            if t.dtype != dt or not t.is_contiguous() or not t.is_cuda:
+                raise TilefishPreconditionError(f"PeerAllReduce.norm_exchange_: {name} must be a contiguous {dt} device tensor", kind="dtype", arg=name)
+        rows_local = rows_total // self.world
+        if residual_rows.numel() != rows_local * d or h_scratch.numel() < rows_local * d or w.numel() != d:
+            raise TilefishPreconditionError("PeerAllReduce.norm_exchange_: residual_rows / h_scratch / w do not match rows_total / world x d", kind="shape",
+                                            arg="residual_rows")
+        N.check(self.lib.tf_tp_norm_exchange(self._bufs, self._states[channel], ctypes.c_uint64(self.multicast_ptr), int(self.reduce_in_switch), self.rank,
+                                            self.world, partial_offset, codes_offset, scales_offset, gs_offset, rows_total, d, int(bool(sum_peers)),
+                                            residual_rows.data_ptr(), w.data_ptr(), h_scratch.data_ptr(), amax.data_ptr() if amax is not None else None,
+                                            float(eps), K.FORMATS[fmt], self.num_ctas, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
+                "tf_tp_norm_exchange")
 
     def status(self) -> int:
         """0 when healthy; else the first nonzero error word of the channels (1: a local barrier gave up, 2: a peer never

@@ -19,7 +19,7 @@
 // arguments) still produces fresh values. Every spin is bounded by %globaltimer (two seconds): on a timeout the kernel writes an
 // error word into the state block and returns; nothing traps and nothing spins forever. The kernels of all ranks must be
 // running at the same time for the barriers to complete: that holds because every rank is its own GPU.
-#include "common.cuh"
+#include "quant_core.cuh"
 
 namespace tf {
 
@@ -215,6 +215,216 @@ __global__ void __launch_bounds__(kArThreads, 1) allreduce_bf16_kernel(const ArP
   }
 }
 
+// ---- the tensor-parallel exchange fused with the next block's normalisation -------------------------------------------------
+// One kernel per rank replaces, between two blocks of the MLP stack, the all-reduce of the second GEMM's partial results, the
+// residual_add_rmsnorm of the next block and the quantization of its output: with the normalisation sharded by rows, rank r
+//   1. sums ITS rows of the partial results over the ranks (peer loads in rank order, f32, rounded to bf16 once: the value a
+//      bf16 all-reduce would have delivered; or the switch's multimem.ld_reduce), adds them into its rows of the f32 residual
+//      stream and normalises them (the arithmetic and thread mapping of residual_add_rmsnorm_kernel: the same bytes),
+//   2. derives the nvfp4 global scale of its row block from the block's amax (a grid-wide barrier inside the kernel),
+//   3. quantizes its rows and writes codes, swizzled scales and the global scale into EVERY rank's buffers (multimem.st through
+//      the switch, or one store per peer), so that every rank holds the quantized activation of all rows for its first GEMM.
+// Per GPU and block the bytes received drop from 2 x (all-reduce of bf16 [M, H]) to (1/n of it, or (n-1)/n with peer loads)
+// + 0.28 x: the activation crosses the links in 4.5 bits per element instead of 16, and the normalisation work is divided by n.
+struct NxParams {
+  ArParams ar;  // bufs = every rank's symmetric buffer; offset_bytes / count unused
+  long long partial_off, codes_off, scales_off, gs_off;  // byte offsets inside the symmetric buffer (this row chunk's regions)
+  int rows_total, d;  // rows of the chunk over all ranks (a multiple of 128 x world), row length
+  int sum_peers;      // 0: the partial region already holds complete values on every rank (the stack's input)
+  float* residual;    // this rank's rows of the residual stream, f32 [rows_total / world, d], updated in place
+  const uint4* w;     // bf16 [d]
+  uint4* h_scratch;   // bf16 [rows_total / world, d]: the normalised rows between the two passes
+  unsigned int* amax; // one word, zeroed by the caller
+  float eps, inv_d;
+};
+
+template <int BYTES>
+__device__ __forceinline__ void store_all_ranks(const ArParams& p, long long off, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  if (p.mc_ptr) {
+    const unsigned long long addr = p.mc_ptr + off;
+    if (BYTES == 16) asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+    else if (BYTES == 8) asm volatile("multimem.st.relaxed.sys.global.v2.f32 [%0], {%1, %2};" ::"l"(addr), "r"(a), "r"(b) : "memory");
+    else asm volatile("multimem.st.relaxed.sys.global.f32 [%0], %1;" ::"l"(addr), "r"(a) : "memory");
+  } else {
+    for (int r = 0; r < p.world; ++r) {
+      const unsigned long long addr = p.bufs[r] + off;
+      if (BYTES == 16) *reinterpret_cast<uint4*>(addr) = make_uint4(a, b, c, d);
+      else if (BYTES == 8) *reinterpret_cast<uint2*>(addr) = make_uint2(a, b);
+      else *reinterpret_cast<uint32_t*>(addr) = a;
+    }
+  }
+}
+
+template <int VPT, int QFMT>
+__global__ void __launch_bounds__(512, 1) tp_norm_exchange_kernel(const NxParams q) {
+  const ArParams& p = q.ar;
+  unsigned long long* state64 = reinterpret_cast<unsigned long long*>(p.states[p.rank] + 64);
+  unsigned long long* call_counter = state64;
+  unsigned long long* grid_counter = state64 + 1;
+  unsigned long long* grid_base = state64 + 2;
+  volatile unsigned long long* error_word = state64 + 3;
+  const unsigned long long call = ld_acquire_gpu64(call_counter);
+  const unsigned long long gbase = ld_acquire_gpu64(grid_base);
+  const unsigned long long g = gridDim.x;
+  const unsigned int flag = (unsigned int)(call * 4ull);
+  unsigned long long syncs = 0;
+  __shared__ float warp_sums[16];
+  __shared__ unsigned int warp_amax[16];
+  __shared__ float row_rstd;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int nvec = q.d >> 3;
+  const int rows_local = q.rows_total / p.world;
+  const int row0 = p.rank * rows_local;
+
+  // every rank's partial results are complete
+  ar_cross_barrier(p, flag + 1, error_word);
+  bool ok = ar_grid_sync(grid_counter, gbase + (++syncs) * g, error_word);
+
+  // ---- pass 1: sum over the ranks, residual add, normalise (this rank's rows) ----
+  uint32_t amax_bits = 0;
+  if (ok) {
+    for (int row = blockIdx.x; row < rows_local; row += gridDim.x) {
+      const long long grow = row0 + row;
+      float4* rr = reinterpret_cast<float4*>(q.residual) + (long long)row * (nvec * 2);
+      float r[VPT][8];
+      float acc = 0.0f;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * nthreads;
+        if (v < nvec) {
+          const long long off = q.partial_off + (grow * nvec + v) * 16;
+          uint4 xv;
+          if (!q.sum_peers) {
+            xv = ld_peer_16(p.bufs[p.rank] + off);
+          } else if (p.reduce_in_switch) {
+            multimem_ld_reduce_bf16x8(p.mc_ptr + off, xv);
+          } else {
+            uint4 pv[kArMaxWorld];
+#pragma unroll
+            for (int k = 0; k < kArMaxWorld; ++k)
+              if (k < p.world) pv[k] = ld_peer_16(p.bufs[k] + off);
+            float s[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) s[j] = 0.0f;
+#pragma unroll
+            for (int k = 0; k < kArMaxWorld; ++k) {
+              if (k < p.world) {
+                s[0] += bf16lo_to_f32(pv[k].x); s[1] += bf16hi_to_f32(pv[k].x); s[2] += bf16lo_to_f32(pv[k].y); s[3] += bf16hi_to_f32(pv[k].y);
+                s[4] += bf16lo_to_f32(pv[k].z); s[5] += bf16hi_to_f32(pv[k].z); s[6] += bf16lo_to_f32(pv[k].w); s[7] += bf16hi_to_f32(pv[k].w);
+              }
+            }
+            xv = make_uint4(pack_bf16x2(s[0], s[1]), pack_bf16x2(s[2], s[3]), pack_bf16x2(s[4], s[5]), pack_bf16x2(s[6], s[7]));
+          }
+          const float4 a = __ldcs(rr + 2 * v), b = __ldcs(rr + 2 * v + 1);
+          r[i][0] = __fadd_rn(a.x, bf16lo_to_f32(xv.x));
+          r[i][1] = __fadd_rn(a.y, bf16hi_to_f32(xv.x));
+          r[i][2] = __fadd_rn(a.z, bf16lo_to_f32(xv.y));
+          r[i][3] = __fadd_rn(a.w, bf16hi_to_f32(xv.y));
+          r[i][4] = __fadd_rn(b.x, bf16lo_to_f32(xv.z));
+          r[i][5] = __fadd_rn(b.y, bf16hi_to_f32(xv.z));
+          r[i][6] = __fadd_rn(b.z, bf16lo_to_f32(xv.w));
+          r[i][7] = __fadd_rn(b.w, bf16hi_to_f32(xv.w));
+          __stcs(rr + 2 * v, make_float4(r[i][0], r[i][1], r[i][2], r[i][3]));
+          __stcs(rr + 2 * v + 1, make_float4(r[i][4], r[i][5], r[i][6], r[i][7]));
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc = fmaf(r[i][j], r[i][j], acc);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) r[i][j] = 0.0f;
+        }
+      }
+      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
+      if ((tid & 31) == 0) warp_sums[tid >> 5] = acc;
+      __syncthreads();
+      if (tid < 32) {
+        float s = (tid < (nthreads >> 5)) ? warp_sums[tid] : 0.0f;
+        for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+        if (tid == 0) row_rstd = __frsqrt_rn(__fadd_rn(__fmul_rn(s, q.inv_d), q.eps));
+      }
+      __syncthreads();
+      const float rstd = row_rstd;
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) {
+        const int v = tid + i * nthreads;
+        if (v < nvec) {
+          const uint4 wv = __ldg(q.w + v);
+          uint4 o;
+          o.x = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][0], rstd), bf16lo_to_f32(wv.x)), __fmul_rn(__fmul_rn(r[i][1], rstd), bf16hi_to_f32(wv.x)));
+          o.y = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][2], rstd), bf16lo_to_f32(wv.y)), __fmul_rn(__fmul_rn(r[i][3], rstd), bf16hi_to_f32(wv.y)));
+          o.z = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][4], rstd), bf16lo_to_f32(wv.z)), __fmul_rn(__fmul_rn(r[i][5], rstd), bf16hi_to_f32(wv.z)));
+          o.w = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][6], rstd), bf16lo_to_f32(wv.w)), __fmul_rn(__fmul_rn(r[i][7], rstd), bf16hi_to_f32(wv.w)));
+          q.h_scratch[(long long)row * nvec + v] = o;
+          amax_bits = max(amax_bits, amax_bits8(o));
+        }
+      }
+      __syncthreads();  // warp_sums / row_rstd are reused by the next row
+    }
+    if (QFMT == TF_FMT_NVFP4) {  // the row block's amax: one atomic per CTA
+      for (int o = 16; o > 0; o >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xFFFFFFFFu, amax_bits, o));
+      if ((tid & 31) == 0) warp_amax[tid >> 5] = amax_bits;
+      __syncthreads();
+      if (tid == 0) {
+        for (int wi = 1; wi < (nthreads >> 5); ++wi) amax_bits = max(amax_bits, warp_amax[wi]);
+        if (amax_bits) atomicMax(q.amax, amax_bits << 16);
+      }
+    }
+  }
+  ok = ar_grid_sync(grid_counter, gbase + (++syncs) * g, error_word);
+
+  // ---- pass 2: quantize this rank's rows into every rank's buffers ----
+  if (ok) {
+    float gs = 0.0f, inv_t = 0.0f;
+    if (QFMT == TF_FMT_NVFP4) {
+      gs = __fdiv_rn(__uint_as_float(*reinterpret_cast<volatile unsigned int*>(q.amax)), 2688.0f);
+      inv_t = gs != 0.0f ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
+      if (blockIdx.x == 0 && tid == 0) store_all_ranks<4>(p, q.gs_off + 4ll * p.rank, __float_as_uint(gs), 0, 0, 0);
+    }
+    constexpr int kBlk = (QFMT == TF_FMT_NVFP4) ? 16 : 32;
+    constexpr int kLanesPerWord = (QFMT == TF_FMT_NVFP4) ? 4 : 8;  // lanes (16 elements each) whose blocks share one 4-byte scale word
+    const int nvec16 = q.d >> 4;
+    const int n_ct = ((q.d / kBlk) + 3) >> 2;
+    const int rounds = (nvec16 + nthreads - 1) / nthreads;
+    for (int row = blockIdx.x; row < rows_local; row += gridDim.x) {
+      const long long grow = row0 + row;
+      const uint4* hrow = q.h_scratch + (long long)row * nvec;
+      for (int rd = 0; rd < rounds; ++rd) {  // every thread runs every round: the quantizer and the scale packing shuffle
+        const int v = rd * nthreads + tid;
+        const bool has = v < nvec16;
+        uint32_t w8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        if (has) {
+          const uint4 lo = hrow[2 * v], hi = hrow[2 * v + 1];
+          w8[0] = lo.x; w8[1] = lo.y; w8[2] = lo.z; w8[3] = lo.w; w8[4] = hi.x; w8[5] = hi.y; w8[6] = hi.z; w8[7] = hi.w;
+        }
+        uint32_t codes[4], sc;
+        quantize_vec16<QFMT>(w8, gs, inv_t, codes, sc);
+        // four consecutive blocks' scale bytes are four consecutive bytes of the swizzled layout: gather them into the first lane
+        uint32_t word = 0;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const int src = (tid & 31 & ~(kLanesPerWord - 1)) + k * (kLanesPerWord / 4);
+          word |= (__shfl_sync(0xFFFFFFFFu, sc, src) & 0xFFu) << (8 * k);
+        }
+        if (!has) continue;
+        if (QFMT == TF_FMT_MXFP8) store_all_ranks<16>(p, q.codes_off + grow * q.d + (long long)v * 16, codes[0], codes[1], codes[2], codes[3]);
+        else store_all_ranks<8>(p, q.codes_off + grow * (q.d >> 1) + (long long)v * 8, codes[0], codes[1], 0, 0);
+        if ((tid & (kLanesPerWord - 1)) == 0) {
+          const long long c = (QFMT == TF_FMT_NVFP4) ? v : (v >> 1);  // first of the word's four scale columns
+          store_all_ranks<4>(p, q.scales_off + swizzled_scale_offset(grow, c, n_ct), word, 0, 0, 0);
+        }
+      }
+    }
+  }
+  // every rank's rows have landed everywhere
+  ar_grid_sync(grid_counter, gbase + (++syncs) * g, error_word);
+  ar_cross_barrier(p, flag + 2, error_word);
+  __syncthreads();
+  if (blockIdx.x == 0 && threadIdx.x == 0) {
+    *grid_base = gbase + syncs * g;
+    __threadfence();
+    *call_counter = call + 1ull;
+  }
+}
+
 }  // namespace tf
 
 using namespace tf;
@@ -244,5 +454,82 @@ extern "C" tf_status tf_allreduce_bf16(const uint64_t* buffer_ptrs, const uint64
   if (grid > sms) grid = sms;
   allreduce_bf16_kernel<<<grid, kArThreads, 0, (cudaStream_t)stream>>>(p);
   TF_LAUNCH_CHECK();
+  return TF_OK;
+}
+
+template <int VPT>
+static cudaError_t launch_norm_exchange(int q_format, int grid, int threads, cudaStream_t stream, const NxParams& q) {
+  switch (q_format) {
+    case TF_FMT_MXFP8: tp_norm_exchange_kernel<VPT, TF_FMT_MXFP8><<<grid, threads, 0, stream>>>(q); break;
+    case TF_FMT_MXFP4: tp_norm_exchange_kernel<VPT, TF_FMT_MXFP4><<<grid, threads, 0, stream>>>(q); break;
+    default: tp_norm_exchange_kernel<VPT, TF_FMT_NVFP4><<<grid, threads, 0, stream>>>(q); break;
+  }
+  return cudaGetLastError();
+}
+
+extern "C" tf_status tf_tp_norm_exchange(const uint64_t* buffer_ptrs, const uint64_t* state_ptrs, uint64_t multicast_ptr, int32_t reduce_in_switch,
+                                         int32_t rank, int32_t world, int64_t partial_offset, int64_t codes_offset, int64_t scales_offset,
+                                         int64_t gs_offset, int64_t rows_total, int64_t d, int32_t sum_peers, void* residual_rows, const void* w,
+                                         void* h_scratch, float* amax, float eps, int32_t q_format, int32_t num_ctas, void* stream) {
+  clear_error();
+  TF_CHECK_ARG(buffer_ptrs && state_ptrs && residual_rows && w && h_scratch, "%s: null pointer", __func__);
+  TF_CHECK_ARG(world >= 1 && world <= kArMaxWorld && rank >= 0 && rank < world, "%s: bad rank %d / world %d (1..8 ranks)", __func__, rank, world);
+  TF_CHECK_ARG(q_format >= TF_FMT_MXFP8 && q_format <= TF_FMT_NVFP4, "%s: unknown format %d", __func__, q_format);
+  TF_CHECK_ARG(q_format != TF_FMT_NVFP4 || amax, "%s: nvfp4 needs the amax word", __func__);
+  TF_CHECK_ARG(rows_total > 0 && rows_total % (128 * world) == 0, "%s: rows must be a positive multiple of 128 x world", __func__);
+  TF_CHECK_ARG(rows_total <= (1 << 24), "%s: too many rows", __func__);
+  if (d <= 0 || d % 128 != 0 || d > 32768) return fail(TF_ERR_UNSUPPORTED, "%s: d=%lld must be a multiple of 128, at most 32768", __func__, (long long)d);
+  TF_CHECK_ARG(partial_offset >= 0 && partial_offset % 16 == 0 && codes_offset >= 0 && codes_offset % 16 == 0 && scales_offset >= 0 &&
+                   scales_offset % 16 == 0 && gs_offset >= 0 && gs_offset % 16 == 0,
+               "%s: offsets must be multiples of 16", __func__);
+  TF_CHECK_ARG(num_ctas >= 1 && num_ctas <= 148, "%s: num_ctas must be in 1..148", __func__);
+  TF_CHECK_ALIGNED(residual_rows, 16, "residual_rows");
+  TF_CHECK_ALIGNED(w, 16, "w");
+  TF_CHECK_ALIGNED(h_scratch, 16, "h_scratch");
+  NxParams q;
+  for (int i = 0; i < kArMaxWorld; ++i) {
+    q.ar.bufs[i] = i < world ? buffer_ptrs[i] : 0;
+    q.ar.states[i] = i < world ? state_ptrs[i] : 0;
+    if (i < world && (!q.ar.bufs[i] || !q.ar.states[i] || q.ar.bufs[i] % 16 || q.ar.states[i] % 16))
+      return fail(TF_ERR_ALIGNMENT, "%s: peer pointer %d is null or unaligned", __func__, i);
+  }
+  q.ar.mc_ptr = multicast_ptr;
+  q.ar.reduce_in_switch = reduce_in_switch != 0 && multicast_ptr != 0;
+  q.ar.rank = rank;
+  q.ar.world = world;
+  q.ar.offset_bytes = 0;
+  q.ar.count = 0;
+  q.partial_off = partial_offset;
+  q.codes_off = codes_offset;
+  q.scales_off = scales_offset;
+  q.gs_off = gs_offset;
+  q.rows_total = (int)rows_total;
+  q.d = (int)d;
+  q.sum_peers = sum_peers != 0 && world > 1;
+  q.residual = static_cast<float*>(residual_rows);
+  q.w = static_cast<const uint4*>(w);
+  q.h_scratch = static_cast<uint4*>(h_scratch);
+  q.amax = reinterpret_cast<unsigned int*>(amax);
+  q.eps = eps;
+  q.inv_d = 1.0f / (float)d;
+  // the thread mapping of residual_add_rmsnorm_kernel, so that the row sums are formed in the same order
+  const int nvec = (int)(d >> 3);
+  int vpt = (nvec + 511) / 512;
+  vpt = vpt <= 1 ? 1 : vpt <= 2 ? 2 : vpt <= 4 ? 4 : 8;
+  int threads = (nvec + vpt - 1) / vpt;
+  threads = (threads + 31) / 32 * 32;
+  int grid = num_ctas;
+  const int sms = sm_count();
+  if (grid > sms) grid = sms;
+  const int64_t rows_local = rows_total / world;
+  if (grid > rows_local) grid = (int)rows_local;
+  cudaError_t e;
+  switch (vpt) {
+    case 1: e = launch_norm_exchange<1>(q_format, grid, threads, (cudaStream_t)stream, q); break;
+    case 2: e = launch_norm_exchange<2>(q_format, grid, threads, (cudaStream_t)stream, q); break;
+    case 4: e = launch_norm_exchange<4>(q_format, grid, threads, (cudaStream_t)stream, q); break;
+    default: e = launch_norm_exchange<8>(q_format, grid, threads, (cudaStream_t)stream, q); break;
+  }
+  if (e != cudaSuccess) return fail(TF_ERR_CUDA, "%s: launch failed: %s", __func__, cudaGetErrorString(e));
   return TF_OK;
 }

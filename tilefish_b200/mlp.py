@@ -168,14 +168,16 @@ class MlpStack:
         """``comm``: "all_reduce" (one NCCL bf16 all-reduce per block), "peer_all_reduce" (the same exchange by this package's
         own kernel over symmetric memory, see ``collective.PeerAllReduce``; ``sm_margin`` is also its CTA count) or
         "scatter_gather" (rows of the normalisation sharded over the ranks: reduce-scatter of the partial results +
-        all-gather of the quantized activations; see ``decoder_block_row_sharded``)."""
+        all-gather of the quantized activations; see ``decoder_block_row_sharded``) or "fused_exchange" (the same row-sharded
+        scheme as ONE kernel of this package per block: sum of the partial results, residual add, rmsnorm, quantization and the
+        gather of the quantized rows, ``tf_tp_norm_exchange``; ``sm_margin`` is its CTA count)."""
         self.layers = layers
         self.eps = eps
         self.group = group
         self.chunks = chunks if group is not None else 1
         self.sm_margin = sm_margin
         self.comm = comm if group is not None else "all_reduce"
-        if self.comm not in ("all_reduce", "peer_all_reduce", "scatter_gather"):
+        if self.comm not in ("all_reduce", "peer_all_reduce", "fused_exchange", "scatter_gather"):
             raise TilefishPreconditionError(f"unknown comm mode {comm!r}", kind="argument", arg="comm")
         self._peer = None
         # how the peer all-reduce moves data: "multicast_store" (sum over peer loads, result written through the switch),
@@ -206,6 +208,8 @@ class MlpStack:
             return self._forward_row_sharded(x, residual, rows_local)
         if rows_local:
             raise TilefishPreconditionError("rows_local needs comm='scatter_gather'", kind="argument", arg="rows_local")
+        if self.comm == "fused_exchange":
+            return self._forward_fused(x, residual)
         if self.comm == "peer_all_reduce" and self._peer_for(x) is not None:
             return self._forward_peer(x, residual)
         if self.chunks <= 1:
@@ -329,6 +333,113 @@ class MlpStack:
             for ci, (a, b) in enumerate(spans):
                 with torch.cuda.stream(streams[ci]):
                     out[a:b].copy_(xs[ci])
+            for s in streams:
+                if s is not main:
+                    main.wait_stream(s)
+        finally:
+            if multi:
+                N.check(N.load().tf_set_sm_margin(0), "tf_set_sm_margin")
+            self._last_reduce = None
+        return out
+
+    def _forward_fused(self, x, residual):
+        """Row-sharded normalisation with this package's fused exchange kernel. Every rank gets the full ``x`` / ``residual`` and
+        returns the full result (the residual rows of the other ranks arrive with one all-gather at the end). Per block and row
+        chunk: tf_tp_norm_exchange -> gemm + SiLU gate -> (quantize) -> gemm into the symmetric partial buffer."""
+        import torch
+        import torch.distributed as dist
+
+        from . import _native as N
+        from .collective import PeerAllReduce
+
+        world = dist.get_world_size(self.group)
+        rank = dist.get_rank(self.group)
+        m, h = x.shape
+        fmt = self.layers[0].fmt
+        c = max(1, self.chunks)
+        unit = 128 * world
+        if m % (unit * c):
+            c = 1
+        if m % unit or h % 128:
+            raise TilefishPreconditionError(f"fused_exchange needs M={m} to be a multiple of 128 x group size ({unit}) and H={h} of 128", kind="divisible", arg="x")
+        rows = m // c       # rows of a chunk
+        r = rows // world   # rows of a chunk this rank normalises
+        epb = K.ELEMS_PER_BYTE[fmt]
+        part_b, codes_b, scales_b = rows * h * 2, rows * h // epb, K.scale_bytes(fmt, rows, h)
+        chunk_b = (part_b + codes_b + scales_b + 256 + 255) // 256 * 256
+        if self._peer is None or self._peer.nbytes < c * chunk_b or self._peer.channels < c:
+            self._peer = PeerAllReduce(c * chunk_b, self.group, x.device, channels=c, num_ctas=max(1, self.sm_margin),
+                                       multicast=self._peer_path != "peer_loads", reduce_in_switch=self._peer_path == "switch_reduce")
+        peer = self._peer
+        key = ("fused", rows, h, fmt)
+        for ci in range(c):
+            while len(self._scratch) <= ci:
+                self._scratch.append({})
+            if key not in self._scratch[ci]:
+                self._scratch[ci][key] = torch.empty((r, h), dtype=torch.bfloat16, device=x.device)
+        multi = c > 1
+        if multi and (self._streams is None or len(self._streams) < c):
+            self._streams = [torch.cuda.Stream(device=x.device) for _ in range(c)]
+        main = torch.cuda.current_stream()
+        streams = self._streams[:c] if multi else [main]
+        out = torch.empty_like(x)
+        self._last_reduce = None
+
+        def ordered(fn):  # the exchange kernels of all chunks run in one order that is the same on every rank
+            st = torch.cuda.current_stream()
+            if self._last_reduce is not None:
+                st.wait_event(self._last_reduce)
+            fn()
+            ev = torch.cuda.Event()
+            ev.record(st)
+            self._last_reduce = ev
+
+        if multi:
+            N.check(N.load().tf_set_sm_margin(self.sm_margin), "tf_set_sm_margin")
+        try:
+            views = []
+            for ci in range(c):
+                base = ci * chunk_b
+                buf = peer.buffer
+                views.append({
+                    "off": (base, base + part_b, base + part_b + codes_b, base + part_b + codes_b + scales_b),
+                    "partial": buf[base:base + part_b].view(torch.bfloat16).view(rows, h),
+                    "codes": buf[base + part_b:base + part_b + codes_b].view(rows, h // epb),
+                    "scales": buf[base + part_b + codes_b:base + part_b + codes_b + scales_b],
+                    "gs": buf[base + part_b + codes_b + scales_b:base + part_b + codes_b + scales_b + 4 * world].view(torch.float32) if fmt == "nvfp4" else None,
+                    "res": residual[ci * rows + rank * r:ci * rows + (rank + 1) * r],
+                })
+            for s in streams:
+                if s is not main:
+                    s.wait_stream(main)
+            slots = []
+            for ci in range(c):
+                with torch.cuda.stream(streams[ci]):
+                    slots.append(self._amax_slots(ci, x.device))
+                    views[ci]["partial"].copy_(x[ci * rows:(ci + 1) * rows])
+            for li, w in enumerate(self.layers):
+                for ci in range(c):
+                    v = views[ci]
+                    with torch.cuda.stream(streams[ci]):
+                        am = slots[ci][li]
+                        ordered(lambda: peer.norm_exchange_(partial_offset=v["off"][0], codes_offset=v["off"][1], scales_offset=v["off"][2], gs_offset=v["off"][3],
+                                                            rows_total=rows, d=h, sum_peers=li > 0, residual_rows=v["res"], w=w.w_n,
+                                                            h_scratch=self._scratch[ci][key], amax=am[0:1] if am is not None else None, eps=self.eps,
+                                                            fmt=fmt, channel=ci))
+                        hq = K.BlockScaledTensor(fmt, (rows, h), v["codes"], v["scales"], v["gs"], "swizzled", gs_rows=r if fmt == "nvfp4" else 0)
+                        if fmt == "nvfp4":
+                            a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", amax_out=am[1:2])
+                            aq = K.quantize(a, fmt, amax=am[1:2])
+                        else:
+                            _, aq = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", quantize_out=True, want_bf16=False)
+                        K.gemm_blockscaled(aq, w.w_d, out=v["partial"])
+            for ci in range(c):
+                v = views[ci]
+                with torch.cuda.stream(streams[ci]):
+                    ordered(lambda: peer.allreduce_(v["partial"], channel=ci))
+                    out[ci * rows:(ci + 1) * rows].copy_(v["partial"])
+                    if world > 1:
+                        dist.all_gather_into_tensor(residual[ci * rows:(ci + 1) * rows], v["res"].clone(), group=self.group)
             for s in streams:
                 if s is not main:
                     main.wait_stream(s)
