@@ -43,7 +43,7 @@ def parse_args():
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "fused_exchange", "scatter_gather"],
-                    help="tensor-parallel exchange per block (default: peer_all_reduce, this library's kernel, at 2 GPUs, NCCL all_reduce otherwise; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
+                    help="tensor-parallel exchange per block (default: peer_all_reduce, this library's all-reduce kernel; all_reduce = NCCL; fused_exchange = sum + rmsnorm + quantize + gather in one kernel; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
                          "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
     ap.add_argument("--ar-ctas", type=int, default=16, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce also the all-reduce kernel's CTAs")
     ap.add_argument("--peer-path", default="switch_reduce", choices=["multicast_store", "switch_reduce", "peer_loads"],
@@ -521,9 +521,9 @@ def run_ours(args) -> None:
         finish_ranks(world)
         return
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    # default exchange: this library's all-reduce kernel where it was measured faster than NCCL's (2 GPUs: 156.5 k against 148.5 k
-    # tokens/s), NCCL elsewhere (the kernel is tested on 2 GPUs only; pass --comm peer_all_reduce to use it at any N)
-    comm = args.comm or ("peer_all_reduce" if world == 2 else "all_reduce")
+    # default exchange: this library's all-reduce kernel (switch reduction, 16 CTAs beside the other chunk's GEMMs). Measured against
+    # NCCL's all-reduce in the same step: 156.5 k against 148.5 k tokens/s on 2 GPUs, 0.330 against 0.454 ms per block on 8
+    comm = args.comm or ("peer_all_reduce" if world > 1 else "all_reduce")
     stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=args.ar_ctas, peer_path=args.peer_path)
     torch.cuda.synchronize()
 
