@@ -460,6 +460,8 @@ def exchange_sweep(args, torch, MLP, blocks, group, dev, rank, world, layers, m)
                      ("peer_all_reduce", 2, path, 48)]
         variants += [("fused_exchange", 1, path, 148), ("fused_exchange", 1, path, 64), ("fused_exchange", 2, path, 16), ("fused_exchange", 2, path, 32),
                      ("fused_exchange", 2, path, 48)]
+    variants += [("peer_all_reduce", 3, "switch_reduce", 16), ("peer_all_reduce", 4, "switch_reduce", 16), ("peer_all_reduce", 4, "switch_reduce", 8),
+                 ("peer_all_reduce", 2, "switch_reduce", 8), ("fused_exchange", 4, "switch_reduce", 32)]
     for comm, chunks, path, ctas in variants:
         stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=ctas, peer_path=path or "multicast_store")
         cap = stack.capture(x_dev, residual)
