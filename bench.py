@@ -43,9 +43,9 @@ def parse_args():
     ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "fused_exchange", "scatter_gather"],
-                    help="tensor-parallel exchange per block (default: peer_all_reduce, this library's all-reduce kernel; all_reduce = NCCL; fused_exchange = sum + rmsnorm + quantize + gather in one kernel; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
+                    help="tensor-parallel exchange per block (default: fused_exchange = sum + rmsnorm + quantize + gather in one kernel of this library; peer_all_reduce = this library's all-reduce kernel; all_reduce = NCCL; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
                          "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
-    ap.add_argument("--ar-ctas", type=int, default=16, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce also the all-reduce kernel's CTAs")
+    ap.add_argument("--ar-ctas", type=int, default=None, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce / fused_exchange also that kernel's CTAs (default: 16; fused_exchange 24 on 2 GPUs, 32 otherwise)")
     ap.add_argument("--peer-path", default="switch_reduce", choices=["multicast_store", "switch_reduce", "peer_loads"],
                     help="data path of peer_all_reduce: the switch's own reduction (default: fewest bytes; its bf16 sum is within one bf16 step of the exact sum, as "
                          "NCCL's NVLS all-reduce), f32 sum over peer loads + multicast store (exact, rounded once), or peer loads only")
@@ -523,9 +523,12 @@ def run_ours(args) -> None:
         finish_ranks(world)
         return
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    # default exchange: this library's all-reduce kernel (switch reduction, 16 CTAs beside the other chunk's GEMMs). Measured against
-    # NCCL's all-reduce in the same step: 156.5 k against 148.5 k tokens/s on 2 GPUs, 0.330 against 0.454 ms per block on 8
-    comm = args.comm or ("peer_all_reduce" if world > 1 else "all_reduce")
+    # default exchange: this library's fused kernel (sum of the partial results + residual add + rmsnorm + quantize + gather in one
+    # launch per block and chunk, switch reduction). Measured over the full 32 layers, tokens/s: 8 GPUs 483.9 k (32 CTAs) against
+    # 396.9 k with this library's all-reduce kernel and 292 k with NCCL's all-reduce; 2 GPUs 158.2 k (24 CTAs) against 154.9 k and 148.5 k
+    comm = args.comm or ("fused_exchange" if world > 1 else "all_reduce")
+    if args.ar_ctas is None:
+        args.ar_ctas = (24 if world == 2 else 32) if comm == "fused_exchange" else 16
     stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=args.ar_ctas, peer_path=args.peer_path)
     torch.cuda.synchronize()
 
@@ -601,13 +604,13 @@ def run_ours(args) -> None:
         return ms
 
     exchange_note = None
-    if world > 1 and args.comm is None and stack.comm == "peer_all_reduce":
+    if world > 1 and args.comm is None and stack.comm in ("peer_all_reduce", "fused_exchange"):
         # the default picked this library's all-reduce: if its symmetric memory cannot be set up on this machine (every rank sees
         # the same refusal), run the NCCL exchange instead and say so in the line
         try:
             step()
         except Exception as e:  # noqa: BLE001
-            exchange_note = f"peer_all_reduce unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL all_reduce used"
+            exchange_note = f"{stack.comm} unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL all_reduce used"
             stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm="all_reduce", sm_margin=args.ar_ctas)
             launches_per_step = layers * 5 * stack.chunks
     for _ in range(max(args.warmup, 3)):
