@@ -534,9 +534,9 @@ def run_ours(args) -> None:
 
     gx = torch.Generator().manual_seed(0)
     x_all = torch.randn((m, H), generator=gx).to(torch.bfloat16)
-    # scatter_gather keeps every token on one rank outside the GEMMs: each rank uploads, normalises and downloads only its own
+    # scatter_gather and fused_exchange keep every token on one rank outside the GEMMs: each rank uploads, normalises and downloads only its own
     # rows, so the job's input and output cross PCIe once in total (m * H * 2 bytes each way over all ranks)
-    rows_local = world > 1 and stack.comm == "scatter_gather"
+    rows_local = world > 1 and stack.comm in ("scatter_gather", "fused_exchange")
     m_io = m // world if rows_local else m
     x_host = (x_all[rank * m_io:(rank + 1) * m_io] if rows_local else x_all).contiguous().pin_memory()
     out_host = torch.empty((m_io, H), dtype=torch.bfloat16).pin_memory()
@@ -610,8 +610,8 @@ def run_ours(args) -> None:
         try:
             step()
         except Exception as e:  # noqa: BLE001
-            exchange_note = f"{stack.comm} unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL all_reduce used"
-            stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm="all_reduce", sm_margin=args.ar_ctas)
+            exchange_note = f"{stack.comm} unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL collectives used"
+            stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm="scatter_gather" if rows_local else "all_reduce", sm_margin=16)
             launches_per_step = layers * 5 * stack.chunks
     for _ in range(max(args.warmup, 3)):
         step()

@@ -129,6 +129,14 @@ def main() -> int:
                 else:
                     # the switch's sums differ in the last bit, which requantizes everything downstream: quantization noise
                     expect(rel < (0.1 if fmt == "mxfp8" else 0.35), f"fused {fmt} chunks={chunks} {path}: rel {rel}")
+                if path == "multicast_store":
+                    # rows_local: the rank brings and gets back only its rows of every chunk; same bytes as those rows of the full run
+                    rows, rr = m // chunks, m // chunks // world
+                    mine = torch.cat([torch.arange(ci * rows + rank * rr, ci * rows + (rank + 1) * rr) for ci in range(chunks)]).to(dev)
+                    res_l = torch.zeros((m // world, h), dtype=torch.float32, device=dev)
+                    y_l = stack(x[mine].contiguous(), res_l, rows_local=True).float()
+                    torch.cuda.synchronize()
+                    expect(torch.equal(y_l, y[mine]) and torch.equal(res_l, res[mine]), f"fused {fmt} chunks={chunks}: rows_local differs from the full run")
                 if chunks == 2 and path == "multicast_store":
                     res2 = torch.zeros((m, h), dtype=torch.float32, device=dev)
                     cap = stack.capture(x.clone(), res2)

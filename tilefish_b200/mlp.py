@@ -202,14 +202,14 @@ class MlpStack:
         return [buf[2 * i:2 * i + 2] for i in range(len(self.layers))]
 
     def forward(self, x, residual, rows_local: bool = False):
-        """``rows_local`` (scatter_gather only): ``x`` and ``residual`` are THIS RANK'S rows ([M / n, H]) and so is the result: no
+        """``rows_local`` (scatter_gather and fused_exchange): ``x`` and ``residual`` are THIS RANK'S rows ([M / n, H]) and so is the result: no
         rank ever holds the other ranks' tokens outside the GEMMs, and the job's input and output cross PCIe once in total."""
         if self.comm == "scatter_gather":
             return self._forward_row_sharded(x, residual, rows_local)
-        if rows_local:
-            raise TilefishPreconditionError("rows_local needs comm='scatter_gather'", kind="argument", arg="rows_local")
         if self.comm == "fused_exchange":
-            return self._forward_fused(x, residual)
+            return self._forward_fused(x, residual, rows_local)
+        if rows_local:
+            raise TilefishPreconditionError("rows_local needs comm='scatter_gather' or 'fused_exchange'", kind="argument", arg="rows_local")
         if self.comm == "peer_all_reduce" and self._peer_for(x) is not None:
             return self._forward_peer(x, residual)
         if self.chunks <= 1:
@@ -342,10 +342,12 @@ class MlpStack:
             self._last_reduce = None
         return out
 
-    def _forward_fused(self, x, residual):
+    def _forward_fused(self, x, residual, rows_local: bool = False):
         """Row-sharded normalisation with this package's fused exchange kernel. Every rank gets the full ``x`` / ``residual`` and
-        returns the full result (the residual rows of the other ranks arrive with one all-gather at the end). Per block and row
-        chunk: tf_tp_norm_exchange -> gemm + SiLU gate -> (quantize) -> gemm into the symmetric partial buffer."""
+        returns the full result (the residual rows of the other ranks arrive with one all-gather at the end); with
+        ``rows_local`` it gets and returns only its own rows (chunk by chunk: rows [rank * r, (rank + 1) * r) of every chunk),
+        which is all the kernel ever reads of the input. Per block and row chunk: tf_tp_norm_exchange -> gemm + SiLU gate ->
+        (quantize) -> gemm into the symmetric partial buffer."""
         import torch
         import torch.distributed as dist
 
@@ -355,6 +357,8 @@ class MlpStack:
         world = dist.get_world_size(self.group)
         rank = dist.get_rank(self.group)
         m, h = x.shape
+        if rows_local:
+            m *= world
         fmt = self.layers[0].fmt
         c = max(1, self.chunks)
         unit = 128 * world
@@ -407,7 +411,7 @@ class MlpStack:
                     "codes": buf[base + part_b:base + part_b + codes_b].view(rows, h // epb),
                     "scales": buf[base + part_b + codes_b:base + part_b + codes_b + scales_b],
                     "gs": buf[base + part_b + codes_b + scales_b:base + part_b + codes_b + scales_b + 4 * world].view(torch.float32) if fmt == "nvfp4" else None,
-                    "res": residual[ci * rows + rank * r:ci * rows + (rank + 1) * r],
+                    "res": residual[ci * r:(ci + 1) * r] if rows_local else residual[ci * rows + rank * r:ci * rows + (rank + 1) * r],
                 })
             for s in streams:
                 if s is not main:
@@ -416,7 +420,10 @@ class MlpStack:
             for ci in range(c):
                 with torch.cuda.stream(streams[ci]):
                     slots.append(self._amax_slots(ci, x.device))
-                    views[ci]["partial"].copy_(x[ci * rows:(ci + 1) * rows])
+                    if rows_local:  # the first exchange reads this rank's rows only
+                        views[ci]["partial"][rank * r:(rank + 1) * r].copy_(x[ci * r:(ci + 1) * r])
+                    else:
+                        views[ci]["partial"].copy_(x[ci * rows:(ci + 1) * rows])
             for li, w in enumerate(self.layers):
                 for ci in range(c):
                     v = views[ci]
@@ -437,9 +444,12 @@ class MlpStack:
                 v = views[ci]
                 with torch.cuda.stream(streams[ci]):
                     ordered(lambda: peer.allreduce_(v["partial"], channel=ci))
-                    out[ci * rows:(ci + 1) * rows].copy_(v["partial"])
-                    if world > 1:
-                        dist.all_gather_into_tensor(residual[ci * rows:(ci + 1) * rows], v["res"].clone(), group=self.group)
+                    if rows_local:
+                        out[ci * r:(ci + 1) * r].copy_(v["partial"][rank * r:(rank + 1) * r])
+                    else:
+                        out[ci * rows:(ci + 1) * rows].copy_(v["partial"])
+                        if world > 1:
+                            dist.all_gather_into_tensor(residual[ci * rows:(ci + 1) * rows], v["res"].clone(), group=self.group)
             for s in streams:
                 if s is not main:
                     main.wait_stream(s)
