@@ -40,7 +40,7 @@ def parse_args():
     ap.add_argument("--layers", type=int, default=LAYERS, help="development only: fewer layers (the line then says so)")
     ap.add_argument("--tokens", type=int, default=M_TOKENS, help="development only")
     ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
-    ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode"],
+    ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode", "exchange"],
                     help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "fused_exchange", "scatter_gather"],
                     help="tensor-parallel exchange per block (default: fused_exchange = sum + rmsnorm + quantize + gather in one kernel of this library; peer_all_reduce = this library's all-reduce kernel; all_reduce = NCCL; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
@@ -398,6 +398,22 @@ def run_single_kernel(name: str, pdl=None) -> None:
         x = torch.randn((64, H), generator=g, device="cuda").to(torch.bfloat16)
         res = torch.zeros((64, H), device="cuda")
         fn = lambda: stack(x, res)  # noqa: E731
+    elif name == "exchange":  # the fused exchange kernel on one GPU (a single rank: nothing to sum; residual add + rmsnorm + amax + nvfp4 quantize)
+        from tilefish_b200.collective import PeerAllReduce
+
+        rows = 8192
+        part_b, codes_b, scales_b = rows * H * 2, rows * H // 2, K.scale_bytes(FMT, rows, H)
+        peer = PeerAllReduce(part_b + codes_b + scales_b + 256, None, torch.device("cuda"), channels=1, num_ctas=148)
+        peer.buffer[:part_b].view(torch.bfloat16).copy_(torch.randn(rows * H, generator=g, device="cuda").to(torch.bfloat16))
+        res = torch.zeros((rows, H), device="cuda")
+        w = torch.ones(H, dtype=torch.bfloat16, device="cuda")
+        scratch = torch.empty((rows, H), dtype=torch.bfloat16, device="cuda")
+        amax = torch.zeros(1, device="cuda")
+
+        def fn():
+            amax.zero_()
+            peer.norm_exchange_(partial_offset=0, codes_offset=part_b, scales_offset=part_b + codes_b, gs_offset=part_b + codes_b + scales_b, rows_total=rows,
+                                d=H, sum_peers=False, residual_rows=res, w=w, h_scratch=scratch, amax=amax, eps=1e-6, fmt=FMT)
     elif name == "rmsnorm":
         x = torch.randn((8192, H), generator=g, device="cuda").to(torch.bfloat16)
         res = torch.zeros((8192, H), device="cuda")
