@@ -268,9 +268,10 @@ __global__ void __launch_bounds__(512, 1) tp_norm_exchange_kernel(const NxParams
   const unsigned long long g = gridDim.x;
   const unsigned int flag = (unsigned int)(call * 4ull);
   unsigned long long syncs = 0;
-  __shared__ float warp_sums[16];
+  constexpr int kRows = VPT <= 2 ? 2 : 1;  // rows in flight per CTA (registers: 8 f32 per vector per row)
+  __shared__ float warp_sums[kRows][16];
   __shared__ unsigned int warp_amax[16];
-  __shared__ float row_rstd;
+  __shared__ float row_rstd[kRows];
   const int tid = threadIdx.x, nthreads = blockDim.x;
   const int nvec = q.d >> 3;
   const int rows_local = q.rows_total / p.world;
@@ -283,81 +284,101 @@ __global__ void __launch_bounds__(512, 1) tp_norm_exchange_kernel(const NxParams
   // ---- pass 1: sum over the ranks, residual add, normalise (this rank's rows) ----
   uint32_t amax_bits = 0;
   if (ok) {
-    for (int row = blockIdx.x; row < rows_local; row += gridDim.x) {
-      const long long grow = row0 + row;
-      float4* rr = reinterpret_cast<float4*>(q.residual) + (long long)row * (nvec * 2);
-      float r[VPT][8];
-      float acc = 0.0f;
+    // kRows rows per round: their loads are in flight together and they share the two block barriers (the sums of a row are
+    // still formed by the same threads in the same order)
+    for (int base = blockIdx.x * kRows; base < rows_local; base += gridDim.x * kRows) {
+      float r[kRows][VPT][8];
+      float acc[kRows];
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * nthreads;
-        if (v < nvec) {
-          const long long off = q.partial_off + (grow * nvec + v) * 16;
-          uint4 xv;
-          if (!q.sum_peers) {
-            xv = ld_peer_16(p.bufs[p.rank] + off);
-          } else if (p.reduce_in_switch) {
-            multimem_ld_reduce_bf16x8(p.mc_ptr + off, xv);
-          } else {
-            uint4 pv[kArMaxWorld];
+      for (int rw = 0; rw < kRows; ++rw) {
+        const int row = base + rw;
+        acc[rw] = 0.0f;
+        const bool row_ok = row < rows_local;
+        const long long grow = row0 + row;
+        float4* rr = reinterpret_cast<float4*>(q.residual) + (long long)row * (nvec * 2);
 #pragma unroll
-            for (int k = 0; k < kArMaxWorld; ++k)
-              if (k < p.world) pv[k] = ld_peer_16(p.bufs[k] + off);
-            float s[8];
+        for (int i = 0; i < VPT; ++i) {
+          const int v = tid + i * nthreads;
+          if (row_ok && v < nvec) {
+            const long long off = q.partial_off + (grow * nvec + v) * 16;
+            uint4 xv;
+            if (!q.sum_peers) {
+              xv = ld_peer_16(p.bufs[p.rank] + off);
+            } else if (p.reduce_in_switch) {
+              multimem_ld_reduce_bf16x8(p.mc_ptr + off, xv);
+            } else {
+              uint4 pv[kArMaxWorld];
 #pragma unroll
-            for (int j = 0; j < 8; ++j) s[j] = 0.0f;
+              for (int k = 0; k < kArMaxWorld; ++k)
+                if (k < p.world) pv[k] = ld_peer_16(p.bufs[k] + off);
+              float s8[8];
 #pragma unroll
-            for (int k = 0; k < kArMaxWorld; ++k) {
-              if (k < p.world) {
-                s[0] += bf16lo_to_f32(pv[k].x); s[1] += bf16hi_to_f32(pv[k].x); s[2] += bf16lo_to_f32(pv[k].y); s[3] += bf16hi_to_f32(pv[k].y);
-                s[4] += bf16lo_to_f32(pv[k].z); s[5] += bf16hi_to_f32(pv[k].z); s[6] += bf16lo_to_f32(pv[k].w); s[7] += bf16hi_to_f32(pv[k].w);
+              for (int j = 0; j < 8; ++j) s8[j] = 0.0f;
+#pragma unroll
+              for (int k = 0; k < kArMaxWorld; ++k) {
+                if (k < p.world) {
+                  s8[0] += bf16lo_to_f32(pv[k].x); s8[1] += bf16hi_to_f32(pv[k].x); s8[2] += bf16lo_to_f32(pv[k].y); s8[3] += bf16hi_to_f32(pv[k].y);
+                  s8[4] += bf16lo_to_f32(pv[k].z); s8[5] += bf16hi_to_f32(pv[k].z); s8[6] += bf16lo_to_f32(pv[k].w); s8[7] += bf16hi_to_f32(pv[k].w);
+                }
               }
+              xv = make_uint4(pack_bf16x2(s8[0], s8[1]), pack_bf16x2(s8[2], s8[3]), pack_bf16x2(s8[4], s8[5]), pack_bf16x2(s8[6], s8[7]));
             }
-            xv = make_uint4(pack_bf16x2(s[0], s[1]), pack_bf16x2(s[2], s[3]), pack_bf16x2(s[4], s[5]), pack_bf16x2(s[6], s[7]));
+            const float4 a4 = __ldcs(rr + 2 * v), b4 = __ldcs(rr + 2 * v + 1);
+            r[rw][i][0] = __fadd_rn(a4.x, bf16lo_to_f32(xv.x));
+            r[rw][i][1] = __fadd_rn(a4.y, bf16hi_to_f32(xv.x));
+            r[rw][i][2] = __fadd_rn(a4.z, bf16lo_to_f32(xv.y));
+            r[rw][i][3] = __fadd_rn(a4.w, bf16hi_to_f32(xv.y));
+            r[rw][i][4] = __fadd_rn(b4.x, bf16lo_to_f32(xv.z));
+            r[rw][i][5] = __fadd_rn(b4.y, bf16hi_to_f32(xv.z));
+            r[rw][i][6] = __fadd_rn(b4.z, bf16lo_to_f32(xv.w));
+            r[rw][i][7] = __fadd_rn(b4.w, bf16hi_to_f32(xv.w));
+            __stcs(rr + 2 * v, make_float4(r[rw][i][0], r[rw][i][1], r[rw][i][2], r[rw][i][3]));
+            __stcs(rr + 2 * v + 1, make_float4(r[rw][i][4], r[rw][i][5], r[rw][i][6], r[rw][i][7]));
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[rw] = fmaf(r[rw][i][j], r[rw][i][j], acc[rw]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) r[rw][i][j] = 0.0f;
           }
-          const float4 a = __ldcs(rr + 2 * v), b = __ldcs(rr + 2 * v + 1);
-          r[i][0] = __fadd_rn(a.x, bf16lo_to_f32(xv.x));
-          r[i][1] = __fadd_rn(a.y, bf16hi_to_f32(xv.x));
-          r[i][2] = __fadd_rn(a.z, bf16lo_to_f32(xv.y));
-          r[i][3] = __fadd_rn(a.w, bf16hi_to_f32(xv.y));
-          r[i][4] = __fadd_rn(b.x, bf16lo_to_f32(xv.z));
-          r[i][5] = __fadd_rn(b.y, bf16hi_to_f32(xv.z));
-          r[i][6] = __fadd_rn(b.z, bf16lo_to_f32(xv.w));
-          r[i][7] = __fadd_rn(b.w, bf16hi_to_f32(xv.w));
-          __stcs(rr + 2 * v, make_float4(r[i][0], r[i][1], r[i][2], r[i][3]));
-          __stcs(rr + 2 * v + 1, make_float4(r[i][4], r[i][5], r[i][6], r[i][7]));
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc = fmaf(r[i][j], r[i][j], acc);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 8; ++j) r[i][j] = 0.0f;
         }
       }
-      for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xFFFFFFFFu, acc, o);
-      if ((tid & 31) == 0) warp_sums[tid >> 5] = acc;
+#pragma unroll
+      for (int rw = 0; rw < kRows; ++rw) {
+        for (int o = 16; o > 0; o >>= 1) acc[rw] += __shfl_xor_sync(0xFFFFFFFFu, acc[rw], o);
+        if ((tid & 31) == 0) warp_sums[rw][tid >> 5] = acc[rw];
+      }
       __syncthreads();
       if (tid < 32) {
-        float s = (tid < (nthreads >> 5)) ? warp_sums[tid] : 0.0f;
-        for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-        if (tid == 0) row_rstd = __frsqrt_rn(__fadd_rn(__fmul_rn(s, q.inv_d), q.eps));
-      }
-      __syncthreads();
-      const float rstd = row_rstd;
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * nthreads;
-        if (v < nvec) {
-          const uint4 wv = __ldg(q.w + v);
-          uint4 o;
-          o.x = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][0], rstd), bf16lo_to_f32(wv.x)), __fmul_rn(__fmul_rn(r[i][1], rstd), bf16hi_to_f32(wv.x)));
-          o.y = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][2], rstd), bf16lo_to_f32(wv.y)), __fmul_rn(__fmul_rn(r[i][3], rstd), bf16hi_to_f32(wv.y)));
-          o.z = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][4], rstd), bf16lo_to_f32(wv.z)), __fmul_rn(__fmul_rn(r[i][5], rstd), bf16hi_to_f32(wv.z)));
-          o.w = pack_bf16x2(__fmul_rn(__fmul_rn(r[i][6], rstd), bf16lo_to_f32(wv.w)), __fmul_rn(__fmul_rn(r[i][7], rstd), bf16hi_to_f32(wv.w)));
-          q.h_scratch[(long long)row * nvec + v] = o;
-          amax_bits = max(amax_bits, amax_bits8(o));
+        for (int rw = 0; rw < kRows; ++rw) {
+          float s = (tid < (nthreads >> 5)) ? warp_sums[rw][tid] : 0.0f;
+          for (int o = 8; o > 0; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+          if (tid == 0) row_rstd[rw] = __frsqrt_rn(__fadd_rn(__fmul_rn(s, q.inv_d), q.eps));
         }
       }
-      __syncthreads();  // warp_sums / row_rstd are reused by the next row
+      __syncthreads();
+#pragma unroll
+      for (int rw = 0; rw < kRows; ++rw) {
+        const int row = base + rw;
+        const float rstd = row_rstd[rw];
+        if (row < rows_local) {
+#pragma unroll
+          for (int i = 0; i < VPT; ++i) {
+            const int v = tid + i * nthreads;
+            if (v < nvec) {
+              const uint4 wv = __ldg(q.w + v);
+              uint4 o;
+              o.x = pack_bf16x2(__fmul_rn(__fmul_rn(r[rw][i][0], rstd), bf16lo_to_f32(wv.x)), __fmul_rn(__fmul_rn(r[rw][i][1], rstd), bf16hi_to_f32(wv.x)));
+              o.y = pack_bf16x2(__fmul_rn(__fmul_rn(r[rw][i][2], rstd), bf16lo_to_f32(wv.y)), __fmul_rn(__fmul_rn(r[rw][i][3], rstd), bf16hi_to_f32(wv.y)));
+              o.z = pack_bf16x2(__fmul_rn(__fmul_rn(r[rw][i][4], rstd), bf16lo_to_f32(wv.z)), __fmul_rn(__fmul_rn(r[rw][i][5], rstd), bf16hi_to_f32(wv.z)));
+              o.w = pack_bf16x2(__fmul_rn(__fmul_rn(r[rw][i][6], rstd), bf16lo_to_f32(wv.w)), __fmul_rn(__fmul_rn(r[rw][i][7], rstd), bf16hi_to_f32(wv.w)));
+              q.h_scratch[(long long)row * nvec + v] = o;
+              amax_bits = max(amax_bits, amax_bits8(o));
+            }
+          }
+        }
+      }
+      __syncthreads();  // warp_sums / row_rstd are reused by the next round
     }
     if (QFMT == TF_FMT_NVFP4) {  // the row block's amax: one atomic per CTA
       for (int o = 16; o > 0; o >>= 1) amax_bits = max(amax_bits, __shfl_xor_sync(0xFFFFFFFFu, amax_bits, o));
