@@ -11,7 +11,8 @@
 //               to nearest even once) and multimem.st writes the result to all ranks. Each GPU receives about 2 x size bytes.
 //   peer loads  (no multicast mapping): the same sum, stored into the rank's own buffer; after a barrier every rank copies
 //               the other slices from their owners.
-// No TMA anywhere in this file.
+// No TMA anywhere in this file. The second kernel of the file, tp_norm_exchange_kernel, fuses the same sum with the next block's
+// residual add, rmsnorm and quantization and gathers the quantized rows instead (its own comment is further down).
 //
 // Cross-GPU barriers are flags in peer memory: every rank stores a monotonically increasing value into its slot of every
 // peer's flag array (st.release.sys) and spins on its own array (ld.acquire.sys). The value is derived from a call counter kept
