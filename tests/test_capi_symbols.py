@@ -76,3 +76,30 @@ def test_allreduce_refuses_bad_arguments_before_any_launch():
     assert b"num_ctas" in lib.tf_last_error()
     bad = (ctypes.c_uint64 * 2)(0x1000, 0x2004)
     assert call(bad, ptrs, 0, 0, 0, 2, 0, 16, 8, None) != 0                  # unaligned peer pointer
+
+
+def test_norm_exchange_refuses_bad_arguments_before_any_launch():
+    """tf_tp_norm_exchange decides its argument errors on the host: this runs without a GPU."""
+    import ctypes
+
+    from tilefish_b200 import _native
+
+    if not os.path.exists(_native.LIB_PATH):
+        pytest.skip("library not built here (python tilefish_b200/csrc/build.py)")
+    lib = _native.load()
+    ptrs = (ctypes.c_uint64 * 2)(0x1000, 0x2000)
+    buf = ctypes.c_void_p(0x4000)
+
+    def call(world=2, rank=0, rows=256, d=1024, fmt=2, ctas=8, part=0, amax=buf, res=buf):
+        return lib.tf_tp_norm_exchange(ptrs, ptrs, 0, 0, rank, world, part, 4096, 8192, 12288, rows, d, 1, res, buf, buf, amax, 1e-6, fmt, ctas, None)
+
+    assert call(world=9) != 0                 # more ranks than the kernel's tables hold
+    assert call(rank=2) != 0                  # rank outside the group
+    assert call(rows=128) != 0                # rows not a multiple of 128 x world
+    assert b"128 x world" in lib.tf_last_error()
+    assert call(d=1000) != 0                  # row length not a multiple of 128
+    assert call(fmt=7) != 0                   # unknown format
+    assert call(amax=None) != 0               # nvfp4 needs the amax word
+    assert call(ctas=0) != 0                  # no CTAs
+    assert call(part=8) != 0                  # offset not a multiple of 16
+    assert call(res=None) != 0                # no residual rows
