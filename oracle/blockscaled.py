@@ -283,6 +283,100 @@ def decoder_block(x, residual, w_n, q_gu, q_d, fmt: str, eps: float = 1e-6):
 
 
 # ----------------------------------------------------------------------------------------------------------------------
+# the tensor-parallel MLP stack, restated rank by rank (no counterpart in the reference, which has no cross-device exchange:
+# this is the definition the multi-GPU kernels are checked against)
+# ----------------------------------------------------------------------------------------------------------------------
+def tp_shard_gu(q_gu, fmt: str, rank: int, world: int):
+    """Rank ``rank``'s rows of the quantized ``w_gu`` [2F, H]: gate rows [rF/n, (r+1)F/n) and the matching up rows."""
+    f = q_gu[0].shape[0] // 2
+    fl = f // world
+    rows = torch.cat([torch.arange(rank * fl, (rank + 1) * fl), torch.arange(f + rank * fl, f + (rank + 1) * fl)])
+    return (q_gu[0][rows], q_gu[1][rows], q_gu[2])
+
+
+def tp_shard_d(q_d, fmt: str, rank: int, world: int):
+    """Rank ``rank``'s K-slice of the quantized ``w_d`` [H, F]: columns [rF/n, (r+1)F/n) of codes and of block scales."""
+    elem, _, block, _ = FORMATS[fmt]
+    epb = 1 if elem == "e4m3" else 2
+    f = q_d[1].shape[1] * block
+    fl = f // world
+    return (q_d[0][:, rank * fl // epb:(rank + 1) * fl // epb].contiguous(), q_d[1][:, rank * fl // block:(rank + 1) * fl // block].contiguous(), q_d[2])
+
+
+def rank_order_sum_bf16(parts) -> torch.Tensor:
+    """bf16( ((0 + p0) + p1) + ... ): the ranks' bf16 partial results summed in f32 in rank order and rounded once, which is
+    what the peer-load paths of the exchange kernels compute (tilefish_b200/csrc/allreduce.cu)."""
+    acc = torch.zeros_like(parts[0], dtype=torch.float32)
+    for p in parts:
+        acc = acc + p.to(torch.float32)
+    return f32_to_bf16(acc)
+
+
+def _gemm_rowblocks(qa_blocks, qb, fmt: str) -> torch.Tensor:
+    """bf16( deq(A) @ deq(B)^T ) where A is a stack of row blocks that were quantized separately (each with its own nvfp4
+    global scale): the GEMM's ``a_global_scale_rows`` form."""
+    a = torch.cat([dequantize(c, s, fmt, g) for (c, s, g) in qa_blocks])
+    b = dequantize(qb[0], qb[1], fmt, qb[2])
+    return f32_to_bf16(a @ b.t())
+
+
+def tp_mlp_stack(x, residual, layers, fmt: str, world: int, *, norm: str = "replicated", spans=None, eps: float = 1e-6):
+    """The tensor-parallel MLP stack as the kernels compute it, on one CPU. Returns (residual_out f32, y bf16).
+
+    ``layers``: [(w_n bf16 [H], quantize(w_gu), quantize(w_d))] with the FULL quantized weights (plain scales); every rank's
+    shard is cut from them. ``spans``: the row chunks [(begin, end)] (each chunk is its own tensor for the nvfp4 global
+    scales); default one chunk.
+
+    ``norm="replicated"`` (exchange = all-reduce of the partial results): per block and chunk
+        h = rmsnorm(residual += x);  hq = quantize(h)           (nvfp4: global scale of the chunk's amax)
+        rank r:  a_r = silu_gate(bf16 gemm(hq, w_gu shard r));  aq_r = quantize(a_r)   (nvfp4: amax of ITS [rows, F/n])
+                 y_r = bf16 gemm(aq_r, w_d shard r)
+        x_next = rank_order_sum_bf16(y_0 .. y_{n-1})
+    ``norm="row_sharded"`` (the fused exchange and the scatter/gather mode): rank r normalises and quantizes rows
+        [r R, (r+1) R) of every chunk (R = rows / n), nvfp4 with the global scale of ITS row block; the first GEMM multiplies the
+        gathered row blocks, each with its own global scale; everything else as above.
+    """
+    assert norm in ("replicated", "row_sharded")
+    m = x.shape[0]
+    spans = spans or [(0, m)]
+    res = residual.clone()
+    xs = x
+    for (w_n, q_gu, q_d) in layers:
+        nxt = torch.empty_like(xs)
+        for (lo, hi) in spans:
+            r, h = residual_add_rmsnorm(xs[lo:hi], res[lo:hi], w_n, eps)
+            res[lo:hi] = r
+            if norm == "replicated":
+                blocks = [quantize(h, fmt)]
+            else:
+                rr = (hi - lo) // world
+                assert rr * world == hi - lo
+                blocks = [quantize(h[k * rr:(k + 1) * rr], fmt) for k in range(world)]
+            parts = []
+            for rank in range(world):
+                sh_gu = tp_shard_gu(q_gu, fmt, rank, world)
+                t = _gemm_rowblocks(blocks, sh_gu, fmt)
+                fl = t.shape[1] // 2
+                a = silu_gate(t[:, :fl], t[:, fl:])
+                parts.append(gemm_bf16_a(a, tp_shard_d(q_d, fmt, rank, world), fmt))
+            nxt[lo:hi] = rank_order_sum_bf16(parts)
+        xs = nxt
+    return res, xs
+
+
+def compare(got: torch.Tensor, ref: torch.Tensor) -> dict:
+    """The figures every parity statement of a bf16 result uses: max|d| / max|ref|, relative Frobenius error, fraction of
+    elements that differ."""
+    g, r = got.to(torch.float32), ref.to(torch.float32)
+    top = float(r.abs().max())
+    return {
+        "max_rel": float((g - r).abs().max()) / (top if top > 0 else 1.0),
+        "rel_fro": float((g - r).norm() / r.norm()) if float(r.norm()) > 0 else float((g - r).norm()),
+        "frac_diff": float((g != r).float().mean()),
+    }
+
+
+# ----------------------------------------------------------------------------------------------------------------------
 # seeded synthetic inputs of the benchmark configurations
 # ----------------------------------------------------------------------------------------------------------------------
 def randn(shape, seed: int, dtype=torch.float32, scale: float = 1.0) -> torch.Tensor:

@@ -61,6 +61,21 @@ def test_quantize_is_bit_exact(K, fmt, m, k):
 
 
 @pytest.mark.parametrize("fmt", FMTS)
+@pytest.mark.parametrize("m,k", [(300, 2048), (160, 2560), (100, 4128), (24, 28672), (297, 8192)])
+def test_quantize_long_rows_streaming_form_is_bit_exact(K, fmt, m, k):
+    """Long rows: the mxfp8 quantizer and the nvfp4 amax pass stage rows of at least 2048 elements through a shared-memory ring
+    (bulk copies of 4 KB row chunks) once there are enough chunks to fill the GPU; the e2m1 quantizers keep the register form.
+    Full chunks, a ragged last chunk per row, many chunks per row, and a strided input."""
+    x = O.outlier_input(m, k, seed=m + k)
+    check_quant(K, x, fmt, "swizzled")
+    wide = torch.zeros((m, k + 64), dtype=torch.bfloat16)
+    wide[:, :k] = x
+    q = K.quantize(wide.cuda()[:, :k], fmt, layout="plain")
+    codes, scales, _ = O.quantize(x, fmt)
+    assert torch.equal(q.codes.cpu(), codes) and torch.equal(q.plain_scales().cpu(), scales)
+
+
+@pytest.mark.parametrize("fmt", FMTS)
 def test_quantize_sweep_point_8192_is_bit_exact(K, fmt):
     """M = 8192, K = 4096 with 1 % outliers x100 (a point of the quantize sweep), every byte compared with the oracle."""
     x = O.outlier_input(8192, 4096, seed=0)

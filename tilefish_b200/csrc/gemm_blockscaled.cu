@@ -1,8 +1,12 @@
 // Block-scaled GEMM for sm_100a: out[M,N] = bf16( sum_k deq(a)[m,k] * deq(b)[n,k] ), f32 accumulation in tensor memory.
 //
 // One persistent CTA per SM walks output tiles of 128 x BLOCK_N. Three warp roles:
-//   warp 0   producer: TMA tiled loads of the A and B code tiles (128-byte swizzle) and bulk copies of the pre-swizzled
-//            scale tiles into a ring of shared-memory stages, signalled through mbarriers (complete_tx)
+//   warp 0   operand loads: TMA tiled loads of the A and B code tiles (128-byte swizzle) into a ring of shared-memory stages,
+//            signalled through mbarriers (complete_tx). ONE instruction per stage: lane 0 loads the A tile, lanes 1-2 the
+//            128-row halves of the B tile (issuing a TMA copy costs the issuing thread 40-90 clocks; six copies issued one
+//            after another by one thread made that thread, not the memory system, the limit of the whole kernel)
+//   warp 6   scale loads: bulk copies of the pre-swizzled scale tiles of the same stage, again one instruction (lane 0 the A
+//            scales, lanes 1-2 the B scales); both load warps arrive on the stage's "full" barrier with their own byte counts
 //   warp 1   MMA issuer: copies the scale tiles shared -> tensor memory (tcgen05.cp) and issues
 //            tcgen05.mma.kind::{mxf8f6f4, mxf4, mxf4nvf4}.block_scale, 4 per stage (32 bytes of K each); tcgen05.commit frees
 //            the stage and, after the last one, hands the accumulator to the epilogue
@@ -20,6 +24,7 @@
 
 #include <cstdlib>
 
+#include "async_copy.cuh"
 #include "quant_core.cuh"
 
 namespace tf {
@@ -29,7 +34,8 @@ __device__ int g_device_status[2];  // [0] status, [1] detail
 constexpr int kBlockM = 128;
 constexpr int kStageKBytes = 128;  // bytes of K per row per stage: one 128-byte swizzle atom
 constexpr int kAStageBytes = kBlockM * kStageKBytes;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmThreads = 224;  // 7 warps: operand loads, MMA issue, 4 epilogue warps, scale loads (one-CTA kernel)
+constexpr int kPairThreads = 192;  // the CTA-pair kernel keeps one load warp
 constexpr int kSmemLimit = 227 * 1024;
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
 
@@ -101,19 +107,6 @@ struct GemmParams {
 };
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) { asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory"); }
 // ---- thread-block-cluster helpers (the 2-CTA kernel) ----
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
@@ -173,39 +166,14 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d, uint64_t a, uint64_t b, 
   }
 }
 
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 // Bounded wait. Returns false when the limit ran out here or another role already gave up (abort flag).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where,
                                           unsigned long long limit_ns = kWaitLimitNs) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  for (uint32_t spins = 1;; ++spins) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((spins & 0x3F) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > limit_ns) {
-        *abort_flag = 1;
-        if (atomicCAS(&g_device_status[0], 0, TF_ERR_DEVICE_TIMEOUT) == 0) g_device_status[1] = where * 65536 + (int)blockIdx.x;
-        return false;
-      }
-    }
-  }
+  return mbar_wait_bounded(bar, parity, abort_flag, g_device_status, where, limit_ns);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(dst), "l"(map),
                "r"(x), "r"(y), "r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
                : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -558,7 +526,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_full + 8 * s, 2);  // the operand-load warp and the scale-load warp
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_tmem_full, 1);
@@ -576,61 +544,61 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
   const uint32_t tmem_base = *tmem_slot_ptr;
   griddep_wait();  // barriers and tensor memory are set up; nothing of global memory was touched before the previous kernel is done
 
-  if (warp == 0) {
-    // ---------------- producer ----------------
-    if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
-        const int split = SPLITK ? tile / (p.m_blocks * p.n_blocks) : 0;
-        const int rest = SPLITK ? tile % (p.m_blocks * p.n_blocks) : tile;
-        const int m_blk = rest % p.m_blocks, n_blk = rest / p.m_blocks;
-        const int ks_begin = split * p.k_stages_per_split;
-        const int ks_end = min(ks_begin + p.k_stages_per_split, p.num_k_stages);
-        int b_row[kNB], b_rt[kNB];
-        bool b_ok[kNB];
+  if (warp == 0 || warp == 6) {
+    // ---------------- load warps: warp 0 the operand tiles (TMA), warp 6 the scale tiles (bulk copies) ----------------
+    // The whole warp runs the loops; lane 0 serves the A side, lane 1 + nb the 128-row half nb of the B tile, so that one
+    // instruction per stage issues all of the warp's copies.
+    const bool scales = warp == 6;
+    const int nb = lane - 1;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x) {
+      const int split = SPLITK ? tile / (p.m_blocks * p.n_blocks) : 0;
+      const int rest = SPLITK ? tile % (p.m_blocks * p.n_blocks) : tile;
+      const int m_blk = rest % p.m_blocks, n_blk = rest / p.m_blocks;
+      const int ks_begin = split * p.k_stages_per_split;
+      const int ks_end = min(ks_begin + p.k_stages_per_split, p.num_k_stages);
+      int n_b_ok = 0;  // B halves that lie inside the matrix (uniform)
 #pragma unroll
-        for (int nb = 0; nb < kNB; ++nb) {
-          b_row[nb] = (EPI == TF_EPI_SILU_GATE) ? nb * p.n + n_blk * 128 : n_blk * BLOCK_N + nb * 128;
-          b_rt[nb] = b_row[nb] >> 7;
-          b_ok[nb] = b_row[nb] < p.n_rows_b;
-        }
-        for (int ks = ks_begin; ks < ks_end; ++ks) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1)) {
-            ok = false;
-            break;
-          }
+      for (int i = 0; i < kNB; ++i)
+        n_b_ok += (((EPI == TF_EPI_SILU_GATE) ? i * p.n + n_blk * 128 : n_blk * BLOCK_N + i * 128) < p.n_rows_b) ? 1 : 0;
+      // this lane's copy: source row (operands) or scale row-tile, destination inside a stage
+      const int my_row = lane == 0 ? m_blk * kBlockM : ((EPI == TF_EPI_SILU_GATE) ? nb * p.n + n_blk * 128 : n_blk * BLOCK_N + nb * 128);
+      const bool mine = lane == 0 || (lane <= kNB && my_row < p.n_rows_b);
+      const CUtensorMap* my_map = lane == 0 ? &tma_a : &tma_b;
+      const uint32_t my_dst = scales ? (lane == 0 ? smem_sfa : smem_sfb + (uint32_t)(nb < 0 ? 0 : nb) * kST * 512)
+                                     : (lane == 0 ? smem_a : smem_b + (uint32_t)(nb < 0 ? 0 : nb) * 128 * kStageKBytes);
+      const uint32_t my_stage_bytes = scales ? (lane == 0 ? Cfg::kSfaStageBytes : Cfg::kSfbStageBytes) : (lane == 0 ? kAStageBytes : Cfg::kBStageBytes);
+      const uint8_t* my_sf = (lane == 0 ? p.sfa : p.sfb) + (int64_t)((lane == 0 ? my_row : (my_row < 0 ? 0 : my_row)) >> 7) * p.sf_col_tiles * 512;
+      for (int ks = ks_begin; ks < ks_end; ++ks) {
+        ok = mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, 1);
+        ok = __all_sync(0xFFFFFFFFu, ok);
+        if (!ok) break;
+        const uint32_t full = bar_full + 8 * stage;
+        if (scales) {
           int sf_tiles = p.sf_col_tiles - ks * kST;
           sf_tiles = sf_tiles > kST ? kST : sf_tiles;
           const uint32_t sf_bytes = (uint32_t)sf_tiles * 512u;
-          uint32_t tx = (uint32_t)p.a_box_bytes + sf_bytes;
-#pragma unroll
-          for (int nb = 0; nb < kNB; ++nb)
-            if (b_ok[nb]) tx += 128 * kStageKBytes + sf_bytes;
-          const uint32_t full = bar_full + 8 * stage;
-          mbar_expect_tx(full, tx);
-          tma_load_2d(smem_a + stage * kAStageBytes, &tma_a, ks * kStageKBytes, m_blk * kBlockM, full);
-          bulk_load(smem_sfa + stage * Cfg::kSfaStageBytes, p.sfa + ((int64_t)m_blk * p.sf_col_tiles + (int64_t)ks * kST) * 512, sf_bytes, full);
-#pragma unroll
-          for (int nb = 0; nb < kNB; ++nb) {
-            if (b_ok[nb]) {
-              tma_load_2d(smem_b + stage * Cfg::kBStageBytes + nb * 128 * kStageKBytes, &tma_b, ks * kStageKBytes, b_row[nb], full);
-              bulk_load(smem_sfb + stage * Cfg::kSfbStageBytes + nb * kST * 512,
-                        p.sfb + ((int64_t)b_rt[nb] * p.sf_col_tiles + (int64_t)ks * kST) * 512, sf_bytes, full);
-            }
-          }
-          if (++stage == kStages) {
-            stage = 0;
-            phase ^= 1;
-          }
+          if (lane == 0) mbar_expect_tx(full, sf_bytes * (uint32_t)(1 + n_b_ok));
+          __syncwarp();
+          if (mine) bulk_load(my_dst + stage * my_stage_bytes, my_sf + (int64_t)ks * kST * 512, sf_bytes, full);
+        } else {
+          if (lane == 0) mbar_expect_tx(full, (uint32_t)p.a_box_bytes + (uint32_t)n_b_ok * (128u * kStageKBytes));
+          __syncwarp();
+          if (mine) tma_load_2d(my_dst + stage * my_stage_bytes, my_map, ks * kStageKBytes, my_row, full);
+        }
+        __syncwarp();
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1;
         }
       }
-      if (!ok) {
-        // give copies already in flight time to land before shared memory is released
-        const unsigned long long t0 = globaltimer_ns();
-        while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-      }
+    }
+    if (!ok && lane == 0) {
+      // give copies already in flight time to land before shared memory is released
+      const unsigned long long t0 = globaltimer_ns();
+      while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -795,7 +763,7 @@ struct PairCfg {
 };
 
 template <int FMT, int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
+__global__ void __launch_bounds__(kPairThreads, 1) gemm_blockscaled_pair_kernel(const __grid_constant__ CUtensorMap tma_a,
                                                                                  const __grid_constant__ CUtensorMap tma_b,
                                                                                  const __grid_constant__ CUtensorMap tma_sfa,
                                                                                  const __grid_constant__ CUtensorMap tma_sfb, const GemmParams p) {
@@ -1147,7 +1115,7 @@ static tf_status launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, 
   if (p.num_tiles < pairs) pairs = p.num_tiles;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
-  cfg.blockDim = dim3(kGemmThreads);
+  cfg.blockDim = dim3(kPairThreads);
   cfg.dynamicSmemBytes = PC::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1221,6 +1189,19 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
 // from load to process exit. Host code may not use this name as a pointer: it is a host-side stand-in for the symbol.
 constexpr int64_t kStaticScratchBytes = 8ll << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+int* device_status_words() {
+  constexpr int kMaxDevices = 64;
+  static int* cached[kMaxDevices] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+  if (!cached[dev]) {
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_device_status) != cudaSuccess) return nullptr;
+    cached[dev] = static_cast<int*>(ptr);
+  }
+  return cached[dev];
+}
 
 }  // namespace tf
 

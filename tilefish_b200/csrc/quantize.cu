@@ -3,6 +3,7 @@
 // HBM-bound: every thread moves one 256-bit vector of 16 bf16 per step (coalesced: consecutive lanes, consecutive
 // vectors), block maxima are combined with at most one warp shuffle, codes leave as 16-byte (e4m3) or 8-byte (e2m1)
 // coalesced stores. Algorithmic bytes per element: 2 + 1 + 1/32 (mxfp8), 2 + 0.5 + 1/32 (mxfp4), 2 + 0.5 + 1/16 (nvfp4).
+#include "async_copy.cuh"
 #include "quant_core.cuh"
 
 namespace tf {
@@ -70,6 +71,168 @@ __global__ void __launch_bounds__(kQuantThreads) quantize_rows_kernel(const uint
       }
     }
   }
+}
+
+// ---- the streaming form: rows staged through a shared-memory ring by bulk copies -------------------------------------------
+// Used by the mxfp8 quantizer and the amax pass (see use_ring). For long rows (k >= 2048) the input is cut into chunks of up to 2048 consecutive bf16 of one row (4 KB). Every CTA owns a ring
+// of kRingStages chunk buffers; thread 0 keeps the ring full with cp.async.bulk (one 4 KB request per chunk, completion counted
+// on an mbarrier), so each CTA has (kRingStages - 1) x 4 KB in flight whatever its threads are doing, and eight CTAs fit on an
+// SM: the loads no longer wait for registers. The 128 threads then take 32 bytes each from the stage (16 consecutive bf16,
+// the same thread <-> element mapping and the same arithmetic as quantize_rows_kernel, hence the same bytes), hand the stage
+// back, and quantize and store while the next copies are in flight. Waits are bounded (async_copy.cuh).
+constexpr int kRingThreads = 128;
+constexpr int kRingChunkVecs = kRingThreads;        // 16-element vectors per chunk
+constexpr int kRingChunkBytes = kRingChunkVecs * 32;
+constexpr int kRingMaxStages = 8;
+constexpr unsigned long long kRingWaitLimitNs = 1000000000ull;
+constexpr int kModeAmax = 3;  // MODE of ring_rows_kernel beyond the three formats: only the tensor's amax
+
+__device__ __forceinline__ void lds_256(uint32_t addr, uint32_t (&w)[8]) {
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]) : "r"(addr));
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "r"(addr + 16));
+}
+
+// Dynamic shared memory: `stages` chunk buffers of 4 KB, then one mbarrier per stage.
+template <int MODE>
+__global__ void __launch_bounds__(kRingThreads) ring_rows_kernel(const uint8_t* __restrict__ x, int64_t m, int64_t k, int64_t ldx,
+                                                                 uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int swizzled,
+                                                                 const float* __restrict__ gs_ptr, float* __restrict__ gs_out,
+                                                                 unsigned int* __restrict__ amax_bits_out, int* __restrict__ status, int stages) {
+  extern __shared__ __align__(128) uint8_t ring_smem[];
+  __shared__ int abort_flag;
+  constexpr int FMT = MODE == kModeAmax ? TF_FMT_MXFP8 : MODE;
+  const uint32_t ring = smem_u32(ring_smem);
+  const uint32_t bars = ring + (uint32_t)stages * kRingChunkBytes;
+  const int t = threadIdx.x;
+  const int nvec = (int)(k >> 4);
+  const int cpr = (nvec + kRingChunkVecs - 1) / kRingChunkVecs;  // chunks per row
+  const int64_t total = m * cpr;
+  const int64_t stride = gridDim.x;
+  if (t == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(bars + 8 * s, 1);
+    abort_flag = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  griddep_launch_dependents();
+  griddep_wait();
+
+  float gs = 0.0f, inv_t = 0.0f;
+  if (MODE == TF_FMT_NVFP4) {
+    gs = __ldg(gs_ptr);
+    if (gs_out != nullptr) {
+      gs = __fdiv_rn(gs, 2688.0f);
+      if (blockIdx.x == 0 && t == 0) gs_out[0] = gs;
+    }
+    inv_t = gs != 0.0f ? __frcp_rn(__fmul_rn(6.0f, gs)) : 0.0f;
+  }
+
+  // thread 0: one bulk copy per chunk; a chunk is vectors [c * 128, min(nvec, c * 128 + 128)) of its row
+  auto issue = [&](int64_t chunk, int stage) {
+    const int64_t row = chunk / cpr;
+    const int v0 = (int)(chunk - row * cpr) * kRingChunkVecs;
+    const int nv = min(kRingChunkVecs, nvec - v0);
+    const uint32_t bar = bars + 8 * stage;
+    mbar_expect_tx(bar, (uint32_t)nv * 32u);
+    bulk_load(ring + (uint32_t)stage * kRingChunkBytes, x + (row * ldx + (int64_t)v0 * 16) * 2, (uint32_t)nv * 32u, bar);
+  };
+  int64_t chunk = blockIdx.x;
+  if (t == 0) {
+    for (int s = 0; s < stages; ++s)
+      if (chunk + s * stride < total) issue(chunk + s * stride, s);
+  }
+  uint32_t acc = 0;  // MODE == kModeAmax: two packed 16-bit maxima
+  int stage = 0;
+  uint32_t phase = 0;
+  for (; chunk < total; chunk += stride) {
+    const int64_t row = chunk / cpr;
+    const int v0 = (int)(chunk - row * cpr) * kRingChunkVecs;
+    const bool has = v0 + t < nvec;
+    bool ok = mbar_wait_bounded(bars + 8 * stage, phase, &abort_flag, status, 10, kRingWaitLimitNs);
+    uint32_t w[8];
+    if (ok && has) {
+      lds_256(ring + (uint32_t)stage * kRingChunkBytes + t * 32, w);
+    } else {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) w[e] = 0;
+    }
+    // every thread has taken its bytes (or the wait ran out somewhere: then all leave together)
+    if (!__syncthreads_and(ok)) break;
+    if (t == 0 && chunk + stages * stride < total) issue(chunk + stages * stride, stage);
+    if (MODE == kModeAmax) {
+      const uint32_t km = 0x7FFF7FFFu;
+      uint32_t t0 = __vimax3_u16x2(w[0] & km, w[1] & km, w[2] & km);
+      uint32_t t1 = __vimax3_u16x2(w[3] & km, w[4] & km, w[5] & km);
+      t0 = __vimax3_u16x2(t0, w[6] & km, w[7] & km);
+      acc = __vimax3_u16x2(acc, t0, t1);
+    } else {
+      uint32_t c[4], sc;
+      quantize_vec16<FMT>(w, gs, inv_t, c, sc);  // whole warps: lanes without data quantize zeros
+      if (has) store_quantized16<FMT>(codes, scales, swizzled, row, v0 + t, k, c, sc);
+    }
+    if (++stage == stages) {
+      stage = 0;
+      phase ^= 1;
+    }
+  }
+  if (MODE == kModeAmax) {
+    uint32_t mx = max(acc & 0xFFFFu, acc >> 16);
+    for (int o = 16; o > 0; o >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    __shared__ uint32_t warp_max[kRingThreads / 32];
+    if ((t & 31) == 0) warp_max[t >> 5] = mx;
+    __syncthreads();
+    if (t == 0) {
+      for (int wi = 1; wi < kRingThreads / 32; ++wi) mx = max(mx, warp_max[wi]);
+      if (mx) atomicMax(amax_bits_out, mx << 16);
+    }
+  }
+  if (t == 0 && abort_flag) {  // a wait ran out: give copies still in flight time to land before shared memory is released
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+}
+
+// Whether the streaming form serves this shape: rows of at least one full chunk, enough chunks to fill the GPU once. Measured on
+// B200 (65536 x 4096, back-to-back launches): the amax pass gains 10 % (96 % of the copy rate) and mxfp8 9 % (90 %); the
+// e2m1 formats are issue-bound rather than load-bound and lose, so they keep the register form.
+static bool use_ring(int mode, int64_t m, int64_t k) {
+  if (mode != TF_FMT_MXFP8 && mode != kModeAmax) return false;
+  const int64_t cpr = ((k >> 4) + kRingChunkVecs - 1) / kRingChunkVecs;
+  return k >= 2048 && m * cpr >= 2 * (int64_t)sm_count();
+}
+
+struct RingLaunch {
+  unsigned grid;
+  int stages;
+  size_t smem;
+};
+
+// Ring depth and CTAs per SM: stages x 4 KB per CTA, CTAs x that per SM in flight.
+static RingLaunch ring_launch(int mode, int64_t m, int64_t k) {
+  RingLaunch r;
+  r.stages = 4;
+  const int ctas_per_sm = mode == kModeAmax ? 8 : 6;
+  r.smem = (size_t)r.stages * kRingChunkBytes + 8 * (size_t)r.stages;
+  const int64_t cpr = ((k >> 4) + kRingChunkVecs - 1) / kRingChunkVecs;
+  const int64_t total = m * cpr, cap = (int64_t)sm_count() * ctas_per_sm;
+  r.grid = (unsigned)(total < cap ? total : cap);
+  return r;
+}
+
+template <int MODE>
+static cudaError_t ring_configure() {
+  static thread_local int configured_dev = -1;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (configured_dev == dev) return cudaSuccess;
+  e = cudaFuncSetAttribute(ring_rows_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kRingMaxStages * (kRingChunkBytes + 8));
+  if (e != cudaSuccess) return e;
+  // the ring is all these kernels use of the SM's memory: let the carve-out hold as many CTAs' rings as possible
+  e = cudaFuncSetAttribute(ring_rows_kernel<MODE>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+  if (e != cudaSuccess) return e;
+  configured_dev = dev;
+  return cudaSuccess;
 }
 
 // max |x| over the tensor as the f32 bit pattern of a bf16 magnitude: 256-bit loads, four in flight per thread.
@@ -155,6 +318,16 @@ static tf_status launch_quantize(const char* fn, const void* x, int64_t m, int64
   const int64_t cols = k / block_of(FMT);
   if (layout == TF_SCALES_SWIZZLED && ((m & 127) || (cols & 3)))
     TF_CUDA(cudaMemsetAsync(scales, 0, (size_t)tf_scale_bytes(FMT, m, k, layout), stream));
+  if (use_ring(FMT, m, k)) {
+    int* status = device_status_words();
+    if (!status) return fail(TF_ERR_CUDA, "%s: cannot locate the device status words", fn);
+    TF_CUDA(ring_configure<FMT>());
+    const RingLaunch rl = ring_launch(FMT, m, k);
+    TF_CUDA(launch_dependent(ring_rows_kernel<FMT>, dim3(rl.grid), dim3(kRingThreads), rl.smem, stream, static_cast<const uint8_t*>(x), m, k, ldx,
+                             static_cast<uint8_t*>(codes), static_cast<uint8_t*>(scales), (int)(layout == TF_SCALES_SWIZZLED), gs, gs_out,
+                             (unsigned int*)nullptr, status, rl.stages));
+    return TF_OK;
+  }
   int tpr = 2;
   while (tpr < kQuantThreads && tpr * kQuantUnroll < (k >> 4)) tpr <<= 1;
   const int rpb = kQuantThreads / tpr;
@@ -223,6 +396,18 @@ tf_status tf_nvfp4_global_scale(const void* x, int64_t m, int64_t k, int64_t ldx
   TF_CHECK_ALIGNED(x, 32, "x");
   TF_CUDA(cudaMemsetAsync(out, 0, sizeof(float), stream));
   if (m > 0) {
+    if (use_ring(kModeAmax, m, k)) {
+      int* status = device_status_words();
+      if (!status) return fail(TF_ERR_CUDA, "%s: cannot locate the device status words", __func__);
+      TF_CUDA(ring_configure<kModeAmax>());
+      const RingLaunch rl = ring_launch(kModeAmax, m, k);
+      ring_rows_kernel<kModeAmax><<<rl.grid, kRingThreads, rl.smem, stream>>>(static_cast<const uint8_t*>(x), m, k, ldx, nullptr, nullptr, 0, nullptr, nullptr,
+                                                                              reinterpret_cast<unsigned int*>(out), status, rl.stages);
+      TF_LAUNCH_CHECK();
+      finalize_global_scale_kernel<<<1, 1, 0, stream>>>(out);
+      TF_LAUNCH_CHECK();
+      return TF_OK;
+    }
     const int64_t total = m * (k >> 4);
     const int64_t need = (total + 1023) / 1024, cap = (int64_t)sm_count() * 8;
     amax_bits_kernel<<<(unsigned)(need < cap ? need : cap), 256, 0, stream>>>(static_cast<const uint8_t*>(x), m, (int)(k >> 4), ldx,
