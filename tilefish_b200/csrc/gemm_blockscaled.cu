@@ -10,8 +10,9 @@
 //   warp 1   MMA issuer: copies the scale tiles shared -> tensor memory (tcgen05.cp) and issues
 //            tcgen05.mma.kind::{mxf8f6f4, mxf4, mxf4nvf4}.block_scale, 4 per stage (32 bytes of K each); tcgen05.commit frees
 //            the stage and, after the last one, hands the accumulator to the epilogue
-//   warps 2-5 epilogue: tcgen05.ld the accumulator (each warp its 32 lanes), scale, fused epilogue (none / SiLU gate /
-//            residual add), bf16 stores
+//   warps 2-5 and 7-10   epilogue, two groups of four warps: a warp reads its 32 lanes of the accumulator (tcgen05.ld), the groups
+//            share the columns (even / odd 32-column chunks); scale, fused epilogue (none / SiLU gate / residual add), bf16
+//            stores. With short K (10-20 stages per tile) one group of four could not drain a tile as fast as the MMAs fill one
 // The accumulator is double-buffered in tensor memory (overlapped for 256-column tiles, see TileCfg), so a tile's epilogue
 // runs while the next tile's MMAs are issued.
 // No TMA multicast, no clusters. Every mbarrier wait is bounded (about one second): on a timeout the kernel records
@@ -34,7 +35,7 @@ __device__ int g_device_status[2];  // [0] status, [1] detail
 constexpr int kBlockM = 128;
 constexpr int kStageKBytes = 128;  // bytes of K per row per stage: one 128-byte swizzle atom
 constexpr int kAStageBytes = kBlockM * kStageKBytes;
-constexpr int kGemmThreads = 224;  // 7 warps: operand loads, MMA issue, 4 epilogue warps, scale loads (one-CTA kernel)
+constexpr int kGemmThreads = 352;  // 11 warps: operand loads, MMA issue, epilogue group 0 (4), scale loads, epilogue group 1 (4)
 constexpr int kPairThreads = 192;  // the CTA-pair kernel keeps one load warp
 constexpr int kSmemLimit = 227 * 1024;
 constexpr unsigned long long kWaitLimitNs = 1000000000ull;
@@ -326,19 +327,33 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
   }
 }
 
+// Which epilogue warps read chunk `c` (32 accumulator columns): GRP < 0: this warp reads all of them (the CTA-pair kernel has four
+// epilogue warps); GRP 0 / 1: the one-CTA kernel's two groups of four warps share the columns, even chunks to group 0 and odd ones to
+// group 1 (with the SiLU gate: by the gate chunk; its up chunk goes with it).
+template <int GRP, int EPI, int BLOCK_N>
+__device__ __forceinline__ constexpr bool chunk_is_mine(int c) {
+  return GRP < 0 || (((EPI == TF_EPI_SILU_GATE) ? (c % (BLOCK_N / 64)) : c) & 1) == GRP;
+}
+
 // One tile's epilogue for accumulator BUF (compile time, so that the chunks held in registers are indexed statically).
 // t_acc: tensor-memory address of the accumulator for this warp's 32 lanes. Returns after the last store.
-template <int FMT, int BLOCK_N, int EPI, int BUF, bool CLUSTER_BAR = false>
+template <int FMT, int BLOCK_N, int EPI, int BUF, int GRP, bool CLUSTER_BAR = false>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_acc, uint32_t bar_release, int lane, int row, int col0, float alpha,
                                               uint32_t& amax2) {
   using Cfg = TileCfg<FMT, BLOCK_N>;
   constexpr int kOutCols = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 2 : BLOCK_N;
   constexpr int kOv = Cfg::kOverlapChunks;
   constexpr int kOvFirst = (BUF == 0) ? (BLOCK_N / 32 - kOv) : 0;  // first chunk (of this accumulator) the other accumulator also covers
-  uint32_t ov[kOv > 0 ? kOv : 1][32];
+  uint32_t ov[kOv > 0 ? kOv : 1][32];  // rows of chunks this warp does not read are never touched and cost no registers
+  bool any_ov = false;
 #pragma unroll
-  for (int i = 0; i < kOv; ++i) tc_ld32(t_acc + (kOvFirst + i) * 32, ov[i]);
-  if (kOv > 0) tc_wait_ld();
+  for (int i = 0; i < kOv; ++i) {
+    if (chunk_is_mine<GRP, EPI, BLOCK_N>(kOvFirst + i)) {
+      tc_ld32(t_acc + (kOvFirst + i) * 32, ov[i]);
+      any_ov = true;
+    }
+  }
+  if (any_ov) tc_wait_ld();
   // the columns shared with the other accumulator are in registers (or there are none): the next tile's MMAs may start
   tc_fence_before();
   __syncwarp();
@@ -349,9 +364,8 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ac
 
 #pragma unroll
   for (int c = 0; c < kOutCols / 32; ++c) {
+    if (!chunk_is_mine<GRP, EPI, BLOCK_N>(c)) continue;
     uint32_t v[32], packed[16];
-    constexpr int dummy = 0;
-    (void)dummy;
     const bool v_in_regs = kOv > 0 && c >= kOvFirst && c < kOvFirst + kOv;
     if (v_in_regs) {
 #pragma unroll
@@ -390,21 +404,28 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& p, uint32_t t_ac
 }
 
 // Split-K: dumps this (tile, split)'s raw f32 accumulator rows into the workspace [splits][M][acc columns].
-template <int FMT, int BLOCK_N, int BUF>
+template <int FMT, int BLOCK_N, int BUF, int GRP>
 __device__ __forceinline__ void epilogue_partial(const GemmParams& p, uint32_t t_acc, uint32_t bar_release, int lane, int row, int col0,
                                                  float* __restrict__ ws_row) {
   using Cfg = TileCfg<FMT, BLOCK_N>;
   constexpr int kOv = Cfg::kOverlapChunks;
   constexpr int kOvFirst = (BUF == 0) ? (BLOCK_N / 32 - kOv) : 0;
   uint32_t ov[kOv > 0 ? kOv : 1][32];
+  bool any_ov = false;
 #pragma unroll
-  for (int i = 0; i < kOv; ++i) tc_ld32(t_acc + (kOvFirst + i) * 32, ov[i]);
-  if (kOv > 0) tc_wait_ld();
+  for (int i = 0; i < kOv; ++i) {
+    if (chunk_is_mine<GRP, TF_EPI_NONE, BLOCK_N>(kOvFirst + i)) {
+      tc_ld32(t_acc + (kOvFirst + i) * 32, ov[i]);
+      any_ov = true;
+    }
+  }
+  if (any_ov) tc_wait_ld();
   tc_fence_before();
   __syncwarp();
   if (lane == 0) mbar_arrive(bar_release);
 #pragma unroll
   for (int c = 0; c < BLOCK_N / 32; ++c) {
+    if (!chunk_is_mine<GRP, TF_EPI_NONE, BLOCK_N>(c)) continue;
     uint32_t v[32];
     const bool in_regs = kOv > 0 && c >= kOvFirst && c < kOvFirst + kOv;
     if (in_regs) {
@@ -530,7 +551,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       mbar_init(bar_empty + 8 * s, 1);
     }
     mbar_init(bar_tmem_full, 1);
-    mbar_init(bar_tmem_empty, 4);
+    mbar_init(bar_tmem_empty, 8);  // every epilogue warp, once it holds its share of the columns both accumulators cover
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -694,8 +715,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       tile_phase ^= 1;
     }
   } else {
-    // ---------------- epilogue (warps 2..5; warp w reads lanes 32*(w%4) .. +31) ----------------
+    // ---------------- epilogue (warps 2..5 = group 0, warps 7..10 = group 1; warp w reads lanes 32*(w%4) .. +31) ----------------
     const int q = warp & 3;
+    const int grp = warp >= 7 ? 1 : 0;
     const float alpha = (FMT == TF_FMT_NVFP4) ? __fmul_rn(__ldg(p.a_gs), __ldg(p.b_gs)) : 1.0f;
     uint32_t tile_phase = 0, acc_buf = 0;
     uint32_t amax2 = 0;  // running max of |out| as two packed bf16 magnitudes
@@ -713,14 +735,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_blockscaled_kernel(const
       const float alpha_t = (FMT == TF_FMT_NVFP4 && p.a_gs_rows > 0) ? __fmul_rn(__ldg(p.a_gs + min(row, p.m - 1) / p.a_gs_rows), __ldg(p.b_gs)) : alpha;
       if (SPLITK) {
         float* ws_row = p.ws + ((int64_t)split * p.m + row) * p.n;
-        if (acc_buf == 0)
-          epilogue_partial<FMT, BLOCK_N, 0>(p, t_row, bar_tmem_empty, lane, row, col0, ws_row);
-        else
-          epilogue_partial<FMT, BLOCK_N, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, ws_row);
+        if (acc_buf == 0) {
+          if (grp == 0) epilogue_partial<FMT, BLOCK_N, 0, 0>(p, t_row, bar_tmem_empty, lane, row, col0, ws_row);
+          else epilogue_partial<FMT, BLOCK_N, 0, 1>(p, t_row, bar_tmem_empty, lane, row, col0, ws_row);
+        } else {
+          if (grp == 0) epilogue_partial<FMT, BLOCK_N, 1, 0>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, ws_row);
+          else epilogue_partial<FMT, BLOCK_N, 1, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, ws_row);
+        }
       } else if (acc_buf == 0) {
-        epilogue_tile<FMT, BLOCK_N, EPI, 0>(p, t_row, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
+        if (grp == 0) epilogue_tile<FMT, BLOCK_N, EPI, 0, 0>(p, t_row, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
+        else epilogue_tile<FMT, BLOCK_N, EPI, 0, 1>(p, t_row, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
       } else {
-        epilogue_tile<FMT, BLOCK_N, EPI, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
+        if (grp == 0) epilogue_tile<FMT, BLOCK_N, EPI, 1, 0>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
+        else epilogue_tile<FMT, BLOCK_N, EPI, 1, 1>(p, t_row + Cfg::kAccStride, bar_tmem_empty, lane, row, col0, alpha_t, amax2);
       }
       acc_buf ^= 1;
       tile_phase ^= 1;
@@ -952,9 +979,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_blockscaled_pair_kernel(
       const int col0 = n_blk * kOutCols;
       const float alpha_t = (FMT == TF_FMT_NVFP4 && p.a_gs_rows > 0) ? __fmul_rn(__ldg(p.a_gs + min(row, p.m - 1) / p.a_gs_rows), __ldg(p.b_gs)) : alpha;
       if (acc_buf == 0)
-        epilogue_tile<FMT, BLOCK_N, EPI, 0, true>(p, t_row, release, lane, row, col0, alpha_t, amax2);
+        epilogue_tile<FMT, BLOCK_N, EPI, 0, -1, true>(p, t_row, release, lane, row, col0, alpha_t, amax2);
       else
-        epilogue_tile<FMT, BLOCK_N, EPI, 1, true>(p, t_row + Cfg::kAccStride, release, lane, row, col0, alpha_t, amax2);
+        epilogue_tile<FMT, BLOCK_N, EPI, 1, -1, true>(p, t_row + Cfg::kAccStride, release, lane, row, col0, alpha_t, amax2);
       acc_buf ^= 1;
       tile_phase ^= 1;
     }
