@@ -33,6 +33,80 @@ def test_library_exports_every_declared_symbol():
     assert _native.version().startswith("tilefish_b200")
 
 
+def header_prototypes():
+    """{name: (return class, [argument classes])} of every TF_API declaration; classes: "ptr", "i32", "i64", "u64", "f32", "str"."""
+    text = open(os.path.join(ROOT, "include", "tilefish_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", " ", text, flags=re.S)
+
+    def cls(ctype: str) -> str:
+        t = " ".join(ctype.replace("const", " ").split())
+        if "*" in t:
+            return "str" if t.startswith("char") else "ptr"
+        base = t.split()[0] if t else "void"
+        return {"int32_t": "i32", "tf_status": "i32", "int64_t": "i64", "uint64_t": "u64", "float": "f32"}[base]
+
+    out = {}
+    for m in re.finditer(r"TF_API\s+([^;(]*?)\b(tf_[a-z0-9_]+)\s*\(([^)]*)\)\s*;", text, flags=re.S):
+        ret, name, params = m.group(1).strip(), m.group(2), m.group(3).strip()
+        args = []
+        if params and params != "void":
+            for prm in params.split(","):
+                prm = prm.strip()
+                ctype = prm.rsplit(None, 1)[0] if "*" not in prm else prm[: prm.rindex("*") + 1]
+                args.append(cls(ctype))
+        out[name] = (cls(ret), args)
+    return out
+
+
+def _ctypes_class(t) -> str:
+    import ctypes
+
+    if t is ctypes.c_char_p:
+        return "str"
+    if t is ctypes.c_void_p or (isinstance(t, type) and issubclass(t, ctypes._Pointer)):
+        return "ptr"
+    return {ctypes.c_int32: "i32", ctypes.c_int64: "i64", ctypes.c_uint64: "u64", ctypes.c_float: "f32"}[t]
+
+
+def test_ctypes_signatures_match_the_header_prototypes():
+    """Arity and C type of every argument of every entry point: include/tilefish_b200.h against tilefish_b200/_native.py."""
+    from tilefish_b200 import _native
+
+    protos = header_prototypes()
+    assert set(protos) == set(_native.SIGNATURES)
+    for name, (ret, args) in protos.items():
+        res, argtypes = _native.SIGNATURES[name]
+        assert _ctypes_class(res) == ret, name
+        assert [_ctypes_class(a) for a in argtypes] == args, (name, args)
+    assert len(protos["tf_gemm_blockscaled"][1]) == 21 and len(protos["tf_gemm_blockscaled_static"][1]) == 16
+
+
+def test_integration_snippet_matches_the_header_prototypes():
+    """The ctypes binding INTEGRATION.md shows a maintainer: every ``_lib.tf_*.argtypes`` line has the header's arity and types,
+    and every call of an entry point in the snippet passes that many arguments."""
+    protos = header_prototypes()
+    text = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    code = text[text.index("```python") + 9:text.index("```", text.index("```python") + 9)]
+    alias = {"P": "ptr", "I64": "i64", "I32": "i32", "F32": "f32", "U64": "u64"}
+    seen = 0
+    for m in re.finditer(r"_lib\.(tf_[a-z0-9_]+)\.argtypes = \[([^\]]*)\]", code):
+        name, items = m.group(1), [x.strip() for x in m.group(2).split(",") if x.strip()]
+        assert [alias[x] for x in items] == protos[name][1], name
+        seen += 1
+    assert seen >= 5
+    for m in re.finditer(r"_lib\.(tf_[a-z0-9_]+)\(", code):
+        name = m.group(1)
+        depth, i, commas = 1, m.end(), 0
+        while depth:
+            ch = code[i]
+            depth += ch in "(["
+            depth -= ch in ")]"
+            commas += ch == "," and depth == 1
+            i += 1
+        passed = 0 if not code[m.end():i - 1].strip() else commas + 1
+        assert passed == len(protos[name][1]), f"{name}: the snippet passes {passed} arguments, the header declares {len(protos[name][1])}"
+
+
 def test_host_only_queries():
     from tilefish_b200 import _native
 

@@ -136,3 +136,100 @@ def test_export_replay_and_capture(tmp_path):
     y = cap.replay()
     torch.cuda.synchronize()
     check_block(y, rg, x2, res2, w_n, w_gu, w_d, "mxfp8")
+
+
+def test_replay_trust_anchor_outputs_taps_bound_weights_and_single_steps(tmp_path):
+    """The rest of the reference's run-time API for a graph (python/src/tilefish/runtime.py:1275-1406): a replay needs a trust anchor,
+    ``outputs=`` receives the result, ``taps=`` copies a plan buffer out after a step, ``bind_weights`` binds the weights once,
+    ``prepare`` does the allocations ahead of a capture, ``run_step`` launches one step of the verified plan."""
+    from tilefish_b200 import TilefishManifestError, TilefishRuntimeError, runtime
+
+    _, _, block = declare(nvfp4)
+    exp = runtime.export(block, str(tmp_path / "mlp4"))
+    x, res, w_n, w_gu, w_d = inputs(32, seed=3)
+    q_gu, q_d = tilefish.quantize(w_gu.cuda(), "nvfp4"), tilefish.quantize(w_d.cuda(), "nvfp4")
+    args = lambda r: (x.cuda(), r, w_n.cuda(), q_gu, q_d)  # noqa: E731
+    with pytest.raises(TilefishManifestError, match="trust anchor"):
+        tilefish.run(block, *args(res.cuda()), mode="replay", plan=exp.directory)
+    with pytest.raises(TilefishManifestError, match="not both"):
+        tilefish.run(block, *args(res.cuda()), mode="replay", plan=exp.directory, pin=exp.digest, trust_directory=True)
+    with pytest.raises(TilefishRuntimeError, match="for mode='replay'"):
+        tilefish.run(block, *args(res.cuda()), pin=exp.digest)
+    res_a = res.cuda()
+    y_ref = tilefish.run(block, *args(res_a), mode="replay", plan=exp.directory, pin=exp.digest)
+    check_block(y_ref, res_a, x, res, w_n, w_gu, w_d, "nvfp4")
+
+    # outputs= and taps=: the result lands in the caller's tensor; the bf16 activation of the first GEMM is copied out after its step
+    doc = exp.plan.doc
+    steps = next(b for b in doc["buckets"] if b["values"] == {"M": 32})["steps"]
+    gemm1 = next(i for i, s in enumerate(steps) if s.get("entry", "").startswith("gemm_gu"))
+    a_name = next(a["binding"] for a in steps[gemm1]["args"] if a["name"] == "out")
+    out = torch.empty((32, 2560), dtype=torch.bfloat16, device="cuda")
+    tap = torch.zeros((32, 3072), dtype=torch.bfloat16, device="cuda")
+    res_b = res.cuda()
+    y = tilefish.run(block, *args(res_b), mode="replay", plan=exp.directory, trust_directory=True, outputs=[out], taps={a_name: tap})
+    assert y is out and torch.equal(out, y_ref) and torch.equal(res_b, res_a)
+    assert float(tap.float().abs().max()) > 0  # silu(g) * u of the block, as the plan computed it
+    r_ref, h_ref = O.residual_add_rmsnorm(x, res.clone(), w_n)
+    t_ref = O.gemm_bf16_a(h_ref, O.quantize(w_gu, "nvfp4"), "nvfp4")
+    a_ref = O.silu_gate(t_ref[:, :3072], t_ref[:, 3072:])
+    assert float((tap.cpu().float() - a_ref.float()).norm() / a_ref.float().norm()) <= 1e-2
+
+    # weights bound once; prepare() before a capture
+    runtime.prepare(block, mode="replay", plan=exp.directory, pin=exp.digest)
+    w = tilefish.bind_weights(block, {"w_n": w_n.cuda(), "w_gu": q_gu, "w_d": q_d}, mode="replay", plan=exp.directory, pin=exp.digest)
+    res_c = res.cuda()
+    assert torch.equal(w.run(x.cuda(), res_c), y_ref) and torch.equal(res_c, res_a)
+    xg, rg = x.cuda(), res.cuda()
+    cap = w.capture(xg, rg)
+    rg.copy_(res.cuda())
+    assert torch.equal(cap.replay(), y_ref)
+    torch.cuda.synchronize()
+    with pytest.raises(TilefishRuntimeError, match="not a weight"):
+        tilefish.bind_weights(block, {"x": x.cuda()})
+
+    # one step of the plan on the caller's tensors: the last GEMM, fed the quantized activation the tap of its input gives
+    last = len(steps) - 1
+    binds = {a["name"]: a["binding"] for a in steps[last]["args"]}
+    aq = tilefish.quantize(tap, "nvfp4")
+    out2 = torch.empty((32, 2560), dtype=torch.bfloat16, device="cuda")
+    tilefish.run_step(block, last, {binds["a"]: aq, "w_d": q_d, "out0": out2}, mode="replay", plan=exp.directory, pin=exp.digest, bucket={"M": 32})
+    torch.cuda.synchronize()
+    assert float((out2.float() - y_ref.float()).norm() / y_ref.float().norm()) <= 2e-2  # the plan derived a's global scale from the producer's amax: same value
+
+
+def test_config4_block_at_8192_rows_matches_the_oracle_on_sampled_rows():
+    """The fourth benchmark configuration's largest bucket (M = 8192, H = 2560, F = 3072, MXFP8), through the typed API: rows are independent
+    for the MX formats, so 96 sampled rows are compared with the oracle run on those rows alone."""
+    Mbig = Dim("M", buckets=[8192])
+
+    @tilefish.kernel
+    def residual_add_rmsnorm(x: Tensor[Mbig, H, bf16], residual: InOut[Tensor[Mbig, H, f32]], w: Tensor[H, bf16], *, eps: const[f32] = 1e-6) -> Tensor[Mbig, H, bf16]:
+        r = residual + x.to(f32)
+        residual[...] = r
+        rstd = tilefish.rsqrt(tilefish.mean(r * r, axis=-1, keepdims=True) + eps)
+        return (r * rstd * w.to(f32)).to(bf16)
+
+    @tilefish.library("gemm_gu", acc=f32)
+    def gemm_gu(a: Tensor[Mbig, H, bf16], b: Tensor[2 * F, H, mxfp8]) -> Tensor[Mbig, 2 * F, bf16]: ...
+
+    @tilefish.library("gemm_d", acc=f32)
+    def gemm_d(a: Tensor[Mbig, F, bf16], b: Tensor[H, F, mxfp8]) -> Tensor[Mbig, H, bf16]: ...
+
+    @tilefish.graph(inputs=("x",), weights=("w_n", "w_gu", "w_d"))
+    def block(x: Tensor[Mbig, H, bf16], residual: InOut[Tensor[Mbig, H, f32]], w_n: Tensor[H, bf16], w_gu: Tensor[2 * F, H, mxfp8], w_d: Tensor[H, F, mxfp8]):
+        h = residual_add_rmsnorm(x, residual, w_n)
+        g, u = gemm_gu(h, w_gu).split(F, axis=-1)
+        return gemm_d((tilefish.silu(g.to(f32)) * u.to(f32)).to(bf16), w_d)
+
+    x, res, w_n, w_gu, w_d = inputs(8192, seed=21)
+    q_gu, q_d = tilefish.quantize(w_gu.cuda(), "mxfp8"), tilefish.quantize(w_d.cuda(), "mxfp8")
+    res_gpu = res.cuda()
+    y = tilefish.run(block, x.cuda(), res_gpu, w_n.cuda(), q_gu, q_d)
+    rows = torch.randint(0, 8192, (96,), generator=torch.Generator().manual_seed(2))
+    rows[:3] = torch.tensor([0, 127, 8191])
+    r_ref, y_ref = O.decoder_block(x[rows], res[rows].clone(), w_n, O.quantize(w_gu, "mxfp8"), O.quantize(w_d, "mxfp8"), "mxfp8")
+    assert torch.equal(res_gpu[rows.cuda()].cpu(), r_ref)
+    g, r = y[rows.cuda()].cpu().float(), y_ref.float()
+    assert float((g - r).abs().max()) <= 2.0**-6 * float(r.abs().max())
+    assert float((g - r).norm() / r.norm()) <= 1e-2

@@ -6,6 +6,7 @@ README kernel and graph, rounding points, and the refusals of the call checker.
 """
 
 import json
+import os
 
 import pytest
 
@@ -170,33 +171,114 @@ def block_graph(fmt):
     return block
 
 
+def _steps(doc, m):
+    return next(b for b in doc["buckets"] if b["values"] == {"M": m})["steps"]
+
+
+def _args(step):
+    return {a["name"]: a["binding"] for a in step["args"]}
+
+
 def test_plan_of_the_decoder_block():
     from tilefish_b200 import _plan
 
     block = block_graph(mxfp8)
     p = tilefish.plan(block)
     doc = p.doc
-    assert doc["schema"] == "tilefish.plan.v1" and doc["arena_alignment"] == 256 and sorted(doc["buckets"]) == ["M=1", "M=32", "M=512"]
+    # the reference's plan schema 1: exactly these top-level keys (docs/en/plan-schema-1.md, section 2)
+    assert set(doc) == set(_plan.TOP_KEYS) | {"roles"} and doc["roles"] == "declared"
+    assert doc["schema"] == "tilefish.plan.v1" and doc["arena_alignment"] == 256 and doc["dims"] == {"M": [1, 32, 512]} and doc["outputs"] == ["out0"]
+    assert doc["arch"] is None and doc["manifest_digest"] is None  # a plan that was only made; an exported one names sm_100 and its manifest
+    assert [b["values"] for b in doc["buckets"]] == [{"M": 1}, {"M": 32}, {"M": 512}]
     # three launches: both activation quantizations are done by the kernels that produce the activations
-    assert [s["entry"] for s in doc["steps"]] == ["rms", "gemm_gu", "gemm_d"]
-    assert [s["kind"] for s in doc["steps"]] == ["kernel", "library", "library"]
-    assert doc["steps"][1]["attrs"] == {"format": "mxfp8", "epilogue": "silu_gate", "impl": "sm100.gemm_blockscaled", "q_format": "mxfp8"}
-    assert doc["steps"][0]["attrs"]["q_format"] == "mxfp8" and "out" not in doc["steps"][0]["args"]  # rmsnorm emits the quantized copy only
-    assert "out" not in doc["steps"][1]["args"] and doc["steps"][2]["args"]["a"] == doc["steps"][1]["args"]["q"]  # `a` never exists in bf16
-    roles = {b["name"]: b["role"] for b in doc["buffers"]}
-    assert roles["x"] == "input" and roles["residual"] == "inout" and roles["w_gu"] == "weight" and roles["out0"] == "output"
-    b32 = doc["buckets"]["M=32"]
-    for name, entry in b32["buffers"].items():
-        for off in entry.get("offset", {}).values():
-            assert off % 256 == 0
-    act = next(n for n, r in roles.items() if r == "intermediate" and b32["buffers"][n]["bytes"].get("codes") == 32 * 2560)
-    assert b32["buffers"][act]["bytes"]["scales"] == 512 * 20  # one row tile x 20 column tiles of swizzled ue8m0 bytes
+    steps = _steps(doc, 32)
+    assert [s["entry"] for s in steps] == ["rms_qmxfp8", "gemm_gu_silu_gate_qmxfp8.M32", "gemm_d.M32"]
+    assert [s["kind"] for s in steps] == ["kernel", "library", "library"]
+    assert set(steps[0]) == {"entry", "kind", "args"} and set(steps[1]) == {"entry", "kind", "args", "workspace"}
+    lib = p.manifest["library"]["gemm_gu_silu_gate_qmxfp8.M32"]
+    assert lib["attrs"] == {"format": "mxfp8", "epilogue": "silu_gate", "q_format": "mxfp8"} and lib["impl"] == "sm100.gemm_blockscaled"
+    assert lib["symbol"] == "tf_gemm_blockscaled" and (lib["m"], lib["n"], lib["k"]) == (32, 3072, 2560)
+    a0, a1, a2 = _args(steps[0]), _args(steps[1]), _args(steps[2])
+    assert "out" not in a0 and "out" not in a1  # rmsnorm and the first gemm emit the quantized copies only: `a` never exists in bf16
+    assert a1["a"] == a0["q"] and a1["a_scales"] == a0["q_scales"] and a2["a"] == a1["q"] and a2["a_scales"] == a1["q_scales"]
+    # a BlockScaled tensor is separate bindings: codes, swizzled scale bytes (and the global scale for nvfp4)
+    assert a1["b"] == "w_gu" and a1["b_scales"] == "w_gu__scales" and [a["name"] for a in steps[1]["args"]] == lib["params"]
+    bufs = {b["name"]: b for b in doc["buffers"]}
+    assert [b["name"] for b in doc["buffers"]][:7] == ["x", "residual", "w_n", "w_gu", "w_gu__scales", "w_d", "w_d__scales"]
+    assert bufs["x"]["role"] == "input" and bufs["residual"]["role"] == "inout" and bufs["w_gu"]["role"] == "weight" and bufs["out0"]["role"] == "output"
+    assert bufs["w_gu"]["dtype"] == "e4m3" and bufs["w_gu"]["shape"] == [6144, 2560] and bufs["x"]["shape"] == ["M", 2560]
+    for b in doc["buffers"]:
+        assert set(b) == {"name", "role", "dtype", "shape", "offset", "bytes"}
+        assert (b["offset"] is None) == (b["role"] not in ("intermediate", "workspace"))
+        assert b["offset"] is None or (b["offset"] % 256 == 0 and b["offset"] + b["bytes"] <= doc["arena_bytes"])
+    act = bufs[a0["q"]]
+    assert act["role"] == "intermediate" and act["dtype"] == "e4m3" and act["bytes"] == 512 * 2560
+    assert bufs[a0["q_scales"]]["bytes"] == 4 * 20 * 512  # four row tiles x 20 column tiles of swizzled ue8m0 bytes at the largest bucket
+    assert bufs["workspace"]["role"] == "workspace" and bufs["workspace"]["bytes"] >= max(e["workspace_bytes"] for e in p.manifest["library"].values())
     assert p.digest == tilefish.plan(block).digest and len(p.digest) == 64
-    assert p.digest == _plan.digest("tilefish.plan-digest.v1", {k: v for k, v in doc.items() if k != "plan_digest"})
-    # nvfp4: amax is reduced by the producers and consumed by the quantizers; an aux buffer carries it
-    steps = tilefish.plan(block_graph(nvfp4)).doc["steps"]
-    assert [s["entry"] for s in steps] == ["rms", "quantize.nvfp4", "gemm_gu", "quantize.nvfp4", "gemm_d"]
-    assert steps[0]["args"]["amax"] == steps[1]["args"]["amax"] == "aux[0]" and steps[2]["args"]["amax"] == steps[3]["args"]["amax"] == "aux[1]"
+    assert p.digest == _plan.digest("tilefish.plan-digest.v1", {k: v for k, v in doc.items() if k not in ("plan_digest", "tilefish")})
+    # nvfp4: amax is reduced by the producers and consumed by the quantizers; an aux buffer carries it and a memset step zeroes it
+    doc4 = tilefish.plan(block_graph(nvfp4)).doc
+    steps = _steps(doc4, 32)
+    assert [s.get("entry", s["kind"]) for s in steps] == ["memset", "rms_amax", "quantize_nvfp4_amax", "gemm_gu_silu_gate_amax.M32", "quantize_nvfp4_amax", "gemm_d.M32"]
+    assert steps[0] == {"kind": "memset", "args": [{"name": "dst", "binding": "aux"}]}
+    amax = [next(a for a in s["args"] if a["name"] == "amax") for s in steps[1:5]]
+    assert [a["view"]["offset"] for a in amax] == [0, 0, 1, 1] and all(a["binding"] == "aux" and a["view"]["shape"] == [1] for a in amax)
+    assert {"name": "b_global", "binding": "w_gu__global"} in steps[3]["args"]
+
+
+def test_reference_validator_accepts_the_plan_and_the_ir_text_is_the_references():
+    """With the reference checked out next to this repository: its own ``validate_doc`` reads the documents this package writes, its
+    digest function agrees, and the graph prints byte for byte as the reference prints it. Skipped elsewhere."""
+    import sys
+
+    src = "/root/reference/python/src"
+    if not os.path.isdir(src):
+        pytest.skip("the reference checkout is not on this machine")
+    from tilefish_b200 import _plan
+
+    sys.path.insert(0, src)
+    try:
+        import tilefish as ref
+        import tilefish._plan as ref_plan
+    finally:
+        sys.path.remove(src)
+    for fmt in (mxfp8, tilefish.mxfp4, nvfp4):
+        for fuse in (True, False):
+            p = _plan.make_plan(block_graph(fmt), library={"file": "libtilefish_b200.so", "sha256": "0" * 64, "version": "test"}, fuse=fuse)
+            ref_plan.validate_doc(p.doc)
+            assert ref_plan.plan_digest(p.doc) == p.digest
+    ref_plan.validate_doc(tilefish.plan(block_graph(mxfp8)).doc, made=True)
+
+    def declare(t, fmt):
+        Mb, Hb, Fb = t.Dim("M", buckets=[1, 32, 512]), t.Dim("H", 2560), t.Dim("F", 3072)
+
+        @t.kernel
+        def residual_add_rmsnorm(x: t.Tensor[Mb, Hb, t.bf16], residual: t.InOut[t.Tensor[Mb, Hb, t.f32]], w: t.Tensor[Hb, t.bf16], *, eps: t.const[t.f32] = 1e-6) -> t.Tensor[Mb, Hb, t.bf16]:
+            r = residual + x.to(t.f32)
+            residual[...] = r
+            rstd = t.rsqrt(t.mean(r * r, axis=-1, keepdims=True) + eps)
+            return (r * rstd * w.to(t.f32)).to(t.bf16)
+
+        @t.library("gemm_gu", acc=t.f32)
+        def gemm_gu(a: t.Tensor[Mb, Hb, t.bf16], b: t.Tensor[2 * Fb, Hb, fmt]) -> t.Tensor[Mb, 2 * Fb, t.bf16]: ...
+
+        @t.library("gemm_d", acc=t.f32)
+        def gemm_d(a: t.Tensor[Mb, Fb, t.bf16], b: t.Tensor[Hb, Fb, fmt]) -> t.Tensor[Mb, Hb, t.bf16]: ...
+
+        @t.graph(inputs=("x",), weights=("w_n", "w_gu", "w_d"))
+        def block(x: t.Tensor[Mb, Hb, t.bf16], residual: t.InOut[t.Tensor[Mb, Hb, t.f32]], w_n: t.Tensor[Hb, t.bf16], w_gu: t.Tensor[2 * Fb, Hb, fmt],
+                  w_d: t.Tensor[Hb, Fb, fmt]):
+            h = residual_add_rmsnorm(x, residual, w_n)
+            g, u = gemm_gu(h, w_gu).split(Fb, axis=-1)
+            return gemm_d((t.silu(g.to(t.f32)) * u.to(t.f32)).to(t.bf16), w_d)
+
+        return str(residual_add_rmsnorm.graph), str(block.graph)
+
+    theirs = declare(ref, ref.BlockScaled(ref.e4m3, ref.ue8m0, 32))
+    ours = declare(tilefish, tilefish.BlockScaled(tilefish.e4m3, tilefish.ue8m0, 32))
+    assert ours == theirs
+    assert "{kind=kernel, consts={eps: 1e-06}, inout=(residual,)}" in ours[1] and ours[1].endswith("final residual = %1")
 
 
 def test_plan_refusals_and_unfused_form():
@@ -206,6 +288,11 @@ def test_plan_refusals_and_unfused_form():
     assert [s.impl for s in steps] == ["tf_residual_add_rmsnorm", "tf_quantize_mxfp8", "tf_gemm_blockscaled", "tf_silu_gate", "tf_quantize_mxfp8",
                                        "tf_gemm_blockscaled"]
     assert steps[3].args["gate"].endswith("[:, 0]") and steps[3].args["up"].endswith("[:, 1]")
+    # in the document the column halves are views of one buffer (docs/en/plan-schema-1.md, section 7.1)
+    doc = _plan.make_plan(block_graph(mxfp8), fuse=False).doc
+    silu = _steps(doc, 32)[3]
+    assert silu["entry"] == "silu_gate" and silu["args"][0]["view"] == {"shape": [32, 3072], "strides": [6144, 1], "offset": 0}
+    assert silu["args"][1]["view"] == {"shape": [32, 3072], "strides": [6144, 1], "offset": 3072} and silu["args"][0]["binding"] == silu["args"][1]["binding"]
 
     with pytest.raises(TilefishPlanError, match="no buckets"):
         tilefish.plan(mlp.__class__(mlp.fn, "m2", mlp.signature, _free_graph().graph, {}))
@@ -237,53 +324,159 @@ def _free_graph():
     return free
 
 
+def test_planner_split_rule_matches_the_kernel_library():
+    """The planner sizes the workspace from its own restatement of the library's split-K rule for 148 SMs; where the library is built
+    (its host-side query needs no GPU and assumes 148 SMs without one) the two must agree."""
+    from tilefish_b200 import _native, _plan
+
+    if not os.path.exists(_native.LIB_PATH):
+        pytest.skip("library not built here")
+    lib = _native.load()
+    for fmt, fid in (("mxfp8", 0), ("mxfp4", 1), ("nvfp4", 2)):
+        for epi, eid in (("none", 0), ("silu_gate", 1), ("residual", 2)):
+            for (m, n, k) in [(1, 6144, 2560), (16, 3072, 2560), (32, 2560, 3072), (64, 28672, 8192), (128, 8192, 28672), (200, 512, 768), (256, 128, 4096),
+                              (257, 6144, 2560), (4096, 6144, 2560)]:
+                assert _plan.gemm_workspace_bytes(m, n, k, fmt, epi) == lib.tf_gemm_workspace_bytes(m, n, k, fid, eid), (fmt, epi, m, n, k)
+
+
 def test_export_files_round_trip_and_tamper_detection(tmp_path):
     from tilefish_b200 import _plan
 
     block = block_graph(mxfp8)
-    p, manifest = _plan.make_plan(block, library={"file": "libtilefish_b200.so", "sha256": "0" * 64, "version": "test"})
+    p = _plan.make_plan(block, library={"file": "libtilefish_b200.so", "sha256": "0" * 64, "version": "test"})
+    assert p.doc["arch"] == "sm_100" and p.doc["manifest_digest"] == p.manifest["manifest_digest"]
     d = str(tmp_path / "export")
-    _plan.write_export(d, p, manifest)
+    _plan.write_export(d, p)
     doc, man = _plan.load_export(d, pin=p.digest)
-    assert doc == p.doc and man == manifest
-    with pytest.raises(TilefishManifestError, match="pins"):
+    assert doc == p.doc and man == p.manifest
+    with pytest.raises(TilefishManifestError, match="but the pin is"):
         _plan.load_export(d, pin="f" * 64)
     with pytest.raises(TilefishManifestError, match="already holds"):
-        _plan.write_export(d, p, manifest)
+        _plan.write_export(d, p)
+    with pytest.raises(TilefishManifestError, match="trust anchor"):
+        _plan.check_anchor(None, False)
+    with pytest.raises(TilefishManifestError, match="not both"):
+        _plan.check_anchor(p.digest, True)
     path = tmp_path / "export" / "plan.json"
-    tampered = json.loads(path.read_text())
-    tampered["steps"][1]["attrs"]["epilogue"] = "none"
+    good = path.read_text()
+    tampered = json.loads(good)
+    tampered["buckets"][1]["steps"][1]["entry"] = "gemm_d.M32"
     path.write_text(json.dumps(tampered))
-    with pytest.raises(TilefishManifestError, match="does not match its own digest"):
-        _plan.load_export(d)
+    with pytest.raises(TilefishManifestError, match="was edited"):
+        _plan.load_export(d, trust_directory=True)
+    # an edit that also rewrites the digest is caught by the pin, and by the manifest's entries when only the directory is trusted
+    tampered["plan_digest"] = _plan.plan_digest(tampered)
+    path.write_text(json.dumps(tampered))
+    with pytest.raises(TilefishManifestError, match="but the pin is"):
+        _plan.load_export(d, pin=p.digest)
+    with pytest.raises(TilefishManifestError, match="the entry takes"):
+        _plan.load_export(d, trust_directory=True)
     path.write_text("{not json")
     with pytest.raises(TilefishManifestError, match="not valid JSON"):
-        _plan.load_export(d)
+        _plan.load_export(d, trust_directory=True)
+    path.write_text(good.replace('"arena_alignment": 256', '"arena_alignment": 256, "arena_alignment": 256'))
+    with pytest.raises(TilefishManifestError, match="duplicate key"):
+        _plan.load_export(d, trust_directory=True)
 
 
-def test_runner_checks_everything_before_the_first_launch():
-    """A recording backend in place of the CUDA one: nothing is launched when a precondition fails (the pattern of the
-    reference's FakeBackend, python/tests/test_planrun.py:49)."""
-    from tilefish_b200 import runtime
+class _FakeTensor:
+    """What the runner needs of a tensor: an address."""
+
+    def __init__(self, address):
+        self.address = address
+
+    def data_ptr(self):
+        return self.address
+
+
+def test_runner_drives_the_backend_through_the_reference_signatures():
+    """A recording backend in place of the CUDA one (the pattern of the reference's FakeBackend, python/tests/test_planrun.py:49): the
+    order of the launches, the raw addresses (arena + offset, + view.offset * itemsize) and the derived scalars, without a GPU; and
+    nothing is allocated or launched when a precondition fails."""
+    from tilefish_b200 import _plan, runtime
     from tilefish_b200.errors import TilefishPreconditionError
+    from tilefish_b200.kernels import BlockScaledTensor
 
     class Recording(runtime.Backend):
+        ARENA = 0x7F00_0000_0000
+
         def __init__(self):
             self.calls = []
+            self.arenas = 0
 
-        def alloc_arena(self, nbytes, device):
-            raise AssertionError("nothing may be allocated for a refused call")
+        def device_index(self, device):
+            return 0
 
-        def launch(self, step, tensors):
-            self.calls.append(step["entry"])
+        def current_device(self):
+            return 0
 
-        def gemm(self, step, tensors):
-            self.calls.append(step["entry"])
+        def capturing(self, index):
+            return False
 
-    rec = Recording()
-    runner = runtime.PlanRunner(tilefish.plan(block_graph(mxfp8)).doc, backend=rec)
-    with pytest.raises(TilefishPreconditionError) as e:
-        runner.run("M=7", {}, device=None)
-    assert e.value.kind == "bucket" and rec.calls == []
+        def stream(self, index):
+            return 77
+
+        def alloc_arena(self, nbytes, index):
+            self.arenas += 1
+            return object(), self.ARENA
+
+        def empty(self, shape, dtype, index):
+            return _FakeTensor(0x5000_0000)
+
+        def load(self, built, index):
+            return built
+
+        def launch(self, loaded, grid, args, stream, scratch=None):
+            self.calls.append(("launch", loaded.symbol, tuple(grid), list(args), stream))
+
+        def memset(self, dst, nbytes, stream):
+            self.calls.append(("memset", dst, nbytes, stream))
+
+        def gemm(self, spec, algo, a, b, bias, out, workspace, stream, index, c=None, *, scaled=None):
+            self.calls.append(("gemm", spec, a, b, bias, out, workspace, stream, index, c, scaled))
+
+    def bs(fmt, shape, base):
+        t = BlockScaledTensor(fmt, shape, _FakeTensor(base), _FakeTensor(base + 0x100_0000), _FakeTensor(base + 0x200_0000) if fmt == "nvfp4" else None)
+        return t
+
+    for fmt, name in ((mxfp8, "mxfp8"), (nvfp4, "nvfp4")):
+        p = _plan.make_plan(block_graph(fmt), exported=False)
+        rec = Recording()
+        runner = runtime.PlanRunner(p.doc, p.manifest, backend=rec)
+        with pytest.raises(TilefishPreconditionError) as e:
+            runner.run({"M": 7}, {}, device=None)
+        assert e.value.kind == "bucket" and rec.calls == [] and rec.arenas == 0
+        tensors = {"x": _FakeTensor(0x1000_0000), "residual": _FakeTensor(0x2000_0000), "w_n": _FakeTensor(0x3000_0000),
+                   "w_gu": bs(name, (6144, 2560), 0x4000_0000), "w_d": bs(name, (2560, 3072), 0x4800_0000)}
+        # a misaligned pointer is a refusal before anything is enqueued
+        bad = dict(tensors, x=_FakeTensor(0x1000_0004))
+        with pytest.raises(TilefishPreconditionError) as e:
+            runner.run({"M": 32}, bad, device=None)
+        assert e.value.kind == "pointer_alignment" and rec.calls == []
+        out = runner.run({"M": 32}, tensors, device=None)
+        assert out.data_ptr() == 0x5000_0000 and rec.arenas == 1
+        bufs = {b["name"]: b for b in p.doc["buffers"]}
+        kinds = [c[0] if c[0] != "launch" else c[1] for c in rec.calls]
+        if name == "mxfp8":
+            assert kinds == ["tf_residual_add_rmsnorm", "gemm", "gemm"]
+            rms = rec.calls[0]
+            q, qs = (bufs[n]["offset"] + Recording.ARENA for n in ("t0", "t0__scales"))
+            assert rms[2] == () and rms[4] == 77
+            assert rms[3] == [("ptr", 0x1000_0000), ("ptr", 0x2000_0000), ("ptr", 0x3000_0000), ("ptr", None), ("i64", 32), ("i64", 2560), ("f32", 1e-6), ("i32", 0),
+                              ("ptr", q), ("ptr", qs), ("i32", 1), ("ptr", None), ("ptr", None)]
+            g1 = rec.calls[1]
+            spec = g1[1]
+            assert (spec.m, spec.n, spec.k, spec.format, spec.epilogue) == (32, 3072, 2560, "mxfp8", "silu_gate") and spec.workspace_bytes == bufs["workspace"]["bytes"]
+            assert g1[2] == q and g1[3] == 0x4000_0000 and g1[4] is None and g1[5] is None and g1[6] == Recording.ARENA + bufs["workspace"]["offset"] and g1[7] == 77
+            assert g1[10].a_scales == qs and g1[10].b_scales == 0x4100_0000 and g1[10].q_codes == Recording.ARENA + bufs["t1"]["offset"]
+            g2 = rec.calls[2]
+            assert g2[2] == g1[10].q_codes and g2[5] == 0x5000_0000 and g2[1].ldo == 2560
+        else:
+            assert kinds == ["memset", "tf_residual_add_rmsnorm", "tf_quantize_nvfp4_from_amax", "gemm", "tf_quantize_nvfp4_from_amax", "gemm"]
+            aux = Recording.ARENA + bufs["aux"]["offset"]
+            assert rec.calls[0] == ("memset", aux, 32, 77)
+            assert rec.calls[1][3][-1] == ("ptr", aux) and rec.calls[2][3][-2] == ("ptr", aux)          # amax slot 0: produced, then consumed
+            assert rec.calls[3][10].amax == aux + 4 and rec.calls[4][3][-2] == ("ptr", aux + 4)         # slot 1: view offset 1 x 4 bytes
+            assert rec.calls[3][10].b_global == 0x4200_0000 and rec.calls[3][10].a_global == rec.calls[2][3][-1][1]
     with pytest.raises(tilefish.TilefishRuntimeError, match="not part of this backend"):
         runtime.run(block_graph(mxfp8), mode="reference")

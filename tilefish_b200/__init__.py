@@ -30,11 +30,11 @@ mxfp8 = BlockScaled(elem=e4m3, scale=ue8m0, block=32, axis=-1)
 mxfp4 = BlockScaled(elem=e2m1, scale=ue8m0, block=32, axis=-1)
 nvfp4 = BlockScaled(elem=e2m1, scale=e4m3, block=16, global_scale=f32)
 
-__version__ = "0.1.0"
+__version__ = "0.2.0"
 
 
 def __getattr__(name):  # the run-time half imports torch lazily
-    if name in ("run", "plan", "capture", "runtime", "quantize", "BlockScaledTensor"):
+    if name in ("run", "plan", "capture", "runtime", "quantize", "BlockScaledTensor", "bind_weights", "prepare", "run_step"):
         import importlib
 
         rt = importlib.import_module(".runtime", __name__)

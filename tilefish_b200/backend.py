@@ -226,6 +226,11 @@ def compile_graph(op: GraphOp, fuse: bool = True) -> Tuple[List[Buffer], List[St
             steps.append(st)
             name_of[n.outputs[0]] = args["out"]
             producer_step[n.outputs[0]] = st
+            # the versions of the InOut tensors the call leaves behind live where the tensors do
+            inout_names = n.attrs.get("inout", ())
+            for new, pname in zip(n.outputs[len(n.outputs) - len(inout_names):], inout_names):
+                src = next(v for p, v in zip(params, n.inputs) if p.name == pname)
+                name_of[new] = name_of[src]
         elif isinstance(callee, LibraryOp):
             a, b = n.inputs
             if not isinstance(b.type.dtype, BlockScaled):

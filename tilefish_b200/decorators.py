@@ -194,12 +194,32 @@ class Op:
         if ctx.kind != "graph":
             raise TilefishTypeError(f"{self.name}: operators can only be called from a @graph body, not from the kernel '{ctx.name}'")
         values, _, rets = check_call(self, args, kwargs)
+        values = [ctx.latest(v) for v in values]  # a tensor an earlier in-place call updated is read at its current version
         attrs = self._call_attrs()
-        outs = ctx.emit(self.name, values, rets, attrs)
+        # the call node as the reference prints it (python/src/tilefish/ir.py:133-206): after the declared results one output per InOut
+        # parameter (the version of the tensor the call leaves behind), the compiled-in consts, the names of the InOut parameters
+        updated = [(p, v) for p, v in zip(self.signature.tensors, values) if p.access == "inout"]
+        consts = {c.name: c.default for c in self.signature.consts}
+        if consts:
+            attrs["consts"] = consts
+        if updated:
+            attrs["inout"] = tuple(p.name for p, _ in updated)
+        outs = ctx.emit(self.name, values, tuple(rets) + tuple(v.type for _, v in updated), attrs)
         ctx.nodes[-1].callee = self
-        for p, v in zip(self.signature.tensors, values):
-            if p.access == "inout":
-                v.consumed = False  # the updated tensor is read back through the same name by later calls of the graph
+        for (p, v), new in zip(updated, outs[len(rets):]):
+            v.consumed = False  # the updated tensor is read back through the same name by later calls of the graph
+            ctx.versions[v] = new
+            root = v
+            while root.producer is not None and root.producer.callee is not None and root in root.producer.outputs:
+                k = root.producer.outputs.index(root) - (len(root.producer.outputs) - len(root.producer.attrs.get("inout", ())))
+                if k < 0:
+                    break
+                names = root.producer.attrs["inout"]
+                src = [x for q, x in zip(root.producer.callee.signature.tensors, root.producer.inputs) if q.name == names[k]]
+                root = src[0]
+            if root.is_param and root.access == "inout":
+                ctx.finals[root.name] = new
+        outs = outs[:len(rets)]
         if not outs:
             return None
         return outs[0] if len(outs) == 1 else outs

@@ -51,8 +51,10 @@ class Value:
 def _fmt_attr(v: Any) -> str:
     if isinstance(v, bool):
         return "true" if v else "false"
-    if isinstance(v, tuple):
+    if isinstance(v, (tuple, list)):
         return "(" + ", ".join(_fmt_attr(x) for x in v) + ("," if len(v) == 1 else "") + ")"
+    if isinstance(v, dict):
+        return "{" + ", ".join(f"{k}: {_fmt_attr(x)}" for k, x in v.items()) + "}"
     return str(v)
 
 

@@ -31,6 +31,13 @@ class TraceContext:
         self.counter = 0
         self.finals: Dict[str, Value] = {}
         self.consts: Dict[str, Scalar] = {}
+        self.versions: Dict[Value, Value] = {}  # a value an in-place call updated -> the version the call produced
+
+    def latest(self, v: Value) -> Value:
+        """The current version of ``v``: what a later read of a tensor that an in-place call updated refers to."""
+        while v in self.versions:
+            v = self.versions[v]
+        return v
 
     def __enter__(self):
         _ACTIVE.append(self)
