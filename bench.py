@@ -6,16 +6,23 @@
 One step = one forward pass of the tensor-parallel MLP stack of the last benchmark configuration: 32 decoder blocks shaped
 like Llama-3-70B's MLP (H = 8192, F = 28672, SiLU-gated), NVFP4 weights quantized from seeded N(0, 1/sqrt(fan_in)) bf16,
 M = 4096 tokens of x ~ N(0, 1): residual_add_rmsnorm -> quantize -> gemm (+ SiLU-gate epilogue) -> quantize -> gemm ->
-(N > 1: one bf16 NCCL all-reduce) per block. ``value`` is tokens/s with x resident in HBM; ``e2e`` is the same step through the
-public API with x in pinned host memory and the result copied back, both copies inside the timed region. The total work is
-fixed as N grows (``scaling: strong``). At N = 1 the line also carries the two single-kernel headline metrics: quantize GB/s
-(M = 65536, K = 4096, every format) and block-scaled GEMM TFLOP/s (M = 4096, N = 6144, K = 2560, MXFP8 and NVFP4).
+(N > 1: one exchange of the partial results) per block. ``value`` is tokens/s with x resident in HBM; ``e2e`` is the same step
+through the public API with x in pinned host memory and the result copied back, both copies inside the timed region. The total
+work is fixed as N grows (``scaling: strong``).
+
+Beside the headline the line carries, at every N: ``parity`` (the first 128 x N rows of the step's real input through two blocks
+of the real weights, on the GPUs and with the CPU oracle of the same tensor-parallel computation), ``decode`` (the same stack at
+M = 64) and, at N > 1, ``row_sharded_quantize``; at N = 1 also the single-kernel metrics: quantize GB/s (M = 65536, K = 4096,
+every format, and the smaller sweep points), block-scaled GEMM TFLOP/s (M = 4096, N = 6144, K = 2560, MXFP8 and NVFP4) against the
+FP8 / FP4 peak measured in the same run with the library's block-scaled GEMM (torch._scaled_mm: the denominator only), the README
+decoder block through the typed API, and the CPU baseline.
 
 ``--impl reference`` times the CPU restatement of the same block (oracle/blockscaled.py, torch on all host threads) on a
 bounded sample of the workload; the reference project itself cannot run this path (it only types BlockScaled tensors).
 """
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -27,8 +34,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-H, F, LAYERS, M_TOKENS, FMT = 8192, 28672, 32, 4096, "nvfp4"
+H, F, LAYERS, M_TOKENS, M_DECODE, FMT = 8192, 28672, 32, 4096, 64, "nvfp4"
 WORKLOAD = f"tp_mlp_stack: {LAYERS} layers H={H} F={F} {FMT} weights, M={M_TOKENS} (prefill)"
+BYTES_PER_ELEM = {"mxfp8": 2 + 1 + 1 / 32, "mxfp4": 2 + 0.5 + 1 / 32, "nvfp4": 2 + 0.5 + 1 / 16}
 
 
 def parse_args():
@@ -37,24 +45,21 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=8)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=LAYERS, help="development only: fewer layers (the line then says so)")
-    ap.add_argument("--tokens", type=int, default=M_TOKENS, help="development only")
-    ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel quantize / GEMM measurements")
-    ap.add_argument("--kernel", default=None, choices=["gemm1", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode", "exchange"],
-                    help="profiling aid: launch only this kernel three times on a reduced case (what the ncu summaries under profiles/ capture) and exit")
+    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers than the benchmark's 32 (the line then says REDUCED)")
+    ap.add_argument("--no-extras", action="store_true", help="skip the single-kernel, decode and typed-API measurements")
+    ap.add_argument("--no-parity", action="store_true", help="skip the oracle comparison after the timed region")
+    ap.add_argument("--kernel", default=None, choices=["gemm1", "gemm-config3", "quantize-mxfp8", "quantize-mxfp4", "quantize-nvfp4", "rmsnorm", "decode", "exchange"],
+                    help="profiling aid: launch only this kernel three times on a reduced case and exit")
     ap.add_argument("--comm", default=None, choices=["all_reduce", "peer_all_reduce", "fused_exchange", "scatter_gather"],
-                    help="tensor-parallel exchange per block (default: fused_exchange = sum + rmsnorm + quantize + gather in one kernel of this library; peer_all_reduce = this library's all-reduce kernel; all_reduce = NCCL; scatter_gather = reduce-scatter + all-gather of the quantized activation, "
-                         "fewer bytes but four collectives per block: measured slower on 8 B200s, where the exchange is latency-bound)")
-    ap.add_argument("--ar-ctas", type=int, default=None, help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce / fused_exchange also that kernel's CTAs (default: 16; fused_exchange 24 on 2 GPUs, 32 otherwise)")
-    ap.add_argument("--peer-path", default="switch_reduce", choices=["multicast_store", "switch_reduce", "peer_loads"],
-                    help="data path of peer_all_reduce: the switch's own reduction (default: fewest bytes; its bf16 sum is within one bf16 step of the exact sum, as "
-                         "NCCL's NVLS all-reduce), f32 sum over peer loads + multicast store (exact, rounded once), or peer loads only")
-    ap.add_argument("--sweep-exchange", action="store_true",
-                    help="N > 1, instead of the benchmark: time the step (one CUDA graph) for every exchange mode / row-chunk count / CTA count over the "
-                         "same weights, and a bare 64 MiB all-reduce by NCCL and by the peer kernel's three paths; one JSON line (profiles/tp_exchange_modes_*)")
-    ap.add_argument("--pdl", type=int, default=None, choices=[0, 1],
-                    help="programmatic dependent launch of this library's kernels (tf_set_programmatic_launch); default: the library's default")
-    ap.add_argument("--chunks", type=int, default=None, help="row chunks whose all-reduces overlap the other chunk's GEMMs (default: 2 when N > 1)")
+                    help="tensor-parallel exchange per block (default: fused_exchange = sum + rmsnorm + quantize + gather in one kernel of this library; "
+                         "peer_all_reduce = this library's all-reduce kernel; all_reduce = NCCL; scatter_gather = reduce-scatter + all-gather of the quantized activation)")
+    ap.add_argument("--ar-ctas", type=int, default=None,
+                    help="SMs the GEMMs leave free while a row chunk's exchange runs beside them; with peer_all_reduce / fused_exchange also that kernel's CTAs")
+    ap.add_argument("--peer-path", default="multicast_store", choices=["multicast_store", "switch_reduce", "peer_loads"],
+                    help="data path of the exchange kernels: f32 sum over peer loads in rank order, rounded once, written through the switch (default: the bytes "
+                         "the oracle computes); the switch's own reduction (fewer bytes, but its bf16 sums are one bf16 step off in a fifth of the elements, "
+                         "which moves every quantization downstream); or peer loads only")
+    ap.add_argument("--chunks", type=int, default=None, help="row chunks whose exchanges overlap the other chunk's GEMMs (default: 2 when N > 1)")
     return ap.parse_args()
 
 
@@ -64,6 +69,13 @@ def peaks():
         d = json.load(open(path))
         return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"], "source": "measured"}
     return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def host_threads() -> int:
+    try:
+        return len(os.sched_getaffinity(0))
+    except (AttributeError, OSError):
+        return os.cpu_count() or 1
 
 
 # ----------------------------------------------------------------------------------------------------------------------
@@ -106,6 +118,8 @@ def run_reference(args, rank: int) -> None:
         return
     import torch
 
+    cores = host_threads()
+    torch.set_num_threads(cores)  # under torch.distributed.run OMP_NUM_THREADS is 1: use the cores this process may run on
     rows = 128
     cpu_block_seconds(rows)  # warm-up (also pages the weights in)
     for _ in range(max(0, min(args.warmup, 2) - 1)):
@@ -114,13 +128,12 @@ def run_reference(args, rank: int) -> None:
     t_block = statistics.median(times)
     t_step = t_block * LAYERS * (M_TOKENS / rows)  # the full step, scaled linearly in rows and layers
     value = M_TOKENS / t_step
-    cores = torch.get_num_threads()
     sample = f"{rows} of {M_TOKENS} rows x 1 of {LAYERS} layers per timed run (f32 matmuls of dequantized operands), scaled linearly"
     line = {
         "impl": "reference", "metric": "mlp_tokens_per_s", "value": value, "unit": "tokens/s", "n_gpus": args.gpus, "steps": len(times),
         "warmup": args.warmup, "ms_per_step": t_step * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic", "config": {"workload": WORKLOAD, "note": "CPU restatement (oracle) of the block; the reference types this path but cannot run it"},
-        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -164,27 +177,70 @@ class ClockSampler:
             for name, val in zip(names, parts[3:7]):
                 if val.lower().startswith("active"):
                     reasons.add(name)
-        # samples under load are the upper half of the clock samples' power... keep it simple: median of all samples
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def event_ms(fn, iters: int, torch, flush=None):
-    """Median device time of fn() over ``iters`` launches, CUDA events on the current stream, L2 flushed between launches."""
-    ts = []
-    for _ in range(iters):
+def graph_us(fns, torch, replays: int = 3, flush=None):
+    """Device time per launch, in microseconds: the launches ``fns`` (a list of callables, each enqueuing one kernel or one short chain)
+    are captured into ONE CUDA graph, so that no host time sits between them, and the graph is replayed ``replays`` times (the best is
+    kept; ``flush`` is zeroed before each replay to empty L2)."""
+    for f in fns[:3]:
+        f()
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for f in fns:
+            f()
+    g.replay()
+    torch.cuda.synchronize()
+    best = float("inf")
+    for _ in range(replays):
         if flush is not None:
             flush.zero_()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        fn()
-        b.record()
-        b.synchronize()
-        ts.append(a.elapsed_time(b))
-    return statistics.median(ts)
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        g.replay()
+        e.record()
+        e.synchronize()
+        best = min(best, s.elapsed_time(e) * 1e3 / len(fns))
+    del g
+    return best
 
 
-def extras(torch, K, pk):
-    """Single-kernel headline metrics at N = 1: quantize GB/s (sweep point M = 65536) and block-scaled GEMM TFLOP/s."""
+def scaled_mm_operands(torch, q):
+    """A BlockScaledTensor as the operands torch._scaled_mm takes: the codes and the swizzled scale bytes, reinterpreted."""
+    if q.fmt == "mxfp8":
+        return q.codes.view(torch.float8_e4m3fn), q.scales.view(torch.float8_e8m0fnu)
+    return q.codes.view(torch.float4_e2m1fn_x2), q.scales.view(torch.float8_e4m3fn)
+
+
+def library_gemm_us(torch, qa, qb, launches: int = 10):
+    """Microseconds of the vendor library's block-scaled GEMM on the same operands (None when this torch build has no such path)."""
+    try:
+        a, sa = scaled_mm_operands(torch, qa)
+        b, sb = scaled_mm_operands(torch, qb)
+        out = torch.empty((qa.shape[0], qb.shape[0]), dtype=torch.bfloat16, device=qa.codes.device)
+        return graph_us([lambda: torch._scaled_mm(a, b.t(), sa, sb, out_dtype=torch.bfloat16, out=out)] * launches, torch)
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def measured_tensor_peaks(torch, K):
+    """The FP8 and FP4 denominators: TFLOP/s of the vendor library's block-scaled GEMM (cuBLASLt through torch._scaled_mm) at 8192^3,
+    measured in this run on this GPU. Used as a peak only; no part of the product calls it."""
+    out = {}
+    g = torch.Generator(device="cuda").manual_seed(7)
+    n = 8192
+    a = torch.randn((n, n), generator=g, device="cuda").to(torch.bfloat16)
+    b = (torch.randn((n, n), generator=g, device="cuda") * n**-0.5).to(torch.bfloat16)
+    for fmt in ("mxfp8", "nvfp4"):
+        us = library_gemm_us(torch, K.quantize(a, fmt), K.quantize(b, fmt))
+        out[fmt] = round(2.0 * n**3 / us / 1e6, 1) if us else None
+    return out
+
+
+def extras(torch, K, pk, tensor_peak):
+    """Single-kernel headline metrics at N = 1: quantize GB/s (every sweep point) and block-scaled GEMM TFLOP/s."""
     out = {"quantize": {}, "gemm": {}}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
     m, k = 65536, 4096
@@ -192,83 +248,80 @@ def extras(torch, K, pk):
     x = torch.randn((m, k), generator=g, device="cuda")
     x = torch.where(torch.rand((m, k), generator=g, device="cuda") < 0.01, x * 100, x).to(torch.bfloat16)
     gs = K.nvfp4_global_scale(x)
-    for fmt, bpe in (("mxfp8", 2 + 1 + 1 / 32), ("mxfp4", 2 + 0.5 + 1 / 32), ("nvfp4", 2 + 0.5 + 1 / 16)):
-        fn = (lambda f=fmt: K.quantize(x, f, global_scale=gs if f == "nvfp4" else None))
-        for _ in range(3):
-            fn()
-        ms = event_ms(fn, 10, torch, flush)
-        gbs = m * k * bpe / ms / 1e6
-        out["quantize"][fmt] = {"GBps": round(gbs, 1), "us": round(ms * 1e3, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 3), "shape": [m, k]}
-    ms = event_ms(lambda: K.nvfp4_global_scale(x, out=gs), 10, torch, flush)
-    out["quantize"]["nvfp4_amax_pass"] = {"GBps": round(m * k * 2 / ms / 1e6, 1), "us": round(ms * 1e3, 1)}
+    copy_dst = torch.empty_like(x)
+    copy_us = graph_us([lambda: copy_dst.copy_(x)] * 5, torch)
+    del copy_dst
+    out["quantize"]["copy_GBps_this_run"] = round(2 * m * k * 2 / copy_us / 1e3, 1)
+    for fmt, bpe in BYTES_PER_ELEM.items():
+        q = K.quantize(x, fmt, global_scale=gs if fmt == "nvfp4" else None)
+        us = graph_us([lambda f=fmt, q=q: K.quantize(x, f, global_scale=gs if f == "nvfp4" else None, out=q)] * 10, torch, flush=flush)
+        gbs = m * k * bpe / us / 1e3
+        out["quantize"][fmt] = {"GBps": round(gbs, 1), "us": round(us, 1), "frac_of_hbm_peak": round(gbs / pk["hbm_gbs"], 3), "shape": [m, k]}
+        del q
+    us_amax = graph_us([lambda: K.nvfp4_global_scale(x, out=gs)] * 10, torch, flush=flush)
+    out["quantize"]["nvfp4_amax_pass"] = {"GBps": round(m * k * 2 / us_amax / 1e3, 1), "us": round(us_amax, 1), "frac_of_hbm_peak": round(m * k * 2 / us_amax / 1e3 / pk["hbm_gbs"], 3)}
+    q = K.quantize(x, "nvfp4")
+    us2 = graph_us([lambda: K.quantize(x, "nvfp4", out=q)] * 5, torch, flush=flush)  # global scale computed inside: amax pass + quantize pass
+    gbs2 = m * k * (BYTES_PER_ELEM["nvfp4"] + 2) / us2 / 1e3
+    out["quantize"]["nvfp4_two_pass"] = {"GBps": round(gbs2, 1), "us": round(us2, 1), "frac_of_hbm_peak": round(gbs2 / pk["hbm_gbs"], 3),
+                                         "bytes_per_elem": BYTES_PER_ELEM["nvfp4"] + 2, "note": "amax pass + quantize pass, the tensor read twice"}
+    del q
     out["quantize"]["sweep"] = {}
-    for ms_rows in (1, 128, 8192):  # the smaller points of the sweep: launch-latency bound up to M = 128
-        xs = x[:ms_rows]
+    for rows in (1, 128, 8192):  # launch-latency bound up to M = 128; four rotating inputs so that M = 8192 (64 MB) does not sit in L2
+        xs = [x[i * rows:(i + 1) * rows] for i in range(4)]
         row = {}
-        for fmt, bpe in (("mxfp8", 2 + 1 + 1 / 32), ("mxfp4", 2 + 0.5 + 1 / 32), ("nvfp4", 2 + 0.5 + 1 / 16)):
-            fn = (lambda f=fmt: K.quantize(xs, f, global_scale=gs if f == "nvfp4" else None))
-            for _ in range(3):
-                fn()
-            t = event_ms(fn, 10, torch, flush if ms_rows >= 8192 else None)
-            row[fmt] = {"us": round(t * 1e3, 1), "GBps": round(ms_rows * k * bpe / t / 1e6, 1)}
-        out["quantize"]["sweep"][f"M={ms_rows}"] = row
-    del x
+        for fmt, bpe in BYTES_PER_ELEM.items():
+            qs = [K.quantize(t, fmt, global_scale=gs if fmt == "nvfp4" else None) for t in xs]
+            fns = [(lambda f=fmt, t=xs[i % 4], q=qs[i % 4]: K.quantize(t, f, global_scale=gs if f == "nvfp4" else None, out=q)) for i in range(20)]
+            us = graph_us(fns, torch)
+            row[fmt] = {"us": round(us, 2), "GBps": round(rows * k * bpe / us / 1e3, 1)}
+        out["quantize"]["sweep"][f"M={rows}"] = row
+    out["quantize"]["timing"] = "every figure: launches captured into one CUDA graph (no host time between them), best of 3 replays; L2 flushed before a replay at M = 65536"
+    del x, xs
     m, n, k = 4096, 6144, 2560
     a = torch.randn((m, k), generator=g, device="cuda").to(torch.bfloat16)
     w = (torch.randn((n, k), generator=g, device="cuda") * k**-0.5).to(torch.bfloat16)
-    for fmt, mult in (("mxfp8", 2), ("nvfp4", 4)):
+    for fmt in ("mxfp8", "nvfp4"):
         qa, qb = K.quantize(a, fmt), K.quantize(w, fmt)
         o = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
-        fn = (lambda: K.gemm_blockscaled(qa, qb, out=o))
-        for _ in range(3):
-            fn()
-        # back-to-back launches so that host launch latency is hidden; operands (tens of MB) stay in L2 by design of the shape
-        iters = 20
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        s.record()
-        for _ in range(iters):
-            fn()
-        e.record()
-        e.synchronize()
-        ms = s.elapsed_time(e) / iters
-        tf = 2 * m * n * k / ms / 1e9
-        ms_q = event_ms(lambda: K.quantize(a, fmt), 5, torch)
+        us = graph_us([lambda: K.gemm_blockscaled(qa, qb, out=o)] * 20, torch)
+        tf = 2 * m * n * k / us / 1e6
+        us_q = graph_us([lambda: K.quantize(a, fmt, out=qa)] * 20, torch)
+        lib_us = library_gemm_us(torch, qa, qb, 20)
         small = {}
-        for sm_rows in (1, 16, 128):  # weight-streaming regime: report time and the rate the weights are read at
-            qs = K.quantize(a[:sm_rows], fmt)
-            os_ = torch.empty((sm_rows, n), dtype=torch.bfloat16, device="cuda")
-            need = K.gemm_workspace_bytes(sm_rows, n, k, fmt)
-            ws = torch.empty(max(need, 1), dtype=torch.uint8, device="cuda")
-            gfn = (lambda: K.gemm_blockscaled(qs, qb, out=os_, workspace=ws))
-            for _ in range(3):
-                gfn()
-            gr = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(gr):
-                for _ in range(20):
-                    gfn()
-            gr.replay()
-            s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            torch.cuda.synchronize()
-            s2.record()
-            gr.replay()
-            e2.record()
-            e2.synchronize()
-            us = s2.elapsed_time(e2) / 20 * 1e3
-            small[f"M={sm_rows}"] = {"us": round(us, 2), "weights_GBps": round(qb.nbytes() / us / 1e3, 1), "TFLOPs": round(2 * sm_rows * n * k / us / 1e6, 2)}
+        for rows in (1, 16, 128):  # weight-streaming regime: report time and the rate the weights are read at
+            qs = K.quantize(a[:rows], fmt)
+            os_ = torch.empty((rows, n), dtype=torch.bfloat16, device="cuda")
+            ws = torch.empty(max(K.gemm_workspace_bytes(rows, n, k, fmt), 1), dtype=torch.uint8, device="cuda")
+            us_s = graph_us([lambda: K.gemm_blockscaled(qs, qb, out=os_, workspace=ws)] * 20, torch)
+            small[f"M={rows}"] = {"us": round(us_s, 2), "weights_GBps": round(qb.nbytes() / us_s / 1e3, 1), "TFLOPs": round(2 * rows * n * k / us_s / 1e6, 2)}
         out["gemm"][fmt + "_small_m"] = small
-        out["gemm"][fmt] = {"TFLOPs": round(tf, 1), "us": round(ms * 1e3, 1), "a_quantize_us": round(ms_q * 1e3, 1), "shape": [m, n, k],
-                            "frac_of_peak": round(tf / (mult * pk["bf16_tflops"]), 3), "peak": f"{mult} x bf16 burst {pk['bf16_tflops']} ({pk['source']})",
-                            "frac_of_nominal": round(tf / (2250.0 * mult), 3)}
+        peak = tensor_peak.get(fmt)
+        out["gemm"][fmt] = {"TFLOPs": round(tf, 1), "us": round(us, 2), "a_quantize_us": round(us_q, 2), "shape": [m, n, k],
+                            "frac_of_peak": round(tf / peak, 3) if peak else None, "peak": peak,
+                            "peak_is": "TFLOP/s of the vendor library's block-scaled GEMM at 8192^3, measured in this run",
+                            "library_same_shape_TFLOPs": round(2 * m * n * k / lib_us / 1e6, 1) if lib_us else None,
+                            "frac_of_library_same_shape": round(lib_us / us, 3) if lib_us else None,
+                            "frac_of_nominal": round(tf / (4500.0 if fmt == "mxfp8" else 9000.0), 3)}
     return out
 
 
-def finish_ranks(world: int) -> None:
-    """End of a multi-rank run: destroying the NCCL process group after its collectives were captured into a CUDA graph
-    blocks forever (observed on this stack), so the ranks meet at a barrier, flush and leave without tearing NCCL down."""
+def cleanup_ranks(world: int, stacks=(), graphs=()) -> None:
+    """End of a multi-rank run. Captured graphs are dropped first (they hold the captured exchange kernels and collectives), every stack
+    releases its symmetric memory and handles, the ranks meet at a barrier; only then does a rank leave. The process still exits through
+    os._exit: destroying an NCCL process group whose collectives had been captured into a CUDA graph blocked on this torch / NCCL pair,
+    and that teardown is not attempted again here."""
+    import torch
+
+    for g in graphs:
+        del g
+    for s in stacks:
+        if s is not None:
+            s.close()
+    gc.collect()
+    torch.cuda.synchronize()
     if world <= 1:
         return
-    import torch
     import torch.distributed as dist
 
     dist.barrier()
@@ -278,18 +331,16 @@ def finish_ranks(world: int) -> None:
     os._exit(0)
 
 
-def extras_mlp(torch, K, pk):
-    """The other two MLP configurations, through the typed API and CUDA-graph replay: the README decoder block (H = 2560,
-    F = 3072, MXFP8; exported plan, replayed and captured) at M = 1, 32, 512, 8192, and the decode shape of the stack
-    (M = 64, 4 of the 32 layers timed, all 32 reported by scaling)."""
+def extras_mlp(torch, K, pk, tensor_peak):
+    """The README decoder block (H = 2560, F = 3072, MXFP8) through the typed API: exported plan, replayed as one captured CUDA graph,
+    at M = 1, 32, 512, 8192."""
     import tempfile
 
     import tilefish_b200 as tilefish
     from tilefish_b200 import Dim, InOut, Tensor, bf16, const, f32, mxfp8
-    from tilefish_b200 import mlp as MLP
     from tilefish_b200 import runtime
 
-    out = {"readme_block_mxfp8": {}, "decode_stack_nvfp4": {}}
+    out = {}
     Mb, Hb, Fb = Dim("M", buckets=[1, 32, 512, 8192]), Dim("H", 2560), Dim("F", 3072)
 
     @tilefish.kernel
@@ -316,6 +367,7 @@ def extras_mlp(torch, K, pk):
     q_gu = K.quantize((torch.randn((6144, 2560), generator=g, device="cuda") * 2560**-0.5).to(torch.bfloat16), "mxfp8")
     q_d = K.quantize((torch.randn((2560, 3072), generator=g, device="cuda") * 3072**-0.5).to(torch.bfloat16), "mxfp8")
     weight_bytes = q_gu.nbytes() + q_d.nbytes()
+    fp8_peak = tensor_peak.get("mxfp8") or 2 * pk["bf16_tflops"]
     with tempfile.TemporaryDirectory() as d:
         exp = runtime.export(block, d)
         for m in (1, 32, 512, 8192):
@@ -333,50 +385,22 @@ def extras_mlp(torch, K, pk):
             e.record()
             e.synchronize()
             us = s.elapsed_time(e) / iters * 1e3
-            roof = max(6 * 2560 * 3072 * m / (2 * pk["bf16_tflops"] * 1e12), weight_bytes / (pk["hbm_gbs"] * 1e9)) * 1e6
-            out["readme_block_mxfp8"][f"M={m}"] = {"tokens_per_s": round(m / us * 1e6, 1), "us_per_step": round(us, 2), "roofline_us": round(roof, 2),
-                                                   "frac_of_roofline": round(roof / us, 3)}
-        out["readme_block_mxfp8"]["note"] = ("exported plan replayed as one captured CUDA graph (3 launches: rmsnorm+quantize, gemm+SiLU gate+quantize, gemm); "
-                                             "roofline = max(6HF*M / (2 x bf16 burst), weight bytes / HBM peak)")
-    # decode: M = 64 through the 70B-shaped stack (4 layers timed)
-    layers = []
-    for layer in range(4):
-        gg = torch.Generator(device="cuda").manual_seed(2000 + layer)
-        w_gu = (torch.randn((2 * F, H), generator=gg, device="cuda") * H**-0.5).to(torch.bfloat16)
-        w_d = (torch.randn((H, F), generator=gg, device="cuda") * F**-0.5).to(torch.bfloat16)
-        layers.append(MLP.quantize_weights(torch.ones(H, dtype=torch.bfloat16, device="cuda"), w_gu, w_d, FMT))
-        del w_gu, w_d
-    stack = MLP.MlpStack(layers)
-    x = torch.randn((64, H), generator=g, device="cuda").to(torch.bfloat16)
-    res = torch.zeros((64, H), device="cuda")
-    cap = stack.capture(x, res)
-    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    ts = []
-    for _ in range(10):
-        flush.zero_()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        cap.replay()
-        e.record()
-        e.synchronize()
-        ts.append(s.elapsed_time(e))
-    ms_layer = statistics.median(ts) / 4
-    wbytes = stack.weight_bytes() / 4
-    out["decode_stack_nvfp4"] = {"M": 64, "us_per_layer": round(ms_layer * 1e3, 1), "tokens_per_s_32_layers": round(64 / (ms_layer * 32 / 1e3), 1),
-                                 "weight_stream_GBps": round(wbytes / ms_layer / 1e6, 1), "frac_of_hbm_peak": round(wbytes / ms_layer / 1e6 / pk["hbm_gbs"], 3),
-                                 "note": "4 of 32 layers timed as one captured graph, L2 flushed between replays; HBM-bound (396 MB of weights per layer)"}
-    return out
+            roof = max(6 * 2560 * 3072 * m / (fp8_peak * 1e12), weight_bytes / (pk["hbm_gbs"] * 1e9)) * 1e6
+            out[f"M={m}"] = {"tokens_per_s": round(m / us * 1e6, 1), "us_per_step": round(us, 2), "roofline_us": round(roof, 2), "frac_of_roofline": round(roof / us, 3)}
+            del cap
+        out["note"] = ("exported plan replayed as one captured CUDA graph (3 launches: rmsnorm+quantize, gemm+SiLU gate+quantize, gemm); "
+                       "roofline = max(6HF*M / measured FP8 peak, weight bytes / HBM peak)")
+        runtime.clear_caches()
+    return {"readme_block_mxfp8": out}
 
 
-def run_single_kernel(name: str, pdl=None) -> None:
-    """Three launches of one kernel on a case of a few hundred MB (larger than L2, small enough for a multi-pass ncu capture)."""
+def run_single_kernel(name: str) -> None:
+    """Three launches of one kernel on a case of a few hundred MB (larger than L2, small enough for a multi-pass profiler capture)."""
     import torch
 
     from tilefish_b200 import kernels as K
 
     K.require_cuda()
-    if pdl is not None:
-        K.set_programmatic_launch(bool(pdl))
     g = torch.Generator(device="cuda").manual_seed(0)
     if name == "gemm1":  # the dominant kernel at half the benchmark's width: M = 4096, F = 14336, K = 8192, nvfp4, SiLU-gate epilogue
         m, f, k = 4096, F // 2, H
@@ -385,6 +409,11 @@ def run_single_kernel(name: str, pdl=None) -> None:
         out = torch.empty((m, f), dtype=torch.bfloat16, device="cuda")
         amax = torch.zeros(1, device="cuda")
         fn = lambda: K.gemm_blockscaled(qa, qb, epilogue="silu_gate", out=out, amax_out=amax)  # noqa: E731
+    elif name == "gemm-config3":  # the third benchmark configuration's GEMM: 4096 x 6144 x 2560, nvfp4
+        qa = K.quantize(torch.randn((4096, 2560), generator=g, device="cuda").to(torch.bfloat16), FMT)
+        qb = K.quantize((torch.randn((6144, 2560), generator=g, device="cuda") * 2560**-0.5).to(torch.bfloat16), FMT)
+        out = torch.empty((4096, 6144), dtype=torch.bfloat16, device="cuda")
+        fn = lambda: K.gemm_blockscaled(qa, qb, out=out)  # noqa: E731
     elif name == "decode":  # two blocks of the stack at M = 64 (weights stream once per block): the launch list of the decode path
         from tilefish_b200 import mlp as MLP
 
@@ -395,8 +424,8 @@ def run_single_kernel(name: str, pdl=None) -> None:
             blocks.append(MLP.quantize_weights(torch.ones(H, dtype=torch.bfloat16, device="cuda"), w_gu, w_d, FMT))
             del w_gu, w_d
         stack = MLP.MlpStack(blocks)
-        x = torch.randn((64, H), generator=g, device="cuda").to(torch.bfloat16)
-        res = torch.zeros((64, H), device="cuda")
+        x = torch.randn((M_DECODE, H), generator=g, device="cuda").to(torch.bfloat16)
+        res = torch.zeros((M_DECODE, H), device="cuda")
         fn = lambda: stack(x, res)  # noqa: E731
     elif name == "exchange":  # the fused exchange kernel on one GPU (a single rank: nothing to sum; residual add + rmsnorm + amax + nvfp4 quantize)
         from tilefish_b200.collective import PeerAllReduce
@@ -431,68 +460,135 @@ def run_single_kernel(name: str, pdl=None) -> None:
     print(json.dumps({"kernel": name, "launches": 3}))
 
 
-def exchange_sweep(args, torch, MLP, blocks, group, dev, rank, world, layers, m) -> None:
-    """Every exchange variant of the tensor-parallel step over the same weights: per variant the step is captured into one CUDA
-    graph and `--steps` replays are timed with CUDA events (max over ranks). Also the bare all-reduce of one [M, H] bf16 tensor."""
+def make_stack(MLP, blocks, group, world, comm, chunks, ctas, peer_path):
+    return MLP.MlpStack(blocks, group=group, chunks=chunks if world > 1 else 1, comm=comm, sm_margin=ctas, peer_path=peer_path)
+
+
+def parity_check(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, peer_path, x_all):
+    """The first 128 x N rows of the step's real input through the first two blocks of the real weights: on the GPUs with the exchange the
+    benchmark uses (one row chunk), and on rank 0's host with the CPU oracle of the same tensor-parallel computation (per-rank weight
+    shards cut from the full quantized weights, bf16 partial results, f32 sum in rank order rounded once, nvfp4 global scales per row
+    block as the exchange forms them). Returns the comparison (rank 0) or None."""
+    from oracle import blockscaled as O  # the checker only: nothing that is timed or shipped calls it
+
+    layers = min(2, len(blocks))
+    rows = 128 * world
+    x = x_all[:rows].contiguous()
+    res0 = torch.zeros((rows, H), dtype=torch.float32)
+    rows_sharded = world > 1 and comm in ("fused_exchange", "scatter_gather")
+    stack = make_stack(MLP, blocks[:layers], group, world, comm, 1, ctas, peer_path)
+    res = res0.to(dev)
+    y = stack(x.to(dev), res)
+    torch.cuda.synchronize()
+    stack.check()
+    y_host, res_host = y.cpu(), res.cpu()
+    stack.close()
+    del stack, y, res
+    out = None
+    if rank == 0:
+        torch.set_num_threads(host_threads())
+        full = []
+        for layer in range(layers):
+            g = torch.Generator(device=dev).manual_seed(1000 + layer)
+            w_gu = (torch.randn((2 * F, H), generator=g, device=dev) * H**-0.5).to(torch.bfloat16)
+            w_d = (torch.randn((H, F), generator=g, device=dev) * F**-0.5).to(torch.bfloat16)
+            w_n = (1 + 0.1 * torch.randn(H, generator=g, device=dev)).to(torch.bfloat16)
+            q = []
+            for w in (w_gu, w_d):  # the full weights, quantized by the kernels (bit-exact with the oracle's quantizer: its own tests), plain scales
+                t = K.quantize(w, FMT, layout="plain")
+                q.append((t.codes.cpu(), t.plain_scales().cpu(), t.global_scale.cpu().reshape(()) if t.global_scale is not None else None))
+                del t
+            full.append((w_n.cpu(), q[0], q[1]))
+            del w_gu, w_d
+        t0 = time.perf_counter()
+        r_ref, y_ref = O.tp_mlp_stack(x, res0, full, FMT, world, norm="row_sharded" if rows_sharded else "replicated")
+        c, cr = O.compare(y_host, y_ref), O.compare(res_host, r_ref)
+        # nvfp4, two blocks of the benchmark's shape: max|d| <= 2**-3 max|ref| and relative Frobenius error <= 5e-2 (measured on two B200s:
+        # 0.068 and 0.018, with 8 % of the elements different: where the GPU's and the host's bf16 activations differ by one ulp (accumulation
+        # order over K = 8192 / 28672, the approximate exponential of the SiLU) an e2m1 code can flip or a block scale move by one e4m3 step.
+        # For scale: two runs whose inputs differ by one bf16 ulp are 7e-2 apart, any nvfp4 run is 0.19 from the unquantized arithmetic, and a
+        # wrong exchange (a rank's partial result missing) is beyond 0.5). With the switch's own reduction, whose sums are one bf16 step off in
+        # a fifth of the elements: 2**-2 and 0.12
+        switch = world > 1 and peer_path == "switch_reduce" and comm in ("fused_exchange", "peer_all_reduce")
+        max_bound, fro_bound = (2.0**-2, 0.12) if switch else (2.0**-3, 5e-2)
+        out = {"rows": rows, "blocks": layers, "oracle": f"tp_mlp_stack(world={world}, norm={'row_sharded' if rows_sharded else 'replicated'}) on the host",
+               "max_rel": round(c["max_rel"], 5), "rel_fro": round(c["rel_fro"], 5), "frac_diff": round(c["frac_diff"], 4), "residual_rel_fro": round(cr["rel_fro"], 6),
+               "bound": {"max_rel": max_bound, "rel_fro": fro_bound},
+               "ok": bool(c["max_rel"] <= max_bound and c["rel_fro"] <= fro_bound and cr["rel_fro"] <= fro_bound),
+               "oracle_seconds": round(time.perf_counter() - t0, 1)}
+    return out
+
+
+def decode_line(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, peer_path, pk):
+    """The same stack at M = 64 (decode): weights stream from HBM once per block, so the roofline is this rank's weight bytes over the HBM peak.
+    With N > 1 the exchange needs 128 x N rows per call: the 64 tokens are padded to that many rows (the padding rows are zeros)."""
     import torch.distributed as dist
 
-    from tilefish_b200.collective import PeerAllReduce
+    layers = len(blocks)
+    fused = world > 1 and comm in ("fused_exchange", "scatter_gather")
+    rows = 128 * world if fused else M_DECODE
+    stack = make_stack(MLP, blocks, group, world, comm, 1, ctas, peer_path)
+    x = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
+    x[:M_DECODE] = torch.randn((M_DECODE, H), generator=torch.Generator(device=dev).manual_seed(3), device=dev).to(torch.bfloat16)
+    res = torch.zeros((rows, H), dtype=torch.float32, device=dev)
+    cap = stack.capture(x, res)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    ts = []
+    for _ in range(8):
+        flush.zero_()
+        res.zero_()
+        if world > 1:
+            dist.barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        cap.replay()
+        e.record()
+        e.synchronize()
+        ts.append(s.elapsed_time(e))
+    ms = statistics.median(ts)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    stack.check()
+    wbytes = stack.weight_bytes() / layers
+    cap.release()
+    stack.close()
+    us_layer = ms * 1e3 / layers
+    return {"M": M_DECODE, "rows_per_call": rows, "layers_timed": layers, "us_per_layer": round(us_layer, 1), "tokens_per_s": round(M_DECODE / (ms / 1e3) * (layers / LAYERS), 1),
+            "weight_stream_GBps_per_gpu": round(wbytes / us_layer / 1e3, 1), "frac_of_hbm_peak": round(wbytes / us_layer / 1e3 / pk["hbm_gbs"], 3),
+            "roofline_us_per_layer": round(wbytes / pk["hbm_gbs"] / 1e3, 1),
+            "note": "one captured CUDA graph per step, L2 flushed between replays, median of 8, max over ranks; tokens/s is for 32 layers"}
 
-    def timed(fn, n):
+
+def row_sharded_quantize_line(torch, K, group, world, rank, dev, pk):
+    """Quantize shards by rows with no exchange (nvfp4: one 4-byte max all-reduce for the tensor's global scale): M = 65536 rows over the ranks."""
+    import torch.distributed as dist
+
+    from tilefish_b200.collective import quantize_rows_sharded
+
+    m, k = 65536 // world, 4096
+    g = torch.Generator(device=dev).manual_seed(rank)
+    x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+    out = {}
+    for fmt, bpe in BYTES_PER_ELEM.items():
         for _ in range(3):
-            fn()
+            quantize_rows_sharded(x, fmt, group)
         dist.barrier()
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        for _ in range(n):
-            fn()
+        for _ in range(10):
+            quantize_rows_sharded(x, fmt, group)
         e.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([s.elapsed_time(e) / n], device=dev)
+        e.synchronize()
+        t = torch.tensor([s.elapsed_time(e) / 10], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return round(float(t.item()), 4)
-
-    out = {"sweep": "tp exchange", "n_gpus": world, "layers": layers, "tokens": m, "bare_allreduce_ms": {}, "step_ms": {}}
-    n = m * H
-    x = torch.randn(n, device=dev).to(torch.bfloat16)
-    out["bare_allreduce_ms"]["nccl"] = timed(lambda: dist.all_reduce(x), 20)
-    for path in ("switch_reduce", "multicast_store", "peer_loads"):
-        for ctas in (16, 32, 64, 128):
-            peer = PeerAllReduce(2 * n, group, dev, channels=1, num_ctas=ctas, multicast=path != "peer_loads", reduce_in_switch=path == "switch_reduce")
-            v = peer.view(0, (n,))
-            v.copy_(x)
-            out["bare_allreduce_ms"][f"{peer.mode}/{ctas} CTAs"] = timed(lambda: peer.allreduce_(v), 20)
-            if peer.status():
-                out["bare_allreduce_ms"][f"{peer.mode}/{ctas} CTAs"] = "bounded wait gave up"
-            del peer, v
-    del x
-    g = torch.Generator().manual_seed(0)
-    x_dev = torch.randn((m, H), generator=g).to(torch.bfloat16).to(dev)
-    residual = torch.zeros((m, H), dtype=torch.float32, device=dev)
-    variants = [("all_reduce", 1, None, 16), ("all_reduce", 2, None, 16)]
-    for path in ("switch_reduce", "multicast_store"):
-        variants += [("peer_all_reduce", 1, path, 148), ("peer_all_reduce", 1, path, 64), ("peer_all_reduce", 2, path, 16), ("peer_all_reduce", 2, path, 32),
-                     ("peer_all_reduce", 2, path, 48)]
-        variants += [("fused_exchange", 1, path, 148), ("fused_exchange", 1, path, 64), ("fused_exchange", 2, path, 16), ("fused_exchange", 2, path, 32),
-                     ("fused_exchange", 2, path, 48)]
-    variants += [("peer_all_reduce", 3, "switch_reduce", 16), ("peer_all_reduce", 4, "switch_reduce", 16), ("peer_all_reduce", 4, "switch_reduce", 8),
-                 ("peer_all_reduce", 2, "switch_reduce", 8), ("fused_exchange", 4, "switch_reduce", 32)]
-    for comm, chunks, path, ctas in variants:
-        stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=ctas, peer_path=path or "multicast_store")
-        cap = stack.capture(x_dev, residual)
-
-        def step():
-            residual.zero_()
-            cap.replay()
-
-        key = f"{comm}" + (f"/{path}" if path else "") + f", {chunks} chunk(s), {ctas} CTAs left to the exchange"
-        out["step_ms"][key] = timed(step, args.steps)
-        if getattr(stack, "_peer", None) is not None and stack._peer.status():
-            out["step_ms"][key] = "bounded wait gave up"
-        del cap, stack
-    if rank == 0:
-        print(json.dumps(out), flush=True)
+        us = float(t.item()) * 1e3
+        total_bpe = bpe + (2 if fmt == "nvfp4" else 0)
+        out[fmt] = {"us": round(us, 1), "aggregate_GBps": round(65536 * k * total_bpe / us / 1e3, 1), "frac_of_n_x_hbm_peak": round(65536 * k * total_bpe / us / 1e3 / (world * pk["hbm_gbs"]), 3)}
+    out["note"] = f"65536 x 4096 rows split over {world} ranks, eager launches back to back (max over ranks); nvfp4 includes the amax pass and the 4-byte max all-reduce"
+    return out
 
 
 def run_ours(args) -> None:
@@ -518,10 +614,8 @@ def run_ours(args) -> None:
     from tilefish_b200 import mlp as MLP
 
     K.require_cuda()
-    if args.pdl is not None:
-        K.set_programmatic_launch(bool(args.pdl))
     pk = peaks()
-    layers, m = args.layers, args.tokens
+    layers, m = args.layers, M_TOKENS
 
     # ---- weights: seeded per layer, identical on every rank, quantized once and sharded ----
     blocks = []
@@ -532,20 +626,13 @@ def run_ours(args) -> None:
         w_n = (1 + 0.1 * torch.randn(H, generator=g, device=dev)).to(torch.bfloat16)
         blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, FMT, rank=rank, world=world))
         del w_gu, w_d
-    if args.sweep_exchange:
-        if world < 2:
-            raise SystemExit("bench.py: --sweep-exchange needs --gpus >= 2")
-        exchange_sweep(args, torch, MLP, blocks, group, dev, rank, world, layers, m)
-        finish_ranks(world)
-        return
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    # default exchange: this library's fused kernel (sum of the partial results + residual add + rmsnorm + quantize + gather in one
-    # launch per block and chunk, switch reduction). Measured over the full 32 layers, tokens/s: 8 GPUs 483.9 k (32 CTAs) against
-    # 396.9 k with this library's all-reduce kernel and 292 k with NCCL's all-reduce; 2 GPUs 158.2 k (24 CTAs) against 154.9 k and 148.5 k
+    # default exchange: this library's fused kernel (sum of the partial results + residual add + rmsnorm + quantize + gather in one launch per
+    # block and chunk, switch reduction)
     comm = args.comm or ("fused_exchange" if world > 1 else "all_reduce")
     if args.ar_ctas is None:
         args.ar_ctas = (24 if world == 2 else 32) if comm == "fused_exchange" else 16
-    stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm=comm, sm_margin=args.ar_ctas, peer_path=args.peer_path)
+    stack = make_stack(MLP, blocks, group, world, comm, chunks, args.ar_ctas, args.peer_path)
     torch.cuda.synchronize()
 
     gx = torch.Generator().manual_seed(0)
@@ -586,14 +673,10 @@ def run_ours(args) -> None:
 
     def step_e2e():
         x_dev.copy_(x_host, non_blocking=True)
-        residual.zero_()
-        y = step_inner()
+        y = step()
         out_host.copy_(y, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         return out_host
-
-    def step_inner():
-        return stack(x_dev, residual, rows_local=True) if rows_local else stack(x_dev, residual)
 
     def barrier():
         if world > 1:
@@ -621,20 +704,22 @@ def run_ours(args) -> None:
 
     exchange_note = None
     if world > 1 and args.comm is None and stack.comm in ("peer_all_reduce", "fused_exchange"):
-        # the default picked this library's all-reduce: if its symmetric memory cannot be set up on this machine (every rank sees
+        # the default picked this library's exchange kernel: if its symmetric memory cannot be set up on this machine (every rank sees
         # the same refusal), run the NCCL exchange instead and say so in the line
         try:
             step()
         except Exception as e:  # noqa: BLE001
             exchange_note = f"{stack.comm} unavailable ({type(e).__name__}: {str(e)[:120]}); NCCL collectives used"
-            stack = MLP.MlpStack(blocks, group=group, chunks=chunks, comm="scatter_gather" if rows_local else "all_reduce", sm_margin=16)
+            comm = "scatter_gather" if rows_local else "all_reduce"
+            stack = make_stack(MLP, blocks, group, world, comm, chunks, 16, args.peer_path)
             launches_per_step = layers * 5 * stack.chunks
     for _ in range(max(args.warmup, 3)):
         step()
     use_graph = world > 1
+    cap_graph = None
     if use_graph:
         # N > 1: the per-layer kernels are short (tens of microseconds per row chunk at 8 GPUs) and Python cannot enqueue them
-        # fast enough, so the whole step (kernels, both chunk streams, the NCCL all-reduces) is one captured CUDA graph.
+        # fast enough, so the whole step (kernels, both chunk streams, the exchanges) is one captured CUDA graph.
         # Per-kernel events cannot be recorded inside a replay: the dominant kernel is timed in an instrumented eager pass of
         # the same step right after the timed region.
         torch.cuda.synchronize()
@@ -671,54 +756,80 @@ def run_ours(args) -> None:
         step_e2e_fast()
     e2e_ms = timed(step_e2e_fast, args.steps)
     K.gemm_blockscaled = orig_gemm
+    error_word = stack._peer.status() if getattr(stack, "_peer", None) is not None else None
+    exchange = ({"kernel": "tp_norm_exchange_kernel" if stack.comm == "fused_exchange" else "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas,
+                 "error_word": error_word} if getattr(stack, "_peer", None) is not None else None)
+    stack_comm, stack_chunks = stack.comm, stack.chunks
+    # the timed stack's graph and symmetric memory go before the follow-up measurements build their own
+    cap_graph = None
+    y_cap = None
+    stack.close()
+    del stack
+    gc.collect()
 
     ms_per_step = total_ms / args.steps
     value = m / (ms_per_step / 1e3)
     e2e_value = m / (e2e_ms / args.steps / 1e3)
 
+    parity = None
+    if not args.no_parity:
+        parity = parity_check(torch, K, MLP, blocks, group, world, rank, dev, comm, args.ar_ctas, args.peer_path, x_all)
+    decode = None
+    sharded_q = None
+    if not args.no_extras:
+        decode = decode_line(torch, K, MLP, blocks[:min(layers, 8)], group, world, rank, dev, comm, args.ar_ctas, args.peer_path, pk)
+        if world > 1:
+            sharded_q = row_sharded_quantize_line(torch, K, group, world, rank, dev, pk)
+
+    if rank != 0:
+        cleanup_ranks(world)
+        return
+    del blocks
+    gc.collect()
+    torch.cuda.empty_cache()
+    tensor_peak = measured_tensor_peaks(torch, K)
+
     # roofline of the dominant kernel: gemm(h, w_gu) with the SiLU-gate epilogue, on this rank's shard
     f_local = F // world
-    flops = 2.0 * (m / stack.chunks) * (2 * f_local) * H
+    flops = 2.0 * (m / stack_chunks) * (2 * f_local) * H
     avg_ms = statistics.mean(gemm_ms) if gemm_ms else float("nan")
     achieved = flops / avg_ms / 1e9
-    peak = 4 * pk["bf16_tflops_sustained"]
+    peak = tensor_peak.get("nvfp4") or 4 * pk["bf16_tflops_sustained"]
     roofline = {"bound": "tensor", "kernel": "gemm_blockscaled_kernel<nvfp4, 256, silu_gate>", "achieved": round(achieved, 1), "peak": peak,
-                "unit": "TFLOP/s", "frac": round(achieved / peak, 4),
-                # DRAM read + write of one launch from the ncu capture summarised under profiles/ (242 MB at half width, F = 14336;
-                # the traffic is proportional to F): algorithmic bytes of a full-width launch are 518 MB
-                "traffic": round(242.3e6 * (2 * f_local) / 28672) if m == M_TOKENS else None, "traffic_unit": "bytes per launch (ncu, scaled from F = 14336)",
-                "peak_note": f"4 x sustained bf16 cuBLAS {pk['bf16_tflops_sustained']} TFLOP/s ({pk['source']}); no FP4 peak was measured on this pool. "
-                             f"Nominal dense FP4 is 9000: frac_of_nominal = {achieved / 9000.0:.4f}",
+                "unit": "TFLOP/s", "frac": round(achieved / peak, 4), "traffic": None,
+                "peak_note": ("FP4 block-scaled GEMM of the vendor library at 8192^3, measured in this run (burst: that GEMM timed alone)" if tensor_peak.get("nvfp4")
+                              else f"4 x sustained bf16 {pk['bf16_tflops_sustained']} TFLOP/s ({pk['source']}): this torch build has no block-scaled library GEMM")
+                             + f". Nominal dense FP4 is 9000: frac_of_nominal = {achieved / 9000.0:.4f}; frac of 4 x sustained bf16 = {achieved / (4 * pk['bf16_tflops_sustained']):.4f}",
                 "launches_timed": len(gemm_ms), "avg_launch_ms": round(avg_ms, 4),
                 "timing": "CUDA events around each launch " + ("in an instrumented eager pass after the timed region (the timed region replays a CUDA graph)"
                                                                if world > 1 else "inside the timed region")}
-
-    if rank != 0:
-        finish_ranks(world)
-        return
     line = {
         "metric": "mlp_tokens_per_s", "value": round(value, 1), "unit": "tokens/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "fp4 (e2m1 x e4m3 block scales, f32 accumulate, bf16 out)",
         "data": "synthetic", "impl": "ours",
-        "config": {"workload": WORKLOAD if (layers, m) == (LAYERS, M_TOKENS) else f"REDUCED {layers} layers M={m} (development run, not the benchmark)",
-                   "parallelism": f"tp{world}" + (f", {stack.comm}, {stack.chunks} row chunks on 2 streams (one chunk's exchange under the other's GEMMs)" if world > 1 else ""), "l2": "inputs larger than L2: every step streams all weights (>= 1.5 GB per GPU)"},
+        "config": {"workload": WORKLOAD if layers == LAYERS else f"REDUCED {layers} layers M={m} (not the benchmark)",
+                   "parallelism": f"tp{world}" + (f", {stack_comm}, {stack_chunks} row chunks on 2 streams (one chunk's exchange under the other's GEMMs)" if world > 1 else ""),
+                   "l2": "inputs larger than L2: every step streams all weights (>= 1.5 GB per GPU)"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": x_host.numel() * 2 * (world if rows_local else 1),
                 "d2h_bytes_per_step": out_host.numel() * 2 * (world if rows_local else 1),
                 "io": (f"each rank copies its own {m_io} rows; bytes are the job's total" if rows_local else "every rank copies the full tensors; bytes are per rank"),
                 "ms_per_step": round(e2e_ms / args.steps, 4)},
         "gpu_launches": launches_per_step * args.steps,
         "exchange_note": exchange_note,
-        "exchange": ({"kernel": "tp_norm_exchange_kernel" if stack.comm == "fused_exchange" else "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas, "error_word": stack._peer.status()}
-                     if getattr(stack, "_peer", None) is not None else None),
+        "exchange": exchange,
+        "parity": parity,
         "roofline": roofline,
+        "tensor_peak_measured": tensor_peak,
         "clocks": clocks,
+        "decode": decode,
     }
+    if sharded_q is not None:
+        line["row_sharded_quantize"] = sharded_q
     if world == 1:
         if not args.no_extras:
-            del stack, blocks
-            torch.cuda.empty_cache()
-            line["kernels"] = extras(torch, K, pk)
-            line["kernels"].update(extras_mlp(torch, K, pk))
+            line["kernels"] = extras(torch, K, pk, tensor_peak)
+            line["kernels"].update(extras_mlp(torch, K, pk, tensor_peak))
+        torch.set_num_threads(host_threads())
         rows = 128
         cpu_block_seconds(rows)
         t_block = cpu_block_seconds(rows, repeats=2)
@@ -726,7 +837,7 @@ def run_ours(args) -> None:
         line["cpu_baseline"] = {"value": round(cpu_value, 3), "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
                                 "sample": f"{rows} of {M_TOKENS} rows x 1 of {LAYERS} layers with the CPU oracle (f32 matmuls of dequantized operands), scaled linearly"}
     print(json.dumps(line), flush=True)
-    finish_ranks(world)
+    cleanup_ranks(world)
 
 
 def main() -> None:
@@ -736,7 +847,7 @@ def main() -> None:
         run_reference(args, rank)
         return
     if args.kernel:
-        run_single_kernel(args.kernel, args.pdl)
+        run_single_kernel(args.kernel)
         return
     run_ours(args)
 

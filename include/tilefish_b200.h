@@ -220,6 +220,38 @@ TF_API tf_status tf_tp_norm_exchange(const uint64_t* buffer_ptrs, const uint64_t
                                      int64_t gs_offset, int64_t rows_total, int64_t d, int32_t sum_peers, void* residual_rows, const void* w,
                                      void* h_scratch, float* amax, float eps, int32_t q_format, int32_t num_ctas, void* stream);
 
+/* ---- a native replay loop for exported plans ------------------------------------------------------------------------------------
+ * The C counterpart of the reference's Rust host for this path (crates/tilefish/src/plan_run.rs:678 PlanRun, :1944 launch, :2097
+ * capture; C ABI crates/tilefish-capi/include/tilefish.h): it reads the directory runtime.export() wrote (plan.json in the
+ * reference's plan schema 1, docs/en/plan-schema-1.md, and this backend's manifest.json), then runs a bucket's steps with no
+ * interpreter between the launches, or captures them into a CUDA graph.
+ *   tf_plan_load         strict JSON; the plan's digest is recomputed and compared with `pin` (64 hex digits; NULL = the caller trusts
+ *                        the directory) and with the file's own; the manifest's digest likewise; every step must name a manifest entry.
+ *                        Needs no GPU.
+ *   tf_plan_instantiate  the arena: `arena` (256-byte aligned, at least tf_plan_arena_bytes) or, with NULL, one cudaMalloc made here
+ *                        (the only allocation of this API; freed by tf_plan_free). Nothing is allocated afterwards.
+ *   tf_plan_bind         the caller's tensor for an external buffer, by the buffer's name in the plan ("x", "residual", "w_gu",
+ *                        "w_gu__scales", "w_gu__global", "out0" ...). Pointers stay bound until rebound.
+ *   tf_plan_find_bucket  the index of the bucket whose dimensions have exactly these values, or -1 (bucket semantics are exact).
+ *   tf_plan_launch       resolves and checks every step of the bucket with the real addresses (bindings present, 16-byte alignment,
+ *                        workspace large enough on this device) BEFORE the first launch, then enqueues the steps in order on `stream`.
+ *   tf_plan_capture      the same checks, then the steps captured on `stream` (not the legacy default stream) into a CUDA graph that
+ *                        the plan object owns; *graph_out is its index. The graph holds the addresses bound at capture time.
+ *   tf_plan_replay       launches a captured graph on `stream`.
+ * A plan object is used by one thread at a time. */
+typedef struct tf_plan tf_plan;
+TF_API tf_status tf_plan_load(const char* directory, const char* pin, tf_plan** out);
+TF_API void tf_plan_free(tf_plan* plan);
+TF_API const char* tf_plan_digest(const tf_plan* plan);
+TF_API int64_t tf_plan_arena_bytes(const tf_plan* plan);
+TF_API int32_t tf_plan_step_count(const tf_plan* plan, int32_t bucket);
+TF_API int32_t tf_plan_find_bucket(const tf_plan* plan, const char* const* dim_names, const int64_t* values, int32_t n);
+TF_API tf_status tf_plan_instantiate(tf_plan* plan, void* arena, int64_t arena_bytes);
+TF_API tf_status tf_plan_bind(tf_plan* plan, const char* buffer, void* device_ptr);
+TF_API tf_status tf_plan_launch(tf_plan* plan, int32_t bucket, void* stream);
+TF_API tf_status tf_plan_capture(tf_plan* plan, int32_t bucket, void* stream, int32_t* graph_out);
+TF_API tf_status tf_plan_replay(tf_plan* plan, int32_t graph, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -364,6 +364,24 @@ def tp_mlp_stack(x, residual, layers, fmt: str, world: int, *, norm: str = "repl
     return res, xs
 
 
+def mlp_stack_unquantized(x, residual, layers, fmt: str, eps: float = 1e-6):
+    """The stack with NO activation quantization and no bf16 rounding between the operators: f32 throughout, against the dequantized
+    weights. Not what the kernels compute; the yardstick for how far ANY quantized run is from the arithmetic it approximates."""
+    res = residual.clone()
+    xs = x.to(torch.float32)
+    for (w_n, q_gu, q_d) in layers:
+        res = res + xs
+        d = res.shape[-1]
+        rstd = torch.rsqrt((res * res).sum(dim=-1, keepdim=True) * (1.0 / d) + eps)
+        h = res * rstd * w_n.to(torch.float32)
+        t = h @ dequantize(q_gu[0], q_gu[1], fmt, q_gu[2]).t()
+        f = t.shape[1] // 2
+        g = t[:, :f]
+        a = g * (1.0 / (1.0 + torch.exp(-g))) * t[:, f:]
+        xs = a @ dequantize(q_d[0], q_d[1], fmt, q_d[2]).t()
+    return res, xs
+
+
 def compare(got: torch.Tensor, ref: torch.Tensor) -> dict:
     """The figures every parity statement of a bf16 result uses: max|d| / max|ref|, relative Frobenius error, fraction of
     elements that differ."""

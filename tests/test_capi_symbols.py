@@ -40,8 +40,10 @@ def header_prototypes():
 
     def cls(ctype: str) -> str:
         t = " ".join(ctype.replace("const", " ").split())
+        if t == "void":
+            return "void"
         if "*" in t:
-            return "str" if t.startswith("char") else "ptr"
+            return "str" if t.replace(" ", "") == "char*" else "ptr"
         base = t.split()[0] if t else "void"
         return {"int32_t": "i32", "tf_status": "i32", "int64_t": "i64", "uint64_t": "u64", "float": "f32"}[base]
 
@@ -61,6 +63,8 @@ def header_prototypes():
 def _ctypes_class(t) -> str:
     import ctypes
 
+    if t is None:
+        return "void"
     if t is ctypes.c_char_p:
         return "str"
     if t is ctypes.c_void_p or (isinstance(t, type) and issubclass(t, ctypes._Pointer)):

@@ -277,3 +277,35 @@ def test_gemm_quantized_output_equals_quantize_of_the_bf16_output(K, fmt, m, n, 
     codes, scales, _ = O.quantize(plain.cpu(), fmt)
     assert torch.equal(q.codes.cpu(), codes) and torch.equal(q.scales.cpu(), O.swizzle_scales(scales))
     no_device_timeout()
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 512), (384, 640, 1024)])
+def test_vendor_blockscaled_gemm_reads_the_same_swizzled_operands(fmt, m, n, k):
+    """An independent witness for the scale layout, the nibble order and the quantizer's bytes: cuBLASLt's block-scaled GEMM (through
+    torch._scaled_mm) is handed THIS package's codes and swizzled scale bytes, reinterpreted, and must meet the same bound against the
+    dequantized-operand oracle as this package's GEMM (2**-8 max|ref| x 1.01). A wrong layout or nibble order misses by orders of
+    magnitude. Rows get very different magnitudes so that every scale byte matters. The vendor GEMM is a checker here, never a product path."""
+    from tilefish_b200 import kernels as K
+
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn((m, k), generator=g) * torch.exp2(torch.randint(-6, 7, (m, 1), generator=g).float())).to(torch.bfloat16)
+    b = (torch.randn((n, k), generator=g) * k**-0.5 * torch.exp2(torch.randint(-4, 5, (n, 1), generator=g).float())).to(torch.bfloat16)
+    # magnitudes also vary along K, block by block
+    a = (a.float() * torch.exp2(torch.randint(-3, 4, (1, k // 32), generator=g).float()).repeat_interleave(32, dim=1)).to(torch.bfloat16)
+    qa, qb = K.quantize(a.cuda(), fmt), K.quantize(b.cuda(), fmt)
+    if fmt == "mxfp8":
+        ops = (qa.codes.view(torch.float8_e4m3fn), qb.codes.view(torch.float8_e4m3fn), qa.scales.view(torch.float8_e8m0fnu), qb.scales.view(torch.float8_e8m0fnu))
+    else:
+        ops = (qa.codes.view(torch.float4_e2m1fn_x2), qb.codes.view(torch.float4_e2m1fn_x2), qa.scales.view(torch.float8_e4m3fn), qb.scales.view(torch.float8_e4m3fn))
+    try:
+        theirs = torch._scaled_mm(ops[0], ops[1].t(), ops[2], ops[3], out_dtype=torch.float32)
+    except Exception as e:  # noqa: BLE001
+        pytest.skip(f"this torch build has no block-scaled library GEMM for {fmt}: {type(e).__name__}")
+    if fmt == "nvfp4":
+        theirs = theirs * (qa.global_scale * qb.global_scale)
+    mine = K.gemm_blockscaled(qa, qb)
+    ref = O.gemm_blockscaled(O.quantize(a, fmt), O.quantize(b, fmt), fmt).float()
+    bound = 2.0**-8 * float(ref.abs().max()) * 1.01
+    assert float((mine.cpu().float() - ref).abs().max()) <= bound
+    assert float((theirs.cpu() - ref).abs().max()) <= bound

@@ -233,3 +233,44 @@ def test_config4_block_at_8192_rows_matches_the_oracle_on_sampled_rows():
     g, r = y[rows.cuda()].cpu().float(), y_ref.float()
     assert float((g - r).abs().max()) <= 2.0**-6 * float(r.abs().max())
     assert float((g - r).norm() / r.norm()) <= 1e-2
+
+
+@pytest.mark.parametrize("fmt", [mxfp8, nvfp4], ids=["mxfp8", "nvfp4"])
+def test_native_replay_loop_gives_the_python_runner_s_bytes(fmt, tmp_path):
+    """The C++ replay loop (tf_plan_*, csrc/plan_replay.cu) over the exported directory: launched step by step and replayed from the
+    CUDA graph it captures, it must produce the bytes the Python runner produces (they call the same entry points with the same
+    arguments), for every bucket; a missing binding is refused before anything is launched."""
+    from tilefish_b200 import TilefishPreconditionError, runtime
+    from tilefish_b200.native_plan import NativePlan
+
+    _, _, block = declare(fmt)
+    name = fmt.format_name
+    exp = runtime.export(block, str(tmp_path / "native"))
+    plan = NativePlan(exp.directory, pin=exp.digest)
+    assert plan.digest == exp.digest
+    for m in (1, 32, 512):
+        x, res, w_n, w_gu, w_d = inputs(m, seed=m)
+        q_gu, q_d = tilefish.quantize(w_gu.cuda(), name), tilefish.quantize(w_d.cuda(), name)
+        res_py = res.cuda()
+        y_py = tilefish.run(block, x.cuda(), res_py, w_n.cuda(), q_gu, q_d, mode="replay", plan=exp.directory, pin=exp.digest)
+        xg, res_n, wn = x.cuda(), res.cuda(), w_n.cuda()
+        out = torch.empty((m, 2560), dtype=torch.bfloat16, device="cuda")
+        bucket = plan.find_bucket(M=m)
+        if m == 1:
+            plan.bind(x=xg, residual=res_n, w_n=wn, w_gu=q_gu, w_d=q_d)
+            before = res_n.clone()
+            with pytest.raises(TilefishPreconditionError, match="no tensor is bound to buffer 'out0'"):
+                plan.launch(bucket)
+            torch.cuda.synchronize()
+            assert torch.equal(res_n, before), "a refused launch must not have run a step"
+        plan.bind(x=xg, residual=res_n, w_n=wn, w_gu=q_gu, w_d=q_d, out0=out)
+        plan.launch(bucket)
+        torch.cuda.synchronize()
+        assert torch.equal(out, y_py) and torch.equal(res_n, res_py)
+        g = plan.capture(bucket)
+        res_n.copy_(res.cuda())
+        out.zero_()
+        plan.replay(g)
+        torch.cuda.synchronize()
+        assert torch.equal(out, y_py) and torch.equal(res_n, res_py)
+    plan.close()

@@ -462,7 +462,7 @@ def test_runner_drives_the_backend_through_the_reference_signatures():
             rms = rec.calls[0]
             q, qs = (bufs[n]["offset"] + Recording.ARENA for n in ("t0", "t0__scales"))
             assert rms[2] == () and rms[4] == 77
-            assert rms[3] == [("ptr", 0x1000_0000), ("ptr", 0x2000_0000), ("ptr", 0x3000_0000), ("ptr", None), ("i64", 32), ("i64", 2560), ("f32", 1e-6), ("i32", 0),
+            assert rms[3] == [("ptr", 0x1000_0000), ("ptr", 0x2000_0000), ("ptr", 0x3000_0000), ("ptr", None), ("i64", 32), ("i64", 2560), ("f32", _plan.f32_from_bits(0x358637BD)), ("i32", 0),
                               ("ptr", q), ("ptr", qs), ("i32", 1), ("ptr", None), ("ptr", None)]
             g1 = rec.calls[1]
             spec = g1[1]
@@ -480,3 +480,44 @@ def test_runner_drives_the_backend_through_the_reference_signatures():
             assert rec.calls[3][10].b_global == 0x4200_0000 and rec.calls[3][10].a_global == rec.calls[2][3][-1][1]
     with pytest.raises(tilefish.TilefishRuntimeError, match="not part of this backend"):
         runtime.run(block_graph(mxfp8), mode="reference")
+
+
+def test_native_replay_loop_reads_and_verifies_an_export(tmp_path):
+    """tf_plan_load (csrc/plan_replay.cu) on a directory runtime.export wrote: its own JSON reader, canonical writer and SHA-256 give the
+    digest Python gave; a pin that differs, an edited file and a plan whose manifest was swapped are refused. Needs no GPU."""
+    from tilefish_b200 import _native, _plan
+
+    if not os.path.exists(_native.LIB_PATH):
+        pytest.skip("library not built here")
+    from tilefish_b200.errors import TilefishPreconditionError
+    from tilefish_b200.native_plan import NativePlan
+
+    for fmt in (mxfp8, nvfp4):
+        p = _plan.make_plan(block_graph(fmt), library={"file": "libtilefish_b200.so", "sha256": "0" * 64, "version": "test"})
+        d = str(tmp_path / ("export_" + str(fmt.format_name)))
+        _plan.write_export(d, p)
+        n = NativePlan(d, pin=p.digest)
+        assert n.digest == p.digest and n.arena_bytes == p.doc["arena_bytes"]
+        assert n.find_bucket(M=32) == 1 and n.step_count(1) == len(p.doc["buckets"][1]["steps"])
+        with pytest.raises(TilefishPreconditionError) as e:
+            n.find_bucket(M=7)
+        assert e.value.kind == "bucket"
+        n.close()
+        with pytest.raises(TilefishPreconditionError, match="but the pin is"):
+            NativePlan(d, pin="f" * 64)
+        NativePlan(d, trust_directory=True).close()
+        with pytest.raises(TilefishManifestError, match="trust anchor"):
+            NativePlan(d)
+    path = tmp_path / "export_mxfp8" / "plan.json"
+    good = path.read_text()
+    path.write_text(good.replace('"arena_bytes": ', '"arena_bytes": 1'))
+    with pytest.raises(TilefishPreconditionError, match="was edited"):
+        NativePlan(str(tmp_path / "export_mxfp8"), trust_directory=True)
+    path.write_text(good.replace('"reuse": false', '"reuse": false, "reuse": false'))
+    with pytest.raises(TilefishPreconditionError, match="duplicate key"):
+        NativePlan(str(tmp_path / "export_mxfp8"), trust_directory=True)
+    path.write_text(good)
+    mpath = tmp_path / "export_mxfp8" / "manifest.json"
+    mpath.write_text(mpath.read_text().replace("tf_residual_add_rmsnorm", "tf_silu_gate"))
+    with pytest.raises(TilefishPreconditionError, match="manifest.json does not match its own digest"):
+        NativePlan(str(tmp_path / "export_mxfp8"), trust_directory=True)

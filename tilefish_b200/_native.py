@@ -55,6 +55,17 @@ SIGNATURES = {
     "tf_tp_norm_exchange": (c_int32, [_P, _P, ctypes.c_uint64, c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, _P, _P,
                                       _P, _P, c_float, c_int32, c_int32, _P]),
     "tf_allreduce_bf16": (c_int32, [_P, _P, ctypes.c_uint64, c_int32, c_int32, c_int32, c_int64, c_int64, c_int32, _P]),
+    "tf_plan_load": (c_int32, [c_char_p, c_char_p, ctypes.POINTER(_P)]),
+    "tf_plan_free": (None, [_P]),
+    "tf_plan_digest": (c_char_p, [_P]),
+    "tf_plan_arena_bytes": (c_int64, [_P]),
+    "tf_plan_step_count": (c_int32, [_P, c_int32]),
+    "tf_plan_find_bucket": (c_int32, [_P, ctypes.POINTER(c_char_p), ctypes.POINTER(c_int64), c_int32]),
+    "tf_plan_instantiate": (c_int32, [_P, _P, c_int64]),
+    "tf_plan_bind": (c_int32, [_P, c_char_p, _P]),
+    "tf_plan_launch": (c_int32, [_P, c_int32, _P]),
+    "tf_plan_capture": (c_int32, [_P, c_int32, _P, ctypes.POINTER(c_int32)]),
+    "tf_plan_replay": (c_int32, [_P, c_int32, _P]),
 }
 
 _lib = None

@@ -339,7 +339,7 @@ def make_plan(graph: GraphOp, buckets: Optional[Dict[str, Sequence[int]]] = None
             stem = entry_stem(s, combo, step_dims)
             args = _step_args(s, by_name, env)
             sd: Dict[str, Any] = {"entry": stem, "kind": s.kind, "args": args}
-            entry = {"symbol": s.impl, "params": [a["name"] for a in args], "attrs": {k: v for k, v in sorted(s.attrs.items()) if k != "impl"}}
+            entry = {"symbol": s.impl, "params": [a["name"] for a in args], "attrs": _entry_attrs(s.attrs)}
             if s.kind == "library":
                 sd["workspace"] = "workspace"
                 m, n, k = _gemm_problem(s, by_name, env)
@@ -388,6 +388,28 @@ def _renumber_intermediates(buffers: List[B.Buffer], steps: List[B.Step]) -> Non
             base = _base(v)
             if base in rename:
                 s.args[k] = rename[base] + v[len(base):]
+
+
+def _entry_attrs(attrs: Dict[str, Any]) -> Dict[str, Any]:
+    """A manifest entry's compile-time attributes. The manifest holds no JSON number but integers (so that every reader computes the
+    same canonical text): a float is stored as the bit pattern of its f32, ``eps`` as ``eps_bits``."""
+    import struct
+
+    out: Dict[str, Any] = {}
+    for k, v in sorted(attrs.items()):
+        if k == "impl":
+            continue
+        if isinstance(v, float):
+            out[k + "_bits"] = struct.unpack("<I", struct.pack("<f", v))[0]
+        else:
+            out[k] = v
+    return out
+
+
+def f32_from_bits(bits: int) -> float:
+    import struct
+
+    return struct.unpack("<f", struct.pack("<I", int(bits)))[0]
 
 
 def _base(spec: str) -> str:

@@ -136,6 +136,71 @@ class PeerAllReduce:
                                             float(eps), K.FORMATS[fmt], self.num_ctas, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
                 "tf_tp_norm_exchange")
 
+    # ---- failure detection -----------------------------------------------------------------------------------------------
+    # Every wait of the exchange kernels on a peer is bounded (two seconds). When one runs out (rank skew beyond the limit, a
+    # stalled host, a rank that left), the kernel stores a nonzero error word in the channel's state block and returns; the
+    # word is sticky, so every later call on that channel returns at once with partial sums. The host must therefore look at
+    # the word: ``status()`` / ``check()`` synchronize and read it; ``arm_poll()`` + ``last_error()`` watch it without a
+    # synchronization (an asynchronous copy into pinned host memory after a forward, read before the next one).
+    @staticmethod
+    def describe_error(word: int) -> str:
+        return {0: "healthy", 1: "a grid barrier of the kernel's own CTAs gave up (not all CTAs were resident: leave that many SMs to the kernel)",
+                2: "a peer never arrived within the two-second limit"}.get(int(word), f"unknown error word {word}")
+
+    def arm_poll(self) -> None:
+        """Enqueues, on the current stream, a copy of the channels' error words into pinned host memory. Capturable in a CUDA graph."""
+        import torch
+
+        if getattr(self, "_poll_host", None) is None:
+            self._poll_host = torch.zeros(self.channels, dtype=torch.int64).pin_memory()
+        words = self.state.view(torch.int64).view(self.channels, STATE_BYTES // 8)[:, ERROR_WORD_OFFSET // 8]
+        self._poll_host.copy_(words, non_blocking=True)
+
+    def last_error(self) -> int:
+        """The first nonzero error word the most recent completed ``arm_poll`` copy saw (0 when none, or when none was armed). No
+        synchronization: the word is sticky, so a failure is seen one poll late at worst."""
+        host = getattr(self, "_poll_host", None)
+        if host is None:
+            return 0
+        for w in host.tolist():
+            if w:
+                return int(w)
+        return 0
+
+    def raise_if_failed(self, where: str = "") -> None:
+        w = self.last_error()
+        if w:
+            raise TilefishRuntimeError(f"PeerAllReduce{(' (' + where + ')') if where else ''}: {self.describe_error(w)}; the results since then are partial sums. "
+                                       "Stop, call reset() on every rank (a collective) and redo the step")
+
+    def reset(self) -> None:
+        """Collective: waits for this rank's work, zeroes its state blocks (flags, call counters, error words) and meets the other ranks, so
+        that no rank launches again before every state block is clean."""
+        import torch
+        import torch.distributed as dist
+
+        torch.cuda.synchronize(self.buffer.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)  # no peer is still writing flags into this rank's block
+        self.state.zero_()
+        if getattr(self, "_poll_host", None) is not None:
+            self._poll_host.zero_()
+        torch.cuda.synchronize(self.buffer.device)
+        if self.world > 1:
+            dist.barrier(group=self.group)
+
+    def close(self) -> None:
+        """Drops the symmetric tensors and the rendezvous handles (after this rank's work is done). Call it on every rank before the
+        process group goes away: a rank must not exit while its memory is still bound to the group's multicast object."""
+        import torch
+
+        if getattr(self, "buffer", None) is not None:
+            torch.cuda.synchronize(self.buffer.device)
+        for name in ("_buf_handle", "_state_handle", "buffer", "state", "_poll_host", "_bufs", "_states"):
+            if hasattr(self, name):
+                setattr(self, name, None)
+        self.multicast_ptr = 0
+
     def status(self) -> int:
         """0 when healthy; else the first nonzero error word of the channels (1: a local barrier gave up, 2: a peer never
         arrived). Synchronizes the device."""
@@ -151,7 +216,8 @@ class PeerAllReduce:
     def check(self) -> None:
         s = self.status()
         if s:
-            raise TilefishRuntimeError(f"PeerAllReduce: a bounded wait gave up (error word {s}); the group's state must be rebuilt")
+            raise TilefishRuntimeError(f"PeerAllReduce: {self.describe_error(s)} (error word {s}); the results since then are partial sums. Stop, call "
+                                       "reset() on every rank (a collective) and redo the step")
 
 
 def peer_all_reduce(group, nbytes: int, device, **kw) -> Optional[PeerAllReduce]:
@@ -161,3 +227,43 @@ def peer_all_reduce(group, nbytes: int, device, **kw) -> Optional[PeerAllReduce]
     if group is None or dist.get_world_size(group) < 2:
         return None
     return PeerAllReduce(nbytes, group, device, **kw)
+
+
+# ---- row-sharded quantize / rmsnorm ---------------------------------------------------------------------------------------------
+# Rows are independent in both operators, so each rank of a group works on a contiguous block of rows and nothing is exchanged, with
+# one exception: the nvfp4 global scale is a property of the whole tensor. One 4-byte max all-reduce of the ranks' amax makes every
+# rank quantize with the tensor's scale, and the shard's codes, scale bytes and global scale are then exactly the bytes the single-GPU
+# quantizer produces for those rows. (max commutes with the correctly rounded division by 2688, so the scales themselves are reduced.)
+def quantize_rows_sharded(x_rows, fmt: str, group=None, *, layout: str = "swizzled", stream=None):
+    """BlockScaled quantization of this rank's rows ``x_rows`` (bf16 [M / n, K]) of a tensor whose rows are spread over ``group``.
+    mxfp8 / mxfp4: no communication. nvfp4: the tensor-wide global scale through one 4-byte max all-reduce."""
+    import torch.distributed as dist
+
+    from . import kernels as K
+
+    if fmt != "nvfp4":
+        return K.quantize(x_rows, fmt, layout=layout, stream=stream)
+    gs = K.nvfp4_global_scale(x_rows, stream=stream)
+    if group is not None and dist.get_world_size(group) > 1:
+        dist.all_reduce(gs, op=dist.ReduceOp.MAX, group=group)
+    return K.quantize(x_rows, fmt, layout=layout, global_scale=gs, stream=stream)
+
+
+def residual_add_rmsnorm_rows_sharded(x_rows, residual_rows, w, eps: float = 1e-6, group=None, *, quantize_to=None):
+    """``residual_add_rmsnorm`` on this rank's rows, optionally followed by the quantization of the result with the scales of the WHOLE
+    tensor (nvfp4: the kernel reduces this rank's amax, one 4-byte max all-reduce gives the tensor's). Returns ``out`` or ``(out, q)``."""
+    import torch
+    import torch.distributed as dist
+
+    from . import kernels as K
+
+    if quantize_to is None:
+        return K.residual_add_rmsnorm(x_rows, residual_rows, w, eps)
+    if quantize_to != "nvfp4":
+        return K.residual_add_rmsnorm(x_rows, residual_rows, w, eps, quantize_to=quantize_to)
+    amax = torch.zeros(1, dtype=torch.float32, device=x_rows.device)
+    out = K.residual_add_rmsnorm(x_rows, residual_rows, w, eps, amax_out=amax)
+    if group is not None and dist.get_world_size(group) > 1:
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    return out, K.quantize(out, "nvfp4", amax=amax)
+

@@ -14,7 +14,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = ["capi.cu", "quantize.cu", "rmsnorm.cu", "silu_gate.cu", "gemm_blockscaled.cu", "allreduce.cu"]
+SOURCES = ["capi.cu", "quantize.cu", "rmsnorm.cu", "silu_gate.cu", "gemm_blockscaled.cu", "allreduce.cu", "plan_replay.cu"]
 LIB = os.path.join(HERE, "libtilefish_b200.so")
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo", "--expt-relaxed-constexpr",

@@ -204,14 +204,22 @@ class MlpStack:
     def forward(self, x, residual, rows_local: bool = False):
         """``rows_local`` (scatter_gather and fused_exchange): ``x`` and ``residual`` are THIS RANK'S rows ([M / n, H]) and so is the result: no
         rank ever holds the other ranks' tokens outside the GEMMs, and the job's input and output cross PCIe once in total."""
+        if self._peer is not None:
+            # a bounded wait of an earlier forward gave up: everything since then is partial sums. Seen without a synchronization
+            # (the copy armed at the end of the previous forward); check() is the synchronizing form
+            self._peer.raise_if_failed(f"MlpStack comm={self.comm}")
         if self.comm == "scatter_gather":
             return self._forward_row_sharded(x, residual, rows_local)
         if self.comm == "fused_exchange":
-            return self._forward_fused(x, residual, rows_local)
+            out = self._forward_fused(x, residual, rows_local)
+            self._peer.arm_poll()
+            return out
         if rows_local:
             raise TilefishPreconditionError("rows_local needs comm='scatter_gather' or 'fused_exchange'", kind="argument", arg="rows_local")
         if self.comm == "peer_all_reduce" and self._peer_for(x) is not None:
-            return self._forward_peer(x, residual)
+            out = self._forward_peer(x, residual)
+            self._peer.arm_poll()
+            return out
         if self.chunks <= 1:
             slots = self._amax_slots(0, x.device)
             for w, am in zip(self.layers, slots):
@@ -517,6 +525,31 @@ class MlpStack:
 
     __call__ = forward
 
+    def check(self) -> None:
+        """Synchronizes and raises ``TilefishRuntimeError`` if a bounded wait of this stack's exchange kernels gave up (their waits on
+        the peers are limited to two seconds; after a failure the outputs are partial sums). Recovery: ``reset()`` on every rank."""
+        if self._peer is not None:
+            self._peer.check()
+
+    def reset(self) -> None:
+        """Collective: clears the exchange kernels' state on every rank after a failure (see ``check``)."""
+        if self._peer is not None:
+            self._peer.reset()
+
+    def close(self) -> None:
+        """Releases what the stack holds of the process group: the symmetric buffers and their handles, the side streams and the scratch
+        tensors. Every rank calls it (after dropping the CUDA graphs captured from the stack) before the process group is destroyed or
+        the process exits."""
+        import torch
+
+        torch.cuda.synchronize()
+        if self._peer is not None:
+            self._peer.close()
+        self._peer = None
+        self._streams = None
+        self._scratch = [{} for _ in range(max(1, self.chunks))]
+        self._last_reduce = None
+
     def capture(self, x, residual, rows_local: bool = False):
         """Captures one ``forward(x, residual)`` into a CUDA graph (after one eager warm-up run, which also sets the kernels'
         attributes). ``x`` and ``residual`` are the graph's fixed input buffers: write new inputs into them, then
@@ -529,7 +562,7 @@ class MlpStack:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             out = self.forward(x, residual, rows_local) if rows_local else self.forward(x, residual)
-        return CapturedStack(graph, x, residual, out)
+        return CapturedStack(graph, x, residual, out, self)
 
     def weight_bytes(self) -> int:
         return sum(w.nbytes() for w in self.layers)
@@ -538,9 +571,18 @@ class MlpStack:
 class CapturedStack:
     """A captured ``MlpStack.forward``: ``replay()`` relaunches it over the captured ``x`` / ``residual`` buffers and returns ``out``."""
 
-    def __init__(self, graph, x, residual, out) -> None:
-        self.graph, self.x, self.residual, self.out = graph, x, residual, out
+    def __init__(self, graph, x, residual, out, stack=None) -> None:
+        self.graph, self.x, self.residual, self.out, self.stack = graph, x, residual, out, stack
 
-    def replay(self):
+    def replay(self, check: bool = False):
+        """``check=True``: look (without synchronizing) at the error words the previous replay copied out, and raise if an exchange
+        kernel's bounded wait gave up; ``stack.check()`` is the synchronizing form."""
+        if check and self.stack is not None and self.stack._peer is not None:
+            self.stack._peer.raise_if_failed("captured MlpStack")
         self.graph.replay()
         return self.out
+
+    def release(self) -> None:
+        """Drops the CUDA graph (it holds the captured exchange kernels and, with NCCL modes, the captured collectives)."""
+        self.graph = None
+        self.out = None

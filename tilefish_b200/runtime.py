@@ -466,7 +466,7 @@ class PlanRunner:
             x = bound["x"]
             m, d = x.shape
             qf = attrs.get("q_format")
-            args = [("ptr", ptr("x")), ("ptr", ptr("residual")), ("ptr", ptr("w")), ("ptr", ptr("out")), ("i64", m), ("i64", d), ("f32", float(attrs["eps"])),
+            args = [("ptr", ptr("x")), ("ptr", ptr("residual")), ("ptr", ptr("w")), ("ptr", ptr("out")), ("i64", m), ("i64", d), ("f32", P.f32_from_bits(attrs["eps_bits"])),
                     ("i32", FORMAT_IDS[qf] if qf else -1), ("ptr", ptr("q")), ("ptr", ptr("q_scales")), ("i32", SCALES_SWIZZLED), ("ptr", ptr("q_global")),
                     ("ptr", ptr("amax"))]
             return [("launch", (loaded, args))]
