@@ -248,10 +248,6 @@ def extras(torch, K, pk, tensor_peak):
     x = torch.randn((m, k), generator=g, device="cuda")
     x = torch.where(torch.rand((m, k), generator=g, device="cuda") < 0.01, x * 100, x).to(torch.bfloat16)
     gs = K.nvfp4_global_scale(x)
-    copy_dst = torch.empty_like(x)
-    copy_us = graph_us([lambda: copy_dst.copy_(x)] * 5, torch)
-    del copy_dst
-    out["quantize"]["copy_GBps_this_run"] = round(2 * m * k * 2 / copy_us / 1e3, 1)
     for fmt, bpe in BYTES_PER_ELEM.items():
         q = K.quantize(x, fmt, global_scale=gs if fmt == "nvfp4" else None)
         us = graph_us([lambda f=fmt, q=q: K.quantize(x, f, global_scale=gs if f == "nvfp4" else None, out=q)] * 10, torch, flush=flush)

@@ -70,12 +70,14 @@ TF_API const char* tf_last_error(void);
  * SYNCHRONIZES the device. *status is TF_OK or TF_ERR_DEVICE_TIMEOUT; *detail identifies the wait that gave up. */
 TF_API tf_status tf_device_status(int32_t* status, int32_t* detail);
 
-/* Process-wide: the persistent GEMM launches on (SM count - sms) SMs from now on, so that a collective running beside it in
+/* PROCESS-WIDE and not synchronized with calls in flight on other threads (set it while no other thread launches): the persistent GEMM
+ * launches on (SM count - sms) SMs from now on, for every caller in the process, tf_gemm_blockscaled_static included; a CUDA graph keeps
+ * the grid that was in force when it was captured. Purpose: so that a collective running beside it in
  * another stream (the tensor-parallel MLP overlaps one row chunk's all-reduce with the other chunk's GEMMs) finds free SMs.
  * 0 restores the default. No counterpart in the reference (its GEMM is cuBLASLt's `sm_count_target`, python/src/tilefish/_cublaslt.py). */
 TF_API tf_status tf_set_sm_margin(int32_t sms);
 
-/* Programmatic dependent launch for this library's kernels (off by default; process-wide). On: the quantize, rmsnorm, GEMM and
+/* Programmatic dependent launch for this library's kernels (off by default; PROCESS-WIDE, as tf_set_sm_margin). On: the quantize, rmsnorm, GEMM and
  * split-K reduction kernels are launched so that each may be scheduled while the kernel before it on the stream is still
  * draining; each waits (griddepcontrol.wait) for that kernel to complete before its first access to global memory, so results
  * are unchanged. It hides launch latency and kernel set-up in chains of short kernels (small M, decode, many GPUs). No
@@ -171,7 +173,9 @@ TF_API tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, 
  *   - All calls on a device share the one array and it keeps the previous call's contents. Nothing in it has to start at
  *     zero (every partial sum that is read was written by the same call first), but two calls that run at the same time on
  *     one GPU (two streams, two threads) overwrite each other's partial sums: order them on one stream.
- * Arguments as tf_gemm_blockscaled, without the workspace. */
+ *   - The looked-up address is cached per device ordinal for the life of the process: it does not survive a cudaDeviceReset.
+ * Arguments as tf_gemm_blockscaled without workspace / workspace_bytes, and without q_codes, q_scales and a_global_scale_rows (passed
+ * on as NULL / NULL / 0): no fused quantized copy of the output, one global scale for the whole of `a`. */
 TF_API int64_t tf_gemm_static_scratch_bytes(void);
 TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
                                      const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,

@@ -44,13 +44,18 @@ def test_static_scratch_gemm_matches_the_workspace_gemm_twice_in_a_row(fmt_name)
         operands.append((K.quantize(a.cuda(), fmt_name), K.quantize(w.cuda(), fmt_name)))
     expected = [K.gemm_blockscaled(qa, qb) for qa, qb in operands]
     outs = [torch.empty((m, n), dtype=torch.bfloat16, device="cuda") for _ in operands]
+    # one warm-up call: the first call on a device looks the array's address up and sets the kernel's attributes
+    warm = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    assert call_static(N, operands[0][0], operands[0][1], warm, m, n, k, fmt, N.EPI_NONE, stream) == N.TF_OK, N.last_error()
     torch.cuda.synchronize()
     before = torch.cuda.memory_allocated()
+    free_before, _ = torch.cuda.mem_get_info()  # the driver's view: sees a cudaMalloc made inside the library, which torch's allocator cannot
     for (qa, qb), out in zip(operands, outs):  # two calls back to back, nothing allocated in between
         status = call_static(N, qa, qb, out, m, n, k, fmt, N.EPI_NONE, stream)
         assert status == N.TF_OK, N.last_error()
     torch.cuda.synchronize()
     assert torch.cuda.memory_allocated() == before
+    assert torch.cuda.mem_get_info()[0] == free_before, "device memory was allocated (or freed) during the two calls"
     for out, ref in zip(outs, expected):
         assert torch.equal(out, ref), "same kernels, same summation order: the bytes must be identical"
     assert not torch.equal(outs[0], outs[1])

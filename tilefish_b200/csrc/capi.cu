@@ -1,4 +1,5 @@
 // Library identity and the thread-local last error.
+#include <atomic>
 #include <string>
 
 #include "common.cuh"
@@ -32,9 +33,9 @@ int sm_count() {
   return cached;
 }
 
-static int g_programmatic_launch = 0;
-bool programmatic_launch_enabled() { return g_programmatic_launch != 0; }
-void set_programmatic_launch(bool on) { g_programmatic_launch = on ? 1 : 0; }
+static std::atomic<int> g_programmatic_launch{0};  // process-wide (tf_set_programmatic_launch)
+bool programmatic_launch_enabled() { return g_programmatic_launch.load(std::memory_order_relaxed) != 0; }
+void set_programmatic_launch(bool on) { g_programmatic_launch.store(on ? 1 : 0, std::memory_order_relaxed); }
 
 }  // namespace tf
 

@@ -23,6 +23,7 @@
 // descriptor for the MX formats; NVFP4 uses all four bytes per MMA).
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 
 #include "async_copy.cuh"
@@ -1032,9 +1033,9 @@ static tf_status make_operand_map(CUtensorMap* map, const void* base, int64_t ro
 }
 
 // SMs the persistent GEMM leaves free (for a collective running beside it in another stream).
-static int g_sm_margin = 0;
+static std::atomic<int> g_sm_margin{0};  // process-wide (tf_set_sm_margin); atomic so that a concurrent reader sees the old or the new value
 static int gemm_sms() {
-  const int n = sm_count() - g_sm_margin;
+  const int n = sm_count() - g_sm_margin.load(std::memory_order_relaxed);
   return n < 2 ? 2 : n;
 }
 
@@ -1254,7 +1255,7 @@ tf_status tf_device_status(int32_t* status, int32_t* detail) {
 tf_status tf_set_sm_margin(int32_t sms) {
   clear_error();
   TF_CHECK_ARG(sms >= 0 && sms <= 64, "%s: the margin must be in 0..64", __func__);
-  g_sm_margin = sms;
+  g_sm_margin.store(sms, std::memory_order_relaxed);
   return TF_OK;
 }
 

@@ -47,9 +47,19 @@ def _dense(t, name: str) -> None:
 
 
 def _stream(stream) -> int:
+    """The raw handle of ``stream`` (None: torch's current stream). Results and scratch tensors these wrappers allocate come from torch's
+    caching allocator, which orders reuse by torch's CURRENT stream: a launch on another stream must not outlive them unnoticed, so a
+    ``stream=`` that is not the current one is refused unless it is a ``torch.cuda.Stream`` the caller made current
+    (``with torch.cuda.stream(s): ...``) or the caller passes every output and workspace itself."""
+    torch = _torch()
+    current = torch.cuda.current_stream().cuda_stream
     if stream is None:
-        return _torch().cuda.current_stream().cuda_stream
-    return getattr(stream, "cuda_stream", stream)
+        return current
+    handle = getattr(stream, "cuda_stream", stream)
+    if handle != current:
+        raise TilefishPreconditionError("stream= is not torch's current stream: tensors allocated here would be recycled in the current stream's order while the "
+                                        "launch runs on another. Make the stream current (with torch.cuda.stream(s)) and call without stream=", kind="argument", arg="stream")
+    return handle
 
 
 class BlockScaledTensor:
