@@ -60,6 +60,9 @@ def parse_args():
                          "the oracle computes); the switch's own reduction (fewer bytes, but its bf16 sums are one bf16 step off in a fifth of the elements, "
                          "which moves every quantization downstream); or peer loads only")
     ap.add_argument("--chunks", type=int, default=None, help="row chunks whose exchanges overlap the other chunk's GEMMs (default: 2 when N > 1)")
+    ap.add_argument("--pull-partials", action="store_true",
+                    help="fused_exchange: the exchange kernel pulls its rows of the partial results over peer loads, instead of the second GEMM's epilogue "
+                         "delivering them into the summing rank's buffer (the default; same bytes either way)")
     return ap.parse_args()
 
 
@@ -456,8 +459,12 @@ def run_single_kernel(name: str) -> None:
     print(json.dumps({"kernel": name, "launches": 3}))
 
 
+DELIVER_PARTIALS = True  # --pull-partials clears it
+
+
 def make_stack(MLP, blocks, group, world, comm, chunks, ctas, peer_path):
-    return MLP.MlpStack(blocks, group=group, chunks=chunks if world > 1 else 1, comm=comm, sm_margin=ctas, peer_path=peer_path)
+    return MLP.MlpStack(blocks, group=group, chunks=chunks if world > 1 else 1, comm=comm, sm_margin=ctas, peer_path=peer_path,
+                        deliver_partials=DELIVER_PARTIALS)
 
 
 def parity_check(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, peer_path, x_all):
@@ -589,6 +596,9 @@ def row_sharded_quantize_line(torch, K, group, world, rank, dev, pk):
 
 def run_ours(args) -> None:
     import torch
+
+    global DELIVER_PARTIALS
+    DELIVER_PARTIALS = not args.pull_partials
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -754,6 +764,8 @@ def run_ours(args) -> None:
     K.gemm_blockscaled = orig_gemm
     error_word = stack._peer.status() if getattr(stack, "_peer", None) is not None else None
     exchange = ({"kernel": "tp_norm_exchange_kernel" if stack.comm == "fused_exchange" else "allreduce_bf16_kernel", "path": stack._peer.mode, "ctas": stack._peer.num_ctas,
+                 "partials": ("delivered by the second GEMM's epilogue (tf_gemm_blockscaled_scatter)" if getattr(stack, "delivered", False)
+                              else "read from the peers by the exchange kernel"),
                  "error_word": error_word} if getattr(stack, "_peer", None) is not None else None)
     stack_comm, stack_chunks = stack.comm, stack.chunks
     # the timed stack's graph and symmetric memory go before the follow-up measurements build their own

@@ -181,6 +181,22 @@ TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_s
                                      const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
                                      int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* stream);
 
+/* The GEMM with a scattered output: the tensor-parallel second GEMM (w_d split along K) whose epilogue delivers each row block of
+ * its partial result straight to the rank that will sum it, so that no separate kernel has to pull the partial results across
+ * NVLink afterwards. No counterpart in the reference (it has no cross-device exchange).
+ *   out_ptrs[owners]   device addresses valid ON THIS GPU (peer-mapped, or local for this rank's own block): rows
+ *            [i * rows_per_owner, (i + 1) * rows_per_owner) of the result are written to out_ptrs[i] as a bf16 [rows_per_owner, n]
+ *            matrix with row stride ldo, by plain 16-byte stores from the epilogue (no TMA, nothing waits on a peer). The caller
+ *            orders the reads behind the kernel (tf_tp_norm_exchange's first barrier does).
+ *   owners 1..8; rows_per_owner a multiple of 128; m == owners * rows_per_owner
+ * No epilogue operator, no amax, no quantized copy. Shapes that tf_gemm_blockscaled would split along K
+ * (tf_gemm_workspace_bytes > 0: few rows) are refused with TF_ERR_UNSUPPORTED: use tf_gemm_blockscaled and let the consumer pull.
+ * Other arguments as tf_gemm_blockscaled. */
+TF_API tf_status tf_gemm_blockscaled_scatter(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
+                                      const void* b_scales, const float* b_global_scale, const uint64_t* out_ptrs, int32_t owners,
+                                      int64_t rows_per_owner, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
+                                      int64_t a_global_scale_rows, void* stream);
+
 /* In-place bf16 sum all-reduce over the ranks of a tensor-parallel group, one call (one kernel) per rank, each on its own GPU.
  * Replaces the cross-rank sum the reference leaves to the caller's framework; the MLP path's only exchange: partial results of
  * the second GEMM (w_d split along K) summed over the ranks.
@@ -198,8 +214,10 @@ TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_s
  *   num_ctas   CTAs of the kernel (1..148); they must all be resident at once, so leave that many SMs to it when other
  *            kernels run beside it (tf_set_sm_margin)
  * Every rank must make the same sequence of calls on a state block. The
- * waits on the peers are bounded (two seconds): a rank that never arrives makes the kernel return with a nonzero error word
- * (the 64-bit word at byte 88 of the state block; the state blocks must then be zeroed again on all ranks). */
+ * waits on the peers are bounded (two seconds, or the number of nanoseconds the host stored in the 64-bit word at byte 96 of this
+ * rank's state block): a rank that never arrives makes the kernel return with a nonzero error word (the 64-bit word at byte 88 of
+ * the state block: 1 = this rank's own CTAs never all met, 2 = a peer never arrived; the state blocks must then be zeroed again on
+ * all ranks). */
 TF_API tf_status tf_allreduce_bf16(const uint64_t* buffer_ptrs, const uint64_t* state_ptrs, uint64_t multicast_ptr, int32_t reduce_in_switch,
                                    int32_t rank, int32_t world, int64_t offset_bytes, int64_t count, int32_t num_ctas, void* stream);
 
@@ -216,7 +234,11 @@ TF_API tf_status tf_allreduce_bf16(const uint64_t* buffer_ptrs, const uint64_t* 
  *   codes_offset, scales_offset, gs_offset   byte offsets of the outputs: codes [rows_total, d] (e4m3) or [rows_total, d/2]
  *            (e2m1), swizzled scales of a [rows_total, d] tensor, f32 [world] global scales (nvfp4; 16-byte aligned)
  *   rows_total (a multiple of 128 * world), d (a multiple of 128)
- *   sum_peers   0: the partial region already holds complete values on this rank (the input of the first block)
+ *   sum_peers   0: the partial region already holds complete values on this rank (the input of the first block).
+ *            1: every rank's buffer holds that rank's partial results for all rows; this rank pulls its rows from all of them.
+ *            2: this rank's OWN buffer holds every rank's partial results for this rank's rows, delivered there by
+ *            tf_gemm_blockscaled_scatter: source rank s at rows [s * rows_total / world, ...) of the partial region. The sum
+ *            reads local memory only (same order, same bytes as 1); not with reduce_in_switch.
  *   residual_rows   this rank's rows [rank * rows_total / world, ...) of the residual stream, f32, updated in place
  *   w bf16 [d]; h_scratch bf16 [rows_total / world, d] (scratch); amax one zeroed f32 (nvfp4) */
 TF_API tf_status tf_tp_norm_exchange(const uint64_t* buffer_ptrs, const uint64_t* state_ptrs, uint64_t multicast_ptr, int32_t reduce_in_switch,

@@ -309,3 +309,36 @@ def test_vendor_blockscaled_gemm_reads_the_same_swizzled_operands(fmt, m, n, k):
     bound = 2.0**-8 * float(ref.abs().max()) * 1.01
     assert float((mine.cpu().float() - ref).abs().max()) <= bound
     assert float((theirs.cpu() - ref).abs().max()) <= bound
+
+
+@pytest.mark.parametrize("fmt", ["mxfp8", "nvfp4"])
+@pytest.mark.parametrize("owners,rows_per_owner,n,k", [(2, 128, 512, 512), (4, 256, 1024, 1024), (8, 128, 256, 2048)])
+def test_scattered_output_holds_the_rows_of_the_plain_gemm(K, fmt, owners, rows_per_owner, n, k):
+    """tf_gemm_blockscaled_scatter writes row block i to its own destination (here: separate local buffers with a padded row
+    stride): every destination must hold exactly the bytes of those rows of the ordinary GEMM, and nothing beside them."""
+    m = owners * rows_per_owner
+    a, w = operands(m, n, k, seed=owners + n)
+    qa, qb = K.quantize(a.cuda(), fmt), K.quantize(w.cuda(), fmt)
+    plain = K.gemm_blockscaled(qa, qb)
+    ldo = n + 64
+    dests = [torch.full((rows_per_owner, ldo), -7.0, dtype=torch.bfloat16, device="cuda") for _ in range(owners)]
+    K.gemm_blockscaled_scatter(qa, qb, [d.data_ptr() for d in dests], rows_per_owner, ldo)
+    torch.cuda.synchronize()
+    for i, d in enumerate(dests):
+        assert torch.equal(d[:, :n], plain[i * rows_per_owner:(i + 1) * rows_per_owner]), f"row block {i}"
+        assert bool((d[:, n:] == -7.0).all()), f"row block {i}: bytes beyond n were written"
+
+
+def test_scattered_output_refuses_what_it_cannot_do(K):
+    from tilefish_b200.errors import TilefishPreconditionError
+
+    a, w = operands(128, 256, 8192, seed=1)
+    qa, qb = K.quantize(a.cuda(), "mxfp8"), K.quantize(w.cuda(), "mxfp8")
+    d = torch.empty((128, 256), dtype=torch.bfloat16, device="cuda")
+    if K.gemm_workspace_bytes(128, 256, 8192, "mxfp8") > 0:  # split along K: no scattered output
+        with pytest.raises(TilefishPreconditionError):
+            K.gemm_blockscaled_scatter(qa, qb, [d.data_ptr()], 128, 256)
+    with pytest.raises(TilefishPreconditionError):
+        K.gemm_blockscaled_scatter(qa, qb, [d.data_ptr(), d.data_ptr()], 128, 256)  # m is not owners x rows_per_owner
+    with pytest.raises(TilefishPreconditionError):
+        K.gemm_blockscaled_scatter(qa, qb, [d.data_ptr() + 2], 128, 256)  # unaligned destination

@@ -51,6 +51,7 @@ SIGNATURES = {
     "tf_gemm_blockscaled": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, _P, _P, c_int64, _P, c_int64, _P]),
     "tf_gemm_static_scratch_bytes": (c_int64, []),
     "tf_gemm_blockscaled_static": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, _P]),
+    "tf_gemm_blockscaled_scatter": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int32, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, c_int64, _P]),
     "tf_set_programmatic_launch": (c_int32, [c_int32]),
     "tf_tp_norm_exchange": (c_int32, [_P, _P, ctypes.c_uint64, c_int32, c_int32, c_int32, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32, _P, _P,
                                       _P, _P, c_float, c_int32, c_int32, _P]),

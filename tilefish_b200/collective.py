@@ -17,8 +17,9 @@ from typing import Optional
 from . import _native as N
 from .errors import TilefishPreconditionError, TilefishRuntimeError
 
-STATE_BYTES = 128  # per channel: flag slots, call counter, grid-barrier counters, error word (see csrc/allreduce.cu)
+STATE_BYTES = 128  # per channel: flag slots, call counter, grid-barrier counters, error word, wait limit (see csrc/allreduce.cu)
 ERROR_WORD_OFFSET = 88
+WAIT_LIMIT_OFFSET = 96  # nanoseconds, 0 = the kernels' two-second default
 
 
 class PeerAllReduce:
@@ -79,6 +80,11 @@ class PeerAllReduce:
         self._states = [u64s(*[s + c * STATE_BYTES for s in states]) for c in range(self.channels)]
 
     @property
+    def buffer_ptrs(self):
+        """The address, on this GPU, of every rank's buffer (entry ``rank`` is this rank's own)."""
+        return [int(p) for p in self._bufs]
+
+    @property
     def mode(self) -> str:
         if not self.multicast_ptr:
             return "peer_loads"
@@ -116,7 +122,9 @@ class PeerAllReduce:
                        residual_rows, w, h_scratch, amax, eps: float, fmt: str, channel: int = 0) -> None:
         """``tf_tp_norm_exchange`` on the current stream: this rank sums its rows of the partial results at ``partial_offset`` over
         the ranks, adds them into ``residual_rows`` (f32, its rows of the residual stream), normalises with ``w`` and writes the
-        quantized rows (codes, swizzled scales, nvfp4 global scale) at the given offsets of EVERY rank's buffer."""
+        quantized rows (codes, swizzled scales, nvfp4 global scale) at the given offsets of EVERY rank's buffer.
+        ``sum_peers``: 0 / False (the region holds complete values), 1 / True (pull this rank's rows from every rank's region) or
+        2 (the producers delivered their partial results for this rank's rows into this rank's region, one slot per source rank)."""
         import torch
 
         from . import kernels as K
@@ -131,7 +139,7 @@ class PeerAllReduce:
             raise TilefishPreconditionError("PeerAllReduce.norm_exchange_: residual_rows / h_scratch / w do not match rows_total / world x d", kind="shape",
                                             arg="residual_rows")
         N.check(self.lib.tf_tp_norm_exchange(self._bufs, self._states[channel], ctypes.c_uint64(self.multicast_ptr), int(self.reduce_in_switch), self.rank,
-                                            self.world, partial_offset, codes_offset, scales_offset, gs_offset, rows_total, d, int(bool(sum_peers)),
+                                            self.world, partial_offset, codes_offset, scales_offset, gs_offset, rows_total, d, int(sum_peers),
                                             residual_rows.data_ptr(), w.data_ptr(), h_scratch.data_ptr(), amax.data_ptr() if amax is not None else None,
                                             float(eps), K.FORMATS[fmt], self.num_ctas, ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)),
                 "tf_tp_norm_exchange")
@@ -142,10 +150,22 @@ class PeerAllReduce:
     # word is sticky, so every later call on that channel returns at once with partial sums. The host must therefore look at
     # the word: ``status()`` / ``check()`` synchronize and read it; ``arm_poll()`` + ``last_error()`` watch it without a
     # synchronization (an asynchronous copy into pinned host memory after a forward, read before the next one).
+    def set_wait_limit(self, seconds: float) -> None:
+        """How long a wait of the exchange kernels on a peer (or on this rank's own CTAs) may last before the kernel gives up, for this
+        rank's later calls on every channel; 0 restores the two-second default. Stream-ordered with the calls around it."""
+        import torch
+
+        ns = int(round(float(seconds) * 1e9))
+        if ns < 0:
+            raise TilefishPreconditionError("PeerAllReduce.set_wait_limit: negative limit", kind="argument", arg="seconds")
+        self._wait_limit_ns = ns
+        words = self.state.view(torch.int64).view(self.channels, STATE_BYTES // 8)
+        words[:, WAIT_LIMIT_OFFSET // 8] = ns
+
     @staticmethod
     def describe_error(word: int) -> str:
         return {0: "healthy", 1: "a grid barrier of the kernel's own CTAs gave up (not all CTAs were resident: leave that many SMs to the kernel)",
-                2: "a peer never arrived within the two-second limit"}.get(int(word), f"unknown error word {word}")
+                2: "a peer never arrived within the wait limit (two seconds unless set_wait_limit changed it)"}.get(int(word), f"unknown error word {word}")
 
     def arm_poll(self) -> None:
         """Enqueues, on the current stream, a copy of the channels' error words into pinned host memory. Capturable in a CUDA graph."""
@@ -183,6 +203,8 @@ class PeerAllReduce:
         if self.world > 1:
             dist.barrier(group=self.group)  # no peer is still writing flags into this rank's block
         self.state.zero_()
+        if getattr(self, "_wait_limit_ns", 0):
+            self.set_wait_limit(self._wait_limit_ns * 1e-9)
         if getattr(self, "_poll_host", None) is not None:
             self._poll_host.zero_()
         torch.cuda.synchronize(self.buffer.device)

@@ -106,7 +106,23 @@ struct GemmParams {
   uint8_t* q_scales;
   int a_gs_rows;  // 0: a has one global scale; else a_gs[row / a_gs_rows] (row blocks quantized separately, e.g. gathered from ranks)
   int a_box_bytes;  // bytes one A load brings per stage: 128 bytes x the rows of its box (fewer than 128 rows when M is small)
+  // Scattered output (tf_gemm_blockscaled_scatter): rows [i * scatter_rows, (i + 1) * scatter_rows) go to scatter_out[i], a
+  // [scatter_rows, n] matrix with leading dimension ldo that may live in another GPU's memory (plain stores over NVLink).
+  // scatter_rows is a multiple of 128, so a tile has one destination. 0: everything goes to `out`.
+  int scatter_rows;
+  uint16_t* scatter_out[8];
 };
+
+// The address of output row `row`: in `out`, or in the row block's own destination.
+__device__ __forceinline__ uint16_t* out_row_ptr(const GemmParams& p, int row) {
+  if (p.scatter_rows == 0) return p.out + (int64_t)row * p.ldo;
+  const int owner = row / p.scatter_rows;
+  uint16_t* base = p.scatter_out[0];
+#pragma unroll
+  for (int i = 1; i < 8; ++i)
+    if (i == owner) base = p.scatter_out[i];
+  return base + (int64_t)(row - owner * p.scatter_rows) * p.ldo;
+}
 
 // ---- PTX wrappers ----------------------------------------------------------------------------------------------------------
 // ---- thread-block-cluster helpers (the 2-CTA kernel) ----
@@ -301,7 +317,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
   if (row >= p.m) return;
   if (p.q_codes && col + 32 <= p.n) store_chunk_quantized<FMT>(p, packed, row, col);
   if (!p.out) return;
-  uint16_t* orow = p.out + (int64_t)row * p.ldo + col;
+  uint16_t* orow = out_row_ptr(p, row) + col;
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     if (col + g * 8 + 8 <= p.n) {
@@ -1315,35 +1331,38 @@ tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, 
                              out_amax, nullptr, nullptr, 0, scratch, need > 0 ? kStaticScratchBytes : 0, stream);
 }
 
-tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
-                              const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
-                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales,
-                              int64_t a_global_scale_rows, void* workspace, int64_t workspace_bytes, void* stream_) {
-  clear_error();
+}  // extern "C"
+
+// Both GEMM entry points. `scatter_ptrs` (null for tf_gemm_blockscaled): the destinations of the row blocks, see GemmParams.
+static tf_status gemm_entry(const char* fn, const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
+                            const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
+                            int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales, int64_t a_global_scale_rows,
+                            void* workspace, int64_t workspace_bytes, const uint64_t* scatter_ptrs, int32_t owners, int64_t rows_per_owner,
+                            void* stream_) {
   cudaStream_t stream = (cudaStream_t)stream_;
-  TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", __func__, format);
-  TF_CHECK_ARG(epilogue >= TF_EPI_NONE && epilogue <= TF_EPI_RESIDUAL, "%s: unknown epilogue %d", __func__, epilogue);
-  TF_CHECK_ARG(m >= 0 && n > 0 && k > 0, "%s: bad shape m=%lld n=%lld k=%lld", __func__, (long long)m, (long long)n, (long long)k);
+  TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", fn, format);
+  TF_CHECK_ARG(epilogue >= TF_EPI_NONE && epilogue <= TF_EPI_RESIDUAL, "%s: unknown epilogue %d", fn, epilogue);
+  TF_CHECK_ARG(m >= 0 && n > 0 && k > 0, "%s: bad shape m=%lld n=%lld k=%lld", fn, (long long)m, (long long)n, (long long)k);
   if (m == 0) return TF_OK;
-  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && (out || q_codes), "%s: null pointer", __func__);
-  TF_CHECK_ARG((q_codes == nullptr) == (q_scales == nullptr), "%s: q_codes and q_scales go together", __func__);
+  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && (out || q_codes), "%s: null pointer", fn);
+  TF_CHECK_ARG((q_codes == nullptr) == (q_scales == nullptr), "%s: q_codes and q_scales go together", fn);
   if (q_codes) {
     if (format == TF_FMT_NVFP4)
-      return fail(TF_ERR_UNSUPPORTED, "%s: a quantized output needs the tensor's global scale first; nvfp4 outputs are quantized by tf_quantize_nvfp4_from_amax", __func__);
-    if (epilogue == TF_EPI_RESIDUAL) return fail(TF_ERR_UNSUPPORTED, "%s: the residual epilogue has no quantized output", __func__);
-    if (n % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: a quantized output needs n %% 32 == 0", __func__);
+      return fail(TF_ERR_UNSUPPORTED, "%s: a quantized output needs the tensor's global scale first; nvfp4 outputs are quantized by tf_quantize_nvfp4_from_amax", fn);
+    if (epilogue == TF_EPI_RESIDUAL) return fail(TF_ERR_UNSUPPORTED, "%s: the residual epilogue has no quantized output", fn);
+    if (n % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: a quantized output needs n %% 32 == 0", fn);
     TF_CHECK_ALIGNED(q_codes, 16, "q_codes");
     const int64_t cols = n / 32;
     if ((m & 127) || (cols & 3)) TF_CUDA(cudaMemsetAsync(q_scales, 0, (size_t)tf_scale_bytes(format, m, n, TF_SCALES_SWIZZLED), stream));
   }
-  TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || out, "%s: the residual epilogue needs out", __func__);
-  TF_CHECK_ARG(a_global_scale_rows >= 0 && a_global_scale_rows % 128 == 0, "%s: a_global_scale_rows must be 0 or a multiple of 128", __func__);
-  TF_CHECK_ARG(format != TF_FMT_NVFP4 || (a_global_scale && b_global_scale), "%s: nvfp4 needs both global scales", __func__);
-  TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || epilogue_arg, "%s: the residual epilogue needs its f32 residual", __func__);
-  if (k % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: k=%lld is not a multiple of 32", __func__, (long long)k);
-  if (n % 8 != 0 || ldo % 8 != 0 || ldo < n) return fail(TF_ERR_ALIGNMENT, "%s: n and ldo must be multiples of 8 with ldo >= n", __func__);
-  if (epilogue == TF_EPI_SILU_GATE && n % 128 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: the SiLU-gate epilogue needs n %% 128 == 0", __func__);
-  if (m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return fail(TF_ERR_UNSUPPORTED, "%s: a dimension exceeds 2^30", __func__);
+  TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || out, "%s: the residual epilogue needs out", fn);
+  TF_CHECK_ARG(a_global_scale_rows >= 0 && a_global_scale_rows % 128 == 0, "%s: a_global_scale_rows must be 0 or a multiple of 128", fn);
+  TF_CHECK_ARG(format != TF_FMT_NVFP4 || (a_global_scale && b_global_scale), "%s: nvfp4 needs both global scales", fn);
+  TF_CHECK_ARG(epilogue != TF_EPI_RESIDUAL || epilogue_arg, "%s: the residual epilogue needs its f32 residual", fn);
+  if (k % 32 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: k=%lld is not a multiple of 32", fn, (long long)k);
+  if (n % 8 != 0 || ldo % 8 != 0 || ldo < n) return fail(TF_ERR_ALIGNMENT, "%s: n and ldo must be multiples of 8 with ldo >= n", fn);
+  if (epilogue == TF_EPI_SILU_GATE && n % 128 != 0) return fail(TF_ERR_UNSUPPORTED, "%s: the SiLU-gate epilogue needs n %% 128 == 0", fn);
+  if (m > (1 << 30) || n > (1 << 30) || k > (1 << 30)) return fail(TF_ERR_UNSUPPORTED, "%s: a dimension exceeds 2^30", fn);
   TF_CHECK_ALIGNED(a_codes, 16, "a_codes");
   TF_CHECK_ALIGNED(b_codes, 16, "b_codes");
   TF_CHECK_ALIGNED(a_scales, 16, "a_scales");
@@ -1387,14 +1406,22 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
   p.q_scales = static_cast<uint8_t*>(q_scales);
   p.a_gs_rows = (int)a_global_scale_rows;
   p.a_box_bytes = a_box_rows * kStageKBytes;
+  p.scatter_rows = 0;
+  for (int i = 0; i < 8; ++i) p.scatter_out[i] = nullptr;
   const SplitPlan sp = split_plan(m, n, k_bytes, epilogue);
+  if (scatter_ptrs) {
+    if (sp.splits > 1)
+      return fail(TF_ERR_UNSUPPORTED, "%s: this shape is split along K (tf_gemm_workspace_bytes > 0), which has no scattered output", fn);
+    p.scatter_rows = (int)rows_per_owner;
+    for (int i = 0; i < owners; ++i) p.scatter_out[i] = reinterpret_cast<uint16_t*>(scatter_ptrs[i]);
+  }
   p.splits = sp.splits;
   p.k_stages_per_split = sp.k_stages_per_split;
   p.ws = static_cast<float*>(workspace);
   if (sp.splits > 1) {
     const int64_t need = (int64_t)sp.splits * m * n_rows_b * 4;
     if (!workspace || workspace_bytes < need)
-      return fail(TF_ERR_WORKSPACE, "%s: this problem is split %d ways along K and needs a %lld-byte workspace (tf_gemm_workspace_bytes)", __func__,
+      return fail(TF_ERR_WORKSPACE, "%s: this problem is split %d ways along K and needs a %lld-byte workspace (tf_gemm_workspace_bytes)", fn,
                   sp.splits, (long long)need);
     TF_CHECK_ALIGNED(workspace, 256, "workspace");
   }
@@ -1403,6 +1430,32 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
     case TF_FMT_MXFP4: return dispatch_gemm<TF_FMT_MXFP4>(ta, tb, p, epilogue, sp, stream);
     default: return dispatch_gemm<TF_FMT_NVFP4>(ta, tb, p, epilogue, sp, stream);
   }
+}
+
+extern "C" {
+
+tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
+                              const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
+                              int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales,
+                              int64_t a_global_scale_rows, void* workspace, int64_t workspace_bytes, void* stream) {
+  clear_error();
+  return gemm_entry(__func__, a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, out, ldo, m, n, k, format, epilogue, epilogue_arg,
+                    out_amax, q_codes, q_scales, a_global_scale_rows, workspace, workspace_bytes, nullptr, 0, 0, stream);
+}
+
+tf_status tf_gemm_blockscaled_scatter(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
+                                      const float* b_global_scale, const uint64_t* out_ptrs, int32_t owners, int64_t rows_per_owner, int64_t ldo,
+                                      int64_t m, int64_t n, int64_t k, int32_t format, int64_t a_global_scale_rows, void* stream) {
+  clear_error();
+  TF_CHECK_ARG(out_ptrs != nullptr, "%s: null pointer", __func__);
+  TF_CHECK_ARG(owners >= 1 && owners <= 8, "%s: owners must be in 1..8", __func__);
+  TF_CHECK_ARG(rows_per_owner > 0 && rows_per_owner % 128 == 0 && rows_per_owner <= (1 << 24), "%s: rows_per_owner must be a positive multiple of 128",
+               __func__);
+  TF_CHECK_ARG(m == (int64_t)owners * rows_per_owner, "%s: m=%lld is not owners x rows_per_owner", __func__, (long long)m);
+  for (int i = 0; i < owners; ++i)
+    if (!out_ptrs[i] || out_ptrs[i] % 16) return fail(TF_ERR_ALIGNMENT, "%s: destination %d is null or not 16-byte aligned", __func__, i);
+  return gemm_entry(__func__, a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, reinterpret_cast<void*>(out_ptrs[0]), ldo, m, n, k,
+                    format, TF_EPI_NONE, nullptr, nullptr, nullptr, nullptr, a_global_scale_rows, nullptr, 0, out_ptrs, owners, rows_per_owner, stream);
 }
 
 }  // extern "C"

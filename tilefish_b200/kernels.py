@@ -8,6 +8,7 @@ reference checks a launch (python/src/tilefish/_launch.py:263-315, :433-500); fa
 
 from __future__ import annotations
 
+import ctypes
 from typing import Optional
 
 from . import _native as N
@@ -372,6 +373,39 @@ def gemm_blockscaled(a: BlockScaledTensor, b: BlockScaledTensor, *, epilogue: st
         "tf_gemm_blockscaled",
     )
     return (out, q) if quantize_out else out
+
+
+def gemm_blockscaled_scatter(a: BlockScaledTensor, b: BlockScaledTensor, out_ptrs, rows_per_owner: int, ldo: int, *, stream=None) -> None:
+    """``deq(a) @ deq(b)^T`` whose row block i (``rows_per_owner`` rows) is written, as bf16 with row stride ``ldo``, to the device
+    address ``out_ptrs[i]``: this GPU's memory or a peer's (plain stores from the epilogue). The tensor-parallel second GEMM uses
+    it to deliver each rank's rows of its partial result to that rank. Shapes the GEMM would split along K are refused
+    (``gemm_workspace_bytes(...) > 0``)."""
+    torch = _torch()
+    _pre(isinstance(a, BlockScaledTensor) and isinstance(b, BlockScaledTensor), "a and b must be BlockScaledTensor", "dtype")
+    _pre(a.fmt == b.fmt, f"a is {a.fmt} but b is {b.fmt}: block-scaled formats must match exactly", "dtype", "b")
+    _pre(a.layout == "swizzled" and b.layout == "swizzled", "the GEMM consumes swizzled scales", "contiguous")
+    m, k = a.shape
+    n, kb = b.shape
+    _pre(k == kb, f"K differs: a is {a.shape}, b is {b.shape}", "shape", "b")
+    owners = len(out_ptrs)
+    _pre(1 <= owners <= 8 and rows_per_owner > 0 and rows_per_owner % 128 == 0 and m == owners * rows_per_owner,
+         f"M={m} must be {owners} destinations x rows_per_owner={rows_per_owner} (a multiple of 128)", "divisible", "out_ptrs")
+    _pre(ldo >= n and ldo % 8 == 0 and n % 8 == 0, "n and ldo must be multiples of 8 with ldo >= n", "alignment", "ldo")
+    _pre(all(int(p) and int(p) % 16 == 0 for p in out_ptrs), "every destination must be a 16-byte aligned device address", "alignment", "out_ptrs")
+    _pre(gemm_workspace_bytes(m, n, k, a.fmt, "none") == 0, "this shape is split along K: it has no scattered output", "shape", "a")
+    for t, nm in ((a.codes, "a.codes"), (b.codes, "b.codes"), (a.scales, "a.scales"), (b.scales, "b.scales")):
+        _check(t, nm, torch.uint8, None, a.device)
+        _dense(t, nm)
+    if a.fmt == "nvfp4":
+        _pre(a.global_scale is not None and b.global_scale is not None, "nvfp4 operands need their global scales", "argument")
+    ptrs = (ctypes.c_uint64 * owners)(*[int(p) for p in out_ptrs])
+    N.check(
+        N.load().tf_gemm_blockscaled_scatter(
+            a.codes.data_ptr(), a.scales.data_ptr(), a.global_scale.data_ptr() if a.global_scale is not None else None,
+            b.codes.data_ptr(), b.scales.data_ptr(), b.global_scale.data_ptr() if b.global_scale is not None else None,
+            ptrs, owners, rows_per_owner, ldo, m, n, k, FORMATS[a.fmt], a.gs_rows, _stream(stream)),
+        "tf_gemm_blockscaled_scatter",
+    )
 
 
 def gemm(a, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, a_global_scale=None, a_amax=None, amax_out=None,

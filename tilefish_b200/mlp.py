@@ -164,14 +164,19 @@ class MlpStack:
     """
 
     def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16,
-                 comm: str = "all_reduce", peer_path: str = "multicast_store") -> None:
+                 comm: str = "all_reduce", peer_path: str = "multicast_store", deliver_partials: bool = True) -> None:
         """``comm``: "all_reduce" (one NCCL bf16 all-reduce per block), "peer_all_reduce" (the same exchange by this package's
         own kernel over symmetric memory, see ``collective.PeerAllReduce``; ``sm_margin`` is also its CTA count) or
         "scatter_gather" (rows of the normalisation sharded over the ranks: reduce-scatter of the partial results +
         all-gather of the quantized activations; see ``decoder_block_row_sharded``) or "fused_exchange" (the same row-sharded
         scheme as ONE kernel of this package per block: sum of the partial results, residual add, rmsnorm, quantization and the
-        gather of the quantized rows, ``tf_tp_norm_exchange``; ``sm_margin`` is its CTA count)."""
+        gather of the quantized rows, ``tf_tp_norm_exchange``; ``sm_margin`` is its CTA count). ``deliver_partials``
+        (fused_exchange, exact peer paths): the second GEMM's epilogue stores each rank's rows of the partial result straight into
+        that rank's buffer (``tf_gemm_blockscaled_scatter``), so the exchange kernel sums local memory only; otherwise, and for
+        shapes that GEMM splits along K, the exchange kernel pulls its rows over peer loads. Same sums, same bytes."""
         self.layers = layers
+        self.deliver_partials = bool(deliver_partials)
+        self.delivered = False
         self.eps = eps
         self.group = group
         self.chunks = chunks if group is not None else 1
@@ -432,13 +437,19 @@ class MlpStack:
                         views[ci]["partial"][rank * r:(rank + 1) * r].copy_(x[ci * r:(ci + 1) * r])
                     else:
                         views[ci]["partial"].copy_(x[ci * rows:(ci + 1) * rows])
+            # the second GEMM delivers its partial results to the ranks that sum them, when it can (one pass, exact sum)
+            f_local = self.layers[0].w_d.shape[1]
+            deliver = (self.deliver_partials and world > 1 and self._peer_path != "switch_reduce"
+                       and K.gemm_workspace_bytes(rows, h, f_local, fmt, "none") == 0)
+            self.delivered = deliver  # what the most recent forward did (tests read it)
+            last = len(self.layers) - 1
             for li, w in enumerate(self.layers):
                 for ci in range(c):
                     v = views[ci]
                     with torch.cuda.stream(streams[ci]):
                         am = slots[ci][li]
                         ordered(lambda: peer.norm_exchange_(partial_offset=v["off"][0], codes_offset=v["off"][1], scales_offset=v["off"][2], gs_offset=v["off"][3],
-                                                            rows_total=rows, d=h, sum_peers=li > 0, residual_rows=v["res"], w=w.w_n,
+                                                            rows_total=rows, d=h, sum_peers=0 if li == 0 else (2 if deliver else 1), residual_rows=v["res"], w=w.w_n,
                                                             h_scratch=self._scratch[ci][key], amax=am[0:1] if am is not None else None, eps=self.eps,
                                                             fmt=fmt, channel=ci))
                         hq = K.BlockScaledTensor(fmt, (rows, h), v["codes"], v["scales"], v["gs"], "swizzled", gs_rows=r if fmt == "nvfp4" else 0)
@@ -447,7 +458,11 @@ class MlpStack:
                             aq = K.quantize(a, fmt, amax=am[1:2])
                         else:
                             _, aq = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", quantize_out=True, want_bf16=False)
-                        K.gemm_blockscaled(aq, w.w_d, out=v["partial"])
+                        if deliver and li < last:
+                            # rows [o * r, (o + 1) * r) of this rank's partial result go to rank o's region, slot `rank`
+                            K.gemm_blockscaled_scatter(aq, w.w_d, [p + v["off"][0] + rank * r * h * 2 for p in peer.buffer_ptrs], r, h)
+                        else:
+                            K.gemm_blockscaled(aq, w.w_d, out=v["partial"])
             for ci in range(c):
                 v = views[ci]
                 with torch.cuda.stream(streams[ci]):
