@@ -52,8 +52,9 @@ def test_dims():
     assert tilefish.cdiv(K, 32) != tilefish.cdiv(K, 16)
     with pytest.raises(TilefishDeclarationError):
         Dim("X", 4, buckets=[1])
+    assert Dim("X", buckets=[2, 1]).buckets == (1, 2)  # kept sorted, as the reference does
     with pytest.raises(TilefishDeclarationError):
-        Dim("X", buckets=[2, 1])
+        Dim("X", buckets=[2, 2])
 
 
 def test_blockscaled_types():
@@ -107,7 +108,7 @@ def test_rmsnorm_kernel_trace():
 
 def test_call_checker_refusals():
     mxfp4 = BlockScaled(elem=e2m1, scale=ue8m0, block=32)
-    with pytest.raises(TilefishTypeError, match="expected blockscaled"):
+    with pytest.raises(TilefishTypeError, match="expected dtype blockscaled"):
         @tilefish.graph
         def bad(x: Tensor[M, H, bf16], w: Tensor[2 * F, H, mxfp4]):
             return gemm(x, w)

@@ -172,7 +172,7 @@ def bucket_combinations(dims: Dict[str, Sequence[int]]) -> List[Dict[str, int]]:
 
 def _shape_entry(s) -> Any:
     e = as_expr(s)
-    return int(e.const) if e.is_static else str(e)
+    return int(e.offset) if e.is_static else str(e)
 
 
 def _concrete(shape, env: Dict[Dim, int]) -> Tuple[int, ...]:
@@ -202,7 +202,7 @@ def _buffer_docs(graph: GraphOp, buffers: List[B.Buffer], envs: List[Dict[Dim, i
         k = as_expr(b.type.shape[-1])
         if not k.is_static:
             raise TilefishPlanError(f"graph '{graph.name}': the blocked axis of '{b.name}' must be static")
-        codes_shape = [_shape_entry(b.type.shape[0]), int(k.const) // epb]
+        codes_shape = [_shape_entry(b.type.shape[0]), int(k.offset) // epb]
         names = part_names(b.name, b.fmt)
         docs.append({"name": names["codes"], "role": b.role, "dtype": "e4m3" if b.fmt == "mxfp8" else "u8", "shape": codes_shape, "offset": None,
                      "bytes": max(s[0] * (s[1] // epb) for s in shapes)})

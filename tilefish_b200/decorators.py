@@ -78,7 +78,7 @@ def parse_signature(fn, what: str) -> Signature:
                 raise TilefishDeclarationError(f"{what} '{fn.__name__}': const parameter '{name}' needs a dtype (const[f32])")
             params.append(Param(name, None, "in", True, ann.dtype, p.default))
         else:
-            raise TilefishDeclarationError(f"{what} '{fn.__name__}': parameter '{name}' needs a Tensor[...], InOut[...], Out[...] or const[...] annotation")
+            raise TilefishDeclarationError(f"{what} '{fn.__name__}': parameter '{name}' needs an annotation: Tensor[...], InOut[...], Out[...] or const[...]")
     ret = sig.return_annotation
     if ret is inspect.Signature.empty or ret is None:
         returns: Tuple[TensorType, ...] = ()
@@ -92,38 +92,62 @@ def parse_signature(fn, what: str) -> Signature:
 
 
 # ---- call type-checking: unify the callee's dimensions with the arguments' -------------------------------------------
-def _unify(callee: str, pname: str, formal, actual, env: Dict[Dim, Any]) -> None:
+def _require_divisible(callee: str, pname: str, d: Dim, axis: int, a) -> None:
+    """The callee's ``d`` (declared ``divisible_by``) is bound to the caller's size ``a``: proven by the declarations, or a static
+    violation (an error), or, for a symbolic size, a requirement recorded on the graph being traced (once per size and divisor)."""
+    from .ir import Requirement
+    from .trace import active as current_context
+
+    n = d.divisible_by
+    ctx = current_context()
+    known = {r.dim: r.divisor for r in ctx.requirements} if ctx is not None else {}
+    if divisible(a, n, known):
+        return
+    if a.is_static:
+        raise TilefishTypeError(f"{callee}: argument '{pname}': {d} requires divisible_by={n} but dimension {axis} is {a.offset}")
+    if ctx is None:
+        raise TilefishTypeError(f"{callee}: argument '{pname}' binds {d} to {simplify(a)}, which is not provably divisible by {n}")
+    ctx.requirements.append(Requirement(a, n, f"{callee}: argument '{pname}'"))
+
+
+def _unify(callee: str, pname: str, formal, actual, env: Dict[Dim, Any], axis: int = 0, arg_type=None, bound_by: Optional[Dict[Dim, str]] = None) -> None:
+    """Binds the callee's dimensions in ``formal`` to the caller's size ``actual`` (axis ``axis`` of argument ``pname``)."""
+    where = f"{callee}: argument '{pname}'" + (f" ({arg_type!r})" if arg_type is not None else "")
     f = as_expr(formal)
     if f.is_static:
         if as_expr(actual) != f:
-            raise TilefishTypeError(f"{callee}: argument '{pname}' has size {actual} where {formal} is required")
+            need = f"{formal} = {f.offset}" if isinstance(formal, Dim) else str(f.offset)
+            raise TilefishTypeError(f"{where}: dimension {axis} is {actual}, but the signature requires {need}")
         return
-    if f.const == 0 and len(f.terms) == 1 and isinstance(f.terms[0][0], Dim):
+    if f.offset == 0 and len(f.terms) == 1 and isinstance(f.terms[0][0], Dim):
         d, coef = f.terms[0]
         a = as_expr(actual)
         if coef != 1:
-            if not (a.const % coef == 0 and all(c % coef == 0 for _, c in a.terms)):
-                raise TilefishTypeError(f"{callee}: argument '{pname}' has size {actual}, not of the form {formal}")
+            if not (a.offset % coef == 0 and all(c % coef == 0 for _, c in a.terms)):
+                raise TilefishTypeError(f"{where}: dimension {axis} is {actual}, which cannot match {formal}")
             from .dims import DimExpr
 
-            a = DimExpr({k: c // coef for k, c in a.terms}, a.const // coef)
+            a = DimExpr({k: c // coef for k, c in a.terms}, a.offset // coef)
         if d in env:
             if as_expr(env[d]) != a:
-                raise TilefishTypeError(f"{callee}: dimension {d} is {env[d]} for an earlier argument but {simplify(a)} for '{pname}'")
+                by = f" ({d} was bound to {env[d]} by argument '{bound_by[d]}')" if bound_by and d in bound_by else ""
+                raise TilefishTypeError(f"{where}: dimension {axis} is {actual}, but the signature requires {d} = {env[d]}{by}")
         else:
-            if d.divisible_by and not divisible(a, d.divisible_by):
-                raise TilefishTypeError(f"{callee}: argument '{pname}' binds {d} to {simplify(a)}, which is not provably divisible by {d.divisible_by}")
+            if d.divisible_by:
+                _require_divisible(callee, pname, d, axis, a)
             env[d] = actual if coef == 1 else simplify(a)
+            if bound_by is not None:
+                bound_by[d] = pname
         return
     if as_expr(actual) != f:
-        raise TilefishTypeError(f"{callee}: argument '{pname}' has size {actual} where {formal} is required")
+        raise TilefishTypeError(f"{where}: dimension {axis} is {actual}, which cannot match {formal}")
 
 
 def _substitute(x, env: Dict[Dim, Any]):
     if isinstance(x, Dim):
         return env.get(x, x) if not x.is_static else x
     e = as_expr(x)
-    total = as_expr(e.const)
+    total = as_expr(e.offset)
     for a, c in e.terms:
         if isinstance(a, Dim) and a in env:
             total = total + as_expr(env[a]) * c
@@ -145,6 +169,7 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
             raise TilefishTypeError(f"{op.name}: argument '{k}' given twice")
         bound[k] = v
     env: Dict[Dim, Any] = {}
+    bound_by: Dict[Dim, str] = {}
     values = []
     for p in tensors:
         if p.access == "out" and p.name not in bound:
@@ -157,17 +182,22 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
         if v.consumed:
             raise TilefishTypeError(f"{op.name}: argument '{p.name}' ({v.ref}) was consumed by an earlier in-place call and cannot be read again")
         if v.type.rank != p.type.rank:
-            raise TilefishTypeError(f"{op.name}: argument '{p.name}' has rank {v.type.rank}, expected {p.type.rank} ({p.type!r})")
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}': expected rank {p.type.rank} ({p.type!r}), got rank {v.type.rank} ({v.type!r})")
         if not same_format(v.type.dtype, p.type.dtype, p.type.rank):
-            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is {v.type.dtype}, expected {p.type.dtype}")
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}': expected dtype {p.type.dtype}, got {v.type.dtype}")
         if p.type.contiguous and not v.type.contiguous:
             raise TilefishTypeError(f"{op.name}: argument '{p.name}' is a strided view ({v.type!r}); the operator takes a contiguous tensor")
-        for formal, actual in zip(p.type.shape, v.type.shape):
-            _unify(op.name, p.name, formal, actual, env)
+        for axis, (formal, actual) in enumerate(zip(p.type.shape, v.type.shape)):
+            _unify(op.name, p.name, formal, actual, env, axis, v.type, bound_by)
         values.append(v)
     for p in sig.consts:
         if p.name in bound and bound[p.name] != p.default:
             raise TilefishTypeError(f"{op.name}: const '{p.name}' is compiled in as {p.default!r}; a call may restate, not change, it")
+    # writing in place to a read-only input of the graph being traced would change the caller's tensor behind its back
+    for p, v in zip(tensors, values):
+        if p.access == "inout" and getattr(v, "is_param", False) and v.access == "in":
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is written in place but '{v.name}' is a read-only input; declare it InOut[...] "
+                                    "in the graph's signature")
     written = [v for p, v in zip(tensors, values) if p.access != "in"]
     if len({id(v) for v in written}) != len(written) or any(sum(1 for u in values if u is w) > 1 for w in written):
         raise TilefishTypeError(f"{op.name}: a written argument is passed more than once (aliasing)")
@@ -175,8 +205,27 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
     return values, env, rets
 
 
+def _op_by_name(module: str, qualname: str):
+    import importlib
+
+    obj = importlib.import_module(module)
+    for part in qualname.split("."):
+        obj = getattr(obj, part)
+    return obj
+
+
 class Op:
     kind = "op"
+
+    # a declared operator is a module-level object, like a function: copies are the object itself, pickles name it
+    def __copy__(self):
+        return self
+
+    def __deepcopy__(self, memo):
+        return self
+
+    def __reduce__(self):
+        return (_op_by_name, (self.fn.__module__, self.fn.__qualname__))
 
     def __init__(self, fn, name: Optional[str], signature: Signature) -> None:
         self.fn = fn
@@ -302,7 +351,7 @@ def _trace(fn, kind: str, name: str, sig: Signature) -> Tuple[Graph, Tuple[Tenso
                 raise TilefishTypeError(f"{kind} '{name}': the body returns ({', '.join(repr(o.type) for o in outs)}) "
                                         f"but the annotation says ({', '.join(repr(r) for r in sig.returns)})")
         consts = [(p.name, p.const_dtype, p.default) for p in sig.consts]
-        graph = Graph(kind, name, inputs, consts, ctx.nodes, outs, ctx.finals)
+        graph = Graph(kind, name, inputs, consts, ctx.nodes, outs, ctx.finals, tuple(ctx.requirements))
     return graph, tuple(o.type for o in outs)
 
 

@@ -11,7 +11,7 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Optional, Tuple
 
-from .dims import DimLike, cdiv, divisible, simplify
+from .dims import DimLike, as_expr, cdiv, divisible, simplify
 from .errors import TilefishDeclarationError, TilefishTypeError
 
 
@@ -44,6 +44,21 @@ class DType:
     def itemsize(self) -> int:
         return max(1, self.bits // 8)
 
+    @property
+    def storage_bits(self) -> int:
+        """Bits of the unit the type is stored in: a byte for the sub-byte types (two e2m1 per byte), else its own width."""
+        return max(8, self.bits)
+
+    # the dtypes are singletons: copies and pickles give the same object back, so `is` comparisons survive them
+    def __copy__(self) -> "DType":
+        return self
+
+    def __deepcopy__(self, memo) -> "DType":
+        return self
+
+    def __reduce__(self):
+        return (_dtype_by_name, (self.name,))
+
     def can_represent(self, other: "DType") -> bool:
         """Whether every value of ``other`` is a value of this type (a cast from ``other`` is then not a rounding point)."""
         if self is other:
@@ -63,6 +78,10 @@ class DType:
         return self.name
 
     __str__ = __repr__
+
+
+def _dtype_by_name(name: str) -> "DType":
+    return ALL[name]
 
 
 bf16 = DType("bf16", 16, "float", 8, 7)
@@ -97,7 +116,8 @@ class BlockScaled:
         if not isinstance(self.block, int) or self.block <= 0:
             raise TilefishDeclarationError(f"BlockScaled: block must be a positive int, got {self.block!r}")
         if self.block % self.elem.elems_per_byte:
-            raise TilefishDeclarationError(f"BlockScaled: a block of {self.block} {self.elem} elements is not a whole number of bytes")
+            raise TilefishDeclarationError(f"BlockScaled: {self.elem} packs {self.elem.elems_per_byte} elements per byte, so block must be a multiple of "
+                                           f"{self.elem.elems_per_byte}, got {self.block}")
         if self.global_scale is not None and not isinstance(self.global_scale, DType):
             raise TilefishDeclarationError("BlockScaled: global_scale must be a dtype or None")
 
@@ -124,7 +144,9 @@ class BlockScaled:
     def check_shape(self, shape: Tuple[DimLike, ...]) -> None:
         ax = self.normalized(len(shape)).axis
         if not divisible(shape[ax], self.block):
-            raise TilefishTypeError(f"{self}: the blocked axis {shape[ax]} is not provably divisible by the block size {self.block}")
+            size = shape[ax]
+            hint = "" if as_expr(size).is_static else f"; declare the dimension with divisible_by={self.block} (or a multiple of it)"
+            raise TilefishTypeError(f"{self}: axis {ax} has size {size}, which is not divisible by block={self.block}{hint}")
 
     def scale_shape(self, shape: Tuple[DimLike, ...]) -> Tuple[DimLike, ...]:
         self.check_shape(shape)

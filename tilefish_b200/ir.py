@@ -89,6 +89,42 @@ class Node:
     __repr__ = __str__
 
 
+class Requirement:
+    """A precondition on a symbolic size found while type-checking a call: ``dim`` must be a multiple of ``divisor`` because
+    ``origin`` (an operator's argument) declares so. The host that launches the graph checks it against the actual sizes
+    (reference: python/src/tilefish/ir.py:34-50)."""
+
+    __slots__ = ("dim", "divisor", "origin")
+
+    def __init__(self, dim, divisor: int, origin: str) -> None:
+        from .dims import as_expr
+
+        object.__setattr__(self, "dim", as_expr(dim))
+        object.__setattr__(self, "divisor", int(divisor))
+        object.__setattr__(self, "origin", origin)
+
+    def __setattr__(self, key, value):
+        raise AttributeError("Requirement is immutable")
+
+    def __reduce__(self):
+        return (Requirement, (self.dim, self.divisor, self.origin))
+
+    def __eq__(self, o) -> bool:
+        return isinstance(o, Requirement) and (self.dim, self.divisor, self.origin) == (o.dim, o.divisor, o.origin)
+
+    def __hash__(self) -> int:
+        return hash((self.dim, self.divisor, self.origin))
+
+    def __str__(self) -> str:
+        e = self.dim
+        atom = e.offset == 0 and len(e.terms) == 1 and e.terms[0][1] == 1
+        dim = str(e) if atom else f"({e})"  # % binds tighter than +
+        return f"{dim} % {self.divisor} == 0  (required by {self.origin})"
+
+    def __repr__(self) -> str:
+        return f"Requirement({self.dim}, {self.divisor}, {self.origin!r})"
+
+
 class Graph:
     def __init__(self, kind: str, name: str, inputs: List[Value], consts: List[Tuple[str, DType, Any]], nodes: List[Node], outputs: List[Value],
                  finals: Dict[str, Value], requirements: Tuple[Any, ...] = ()) -> None:
@@ -134,4 +170,6 @@ class Graph:
         lines.append("  return" + (" " + ", ".join(o.ref for o in self.outputs) if self.outputs else ""))
         for target, v in self.finals.items():
             lines.append(f"  final {target} = {v.ref}")
+        for r in self.requirements:
+            lines.append(f"  requires {r}")
         return "\n".join(lines)

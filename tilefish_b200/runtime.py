@@ -313,11 +313,11 @@ def _bind_dims(op: Op, tensors: Dict[str, Any]) -> Dict[Dim, int]:
         for formal, actual in zip(p.type.shape, shape):
             e = as_expr(formal)
             if e.is_static:
-                if e.const != actual:
-                    raise TilefishPreconditionError(f"{op.name}: argument '{p.name}' has size {actual} where {formal} = {e.const} is compiled in",
+                if e.offset != actual:
+                    raise TilefishPreconditionError(f"{op.name}: argument '{p.name}' has size {actual} where {formal} = {e.offset} is compiled in",
                                                     kind="static_size", arg=p.name)
                 continue
-            if len(e.terms) == 1 and e.const == 0 and isinstance(e.terms[0][0], Dim):
+            if len(e.terms) == 1 and e.offset == 0 and isinstance(e.terms[0][0], Dim):
                 d, coef = e.terms[0]
                 if actual % coef:
                     raise TilefishPreconditionError(f"{op.name}: argument '{p.name}' has size {actual}, not a multiple of {coef}", kind="shape", arg=p.name)

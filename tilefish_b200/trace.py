@@ -11,7 +11,7 @@ from __future__ import annotations
 
 from typing import Any, Dict, List, Optional, Sequence, Tuple
 
-from .dims import as_expr, simplify
+from .dims import as_expr, divisible, exact_ratio, simplify
 from .dtypes import BlockScaled, DType, f32
 from .errors import TilefishAttributeError, TilefishTypeError
 from .ir import Node, Scalar, Value
@@ -32,6 +32,7 @@ class TraceContext:
         self.finals: Dict[str, Value] = {}
         self.consts: Dict[str, Scalar] = {}
         self.versions: Dict[Value, Value] = {}  # a value an in-place call updated -> the version the call produced
+        self.requirements: List = []  # divisibility of symbolic sizes that calls rely on and the declarations do not prove
 
     def latest(self, v: Value) -> Value:
         """The current version of ``v``: what a later read of a tensor that an in-place call updated refers to."""
@@ -149,16 +150,17 @@ def split(x: Value, size, axis: int = -1) -> Tuple[Value, ...]:
     if not 0 <= ax < rank:
         raise TilefishTypeError(f"split: axis {axis} is out of range for {x.type!r}")
     total, part = as_expr(x.type.shape[ax]), as_expr(size)
-    if not (total.is_static and part.is_static) or part.const <= 0 or total.const % part.const:
-        if not (total.is_static and part.is_static):
-            raise TilefishTypeError(f"split: the axis size {x.type.shape[ax]} and the part size {size} must be static")
-        raise TilefishTypeError(f"split: {x.type.shape[ax]} is not a multiple of {size}")
-    count = total.const // part.const
+    if part.is_static and part.offset <= 0:
+        raise TilefishTypeError(f"split: the part size must be positive, got {size}")
+    # the number of parts must be one integer for every binding of the dimensions: a static quotient, or a constant ratio (2*F into F)
+    count = exact_ratio(total, part)
+    if count is None or count <= 0:
+        raise TilefishTypeError(f"split: {x.type.shape[ax]} is not a whole number of parts of {size}")
     size = simplify(size)
     shape = tuple(size if i == ax else s for i, s in enumerate(x.type.shape))
     if isinstance(x.type.dtype, BlockScaled):
         fmt = x.type.dtype.normalized(rank)
-        if fmt.axis == ax and part.const % fmt.block:
+        if fmt.axis == ax and not divisible(part, fmt.block):
             raise TilefishTypeError(f"split: parts of {size} along the blocked axis are not whole blocks of {fmt.block}")
     leading = all(as_expr(s) == as_expr(1) for s in x.type.shape[:ax])
     t = TensorType(shape, x.type.dtype, contiguous=leading and x.type.contiguous)
@@ -222,9 +224,14 @@ def mean(x: Value, axis=-1, keepdims: bool = False) -> Value:
     return reduce("mean", x, axis, keepdims)
 
 
-def sum(x: Value, axis=-1, keepdims: bool = False) -> Value:  # noqa: A001 - the reference's spelling
+def reduce_sum(x: Value, axis=-1, keepdims: bool = False) -> Value:
     return reduce("sum", x, axis, keepdims)
 
 
-def max(x: Value, axis=-1, keepdims: bool = False) -> Value:  # noqa: A001
+def reduce_max(x: Value, axis=-1, keepdims: bool = False) -> Value:
     return reduce("max", x, axis, keepdims)
+
+
+# the reference's spellings (tilefish.sum / tilefish.max); kept out of `import *` because they would shadow the builtins
+sum = reduce_sum  # noqa: A001
+max = reduce_max  # noqa: A001

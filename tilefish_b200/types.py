@@ -39,6 +39,9 @@ class TensorType:
     def __setattr__(self, key, value):
         raise AttributeError("TensorType is immutable")
 
+    def __reduce__(self):  # copies and pickles are rebuilt through the constructor (the slots cannot be set from outside)
+        return (TensorType, (self.shape, self.dtype, self.contiguous))
+
     @property
     def rank(self) -> int:
         return len(self.shape)
