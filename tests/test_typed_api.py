@@ -522,3 +522,28 @@ def test_native_replay_loop_reads_and_verifies_an_export(tmp_path):
     mpath.write_text(mpath.read_text().replace("tf_residual_add_rmsnorm", "tf_silu_gate"))
     with pytest.raises(TilefishPreconditionError, match="manifest.json does not match its own digest"):
         NativePlan(str(tmp_path / "export_mxfp8"), trust_directory=True)
+
+
+def test_symbolic_divisibility_becomes_a_requirement_on_the_graph():
+    """A callee's divisible_by on a dimension the caller has not constrained is recorded on the traced graph (and printed), once per
+    size, instead of being refused; a static violation stays an error (reference: python/tests/test_calls.py:163-207)."""
+    from tilefish_b200 import Requirement
+
+    Kd = Dim("Kd", divisible_by=32)
+    Nn = Dim("Nn")
+
+    @tilefish.library("gemm_plain", acc=f32)
+    def gemm_plain(a: Tensor[M, Kd, bf16], b: Tensor[Nn, Kd, bf16]) -> Tensor[M, Nn, bf16]: ...
+
+    Kg = Dim("Kg")
+
+    @tilefish.graph
+    def g(x: Tensor[M, Kg, bf16], w: Tensor[256, Kg, bf16], v: Tensor[256, Kg, bf16]):
+        return gemm_plain(x, w), gemm_plain(x, v)
+
+    assert g.graph.requirements == (Requirement(Kg, 32, "gemm_plain: argument 'a'"),)
+    assert "requires Kg % 32 == 0  (required by gemm_plain: argument 'a')" in str(g.graph)
+    with pytest.raises(TilefishTypeError, match=r"Kd requires divisible_by=32 but dimension 1 is 100"):
+        @tilefish.graph
+        def bad(x: Tensor[M, 100, bf16], w: Tensor[256, 100, bf16]):
+            return gemm_plain(x, w)

@@ -30,7 +30,7 @@ from typing import Any, Dict, List, Optional, Sequence, Tuple
 from . import _plan as P
 from . import backend as B
 from .decorators import GraphOp, KernelOp, LibraryOp, Op
-from .dims import Dim, as_expr
+from .dims import Dim, as_expr, evaluate
 from .dtypes import TORCH_NAMES, BlockScaled
 from .errors import TilefishManifestError, TilefishPreconditionError, TilefishRuntimeError
 from .kernels import BlockScaledTensor, quantize  # noqa: F401  (re-exported: the run-time value of a BlockScaled tensor)
@@ -330,6 +330,11 @@ def _bind_dims(op: Op, tensors: Dict[str, Any]) -> Dict[Dim, int]:
                 env[d] = v
             else:
                 raise TilefishPreconditionError(f"{op.name}: size expression {formal} of '{p.name}' cannot be bound from a shape", kind="shape", arg=p.name)
+    # what the calls inside the graph rely on beyond the declarations (recorded while the graph was traced)
+    for req in getattr(getattr(op, "graph", None), "requirements", ()):
+        v = evaluate(req.dim, env)
+        if v is not None and v % req.divisor:
+            raise TilefishPreconditionError(f"{op.name}: {req.dim} = {v} is not divisible by {req.divisor} (required by {req.origin})", kind="divisible", arg=None)
     written = [tensors[p.name] for p in op.signature.tensors if p.access != "in" and p.name in tensors]
     for w in written:
         for p in op.signature.tensors:
