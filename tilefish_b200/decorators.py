@@ -337,19 +337,22 @@ def _trace(fn, kind: str, name: str, sig: Signature) -> Tuple[Graph, Tuple[Tenso
         elif isinstance(result, (tuple, list)) and all(isinstance(r, Value) for r in result):
             outs = list(result)
         else:
-            raise TilefishDeclarationError(f"{kind} '{name}': the body must return traced tensor values, got {type(result).__name__}")
+            raise TilefishTypeError(f"{kind} '{name}': the body must return a traced tensor (or a tuple of them, or nothing), got {type(result).__name__}")
+        for o in outs:
+            if o.is_param and o.access == "out":
+                raise TilefishTypeError(f"{kind} '{name}': cannot return Out parameter '{o.name}': an Out parameter is already a result of the operator")
         for p, v in zip(sig.tensors, inputs):
             if p.access == "out" and p.name not in ctx.finals:
                 raise TilefishDeclarationError(f"{kind} '{name}': Out parameter '{p.name}' is never written")
             if p.access == "inout" and kind == "kernel" and p.name not in ctx.finals:
                 raise TilefishDeclarationError(f"{kind} '{name}': InOut parameter '{p.name}' is never written")
-        for o in outs:
+        if sig.returns and len(sig.returns) != len(outs):
+            raise TilefishTypeError(f"{kind} '{name}': the signature declares {len(sig.returns)} return value(s) but the body returns {len(outs)}")
+        for i, o in enumerate(outs):
+            if sig.returns and sig.returns[i] != o.type:
+                raise TilefishTypeError(f"{kind} '{name}': return value {i} has type {o.type!r} but the declaration says {sig.returns[i]!r}")
             if o.is_param:
                 raise TilefishDeclarationError(f"{kind} '{name}': a parameter cannot be returned as is")
-        if sig.returns:
-            if len(sig.returns) != len(outs) or any(a != o.type for a, o in zip(sig.returns, outs)):
-                raise TilefishTypeError(f"{kind} '{name}': the body returns ({', '.join(repr(o.type) for o in outs)}) "
-                                        f"but the annotation says ({', '.join(repr(r) for r in sig.returns)})")
         consts = [(p.name, p.const_dtype, p.default) for p in sig.consts]
         graph = Graph(kind, name, inputs, consts, ctx.nodes, outs, ctx.finals, tuple(ctx.requirements))
     return graph, tuple(o.type for o in outs)
