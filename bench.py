@@ -60,9 +60,9 @@ def parse_args():
                          "the oracle computes); the switch's own reduction (fewer bytes, but its bf16 sums are one bf16 step off in a fifth of the elements, "
                          "which moves every quantization downstream); or peer loads only")
     ap.add_argument("--chunks", type=int, default=None, help="row chunks whose exchanges overlap the other chunk's GEMMs (default: 2 when N > 1)")
-    ap.add_argument("--pull-partials", action="store_true",
-                    help="fused_exchange: the exchange kernel pulls its rows of the partial results over peer loads, instead of the second GEMM's epilogue "
-                         "delivering them into the summing rank's buffer (the default; same bytes either way)")
+    ap.add_argument("--deliver-partials", action="store_true",
+                    help="fused_exchange: the second GEMM's epilogue delivers each rank's rows of the partial results into that rank's buffer with peer "
+                         "stores, instead of the exchange kernel pulling them with bulk copies (the default; same bytes either way)")
     return ap.parse_args()
 
 
@@ -459,7 +459,7 @@ def run_single_kernel(name: str) -> None:
     print(json.dumps({"kernel": name, "launches": 3}))
 
 
-DELIVER_PARTIALS = True  # --pull-partials clears it
+DELIVER_PARTIALS = False  # --deliver-partials sets it
 
 
 def make_stack(MLP, blocks, group, world, comm, chunks, ctas, peer_path):
@@ -524,11 +524,15 @@ def parity_check(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, pee
 
 def decode_line(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, peer_path, pk):
     """The same stack at M = 64 (decode): weights stream from HBM once per block, so the roofline is this rank's weight bytes over the HBM peak.
-    With N > 1 the exchange needs 128 x N rows per call: the 64 tokens are padded to that many rows (the padding rows are zeros)."""
+    With N > 1 the 64 rows stay replicated and the partial results (1 MiB per block) go through this library's all-reduce kernel on 8 CTAs: the
+    row-sharded exchange of the prefill step needs 128 x N rows per call, which for 64 tokens would be mostly padding. (scatter_gather, the NCCL
+    row-sharded mode, pads.)"""
     import torch.distributed as dist
 
     layers = len(blocks)
-    fused = world > 1 and comm in ("fused_exchange", "scatter_gather")
+    if world > 1 and comm in ("fused_exchange", "peer_all_reduce"):
+        comm, ctas = "peer_all_reduce", 8
+    fused = world > 1 and comm == "scatter_gather"
     rows = 128 * world if fused else M_DECODE
     stack = make_stack(MLP, blocks, group, world, comm, 1, ctas, peer_path)
     x = torch.zeros((rows, H), dtype=torch.bfloat16, device=dev)
@@ -558,7 +562,7 @@ def decode_line(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, peer
     cap.release()
     stack.close()
     us_layer = ms * 1e3 / layers
-    return {"M": M_DECODE, "rows_per_call": rows, "layers_timed": layers, "us_per_layer": round(us_layer, 1), "tokens_per_s": round(M_DECODE / (ms / 1e3) * (layers / LAYERS), 1),
+    return {"M": M_DECODE, "rows_per_call": rows, "exchange": comm if world > 1 else None, "layers_timed": layers, "us_per_layer": round(us_layer, 1), "tokens_per_s": round(M_DECODE / (ms / 1e3) * (layers / LAYERS), 1),
             "weight_stream_GBps_per_gpu": round(wbytes / us_layer / 1e3, 1), "frac_of_hbm_peak": round(wbytes / us_layer / 1e3 / pk["hbm_gbs"], 3),
             "roofline_us_per_layer": round(wbytes / pk["hbm_gbs"] / 1e3, 1),
             "note": "one captured CUDA graph per step, L2 flushed between replays, median of 8, max over ranks; tokens/s is for 32 layers"}
@@ -598,7 +602,7 @@ def run_ours(args) -> None:
     import torch
 
     global DELIVER_PARTIALS
-    DELIVER_PARTIALS = not args.pull_partials
+    DELIVER_PARTIALS = args.deliver_partials
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -637,7 +641,7 @@ def run_ours(args) -> None:
     # block and chunk, switch reduction)
     comm = args.comm or ("fused_exchange" if world > 1 else "all_reduce")
     if args.ar_ctas is None:
-        args.ar_ctas = (24 if world == 2 else 32) if comm == "fused_exchange" else 16
+        args.ar_ctas = (16 if world == 2 else 32) if comm == "fused_exchange" else 16
     stack = make_stack(MLP, blocks, group, world, comm, chunks, args.ar_ctas, args.peer_path)
     torch.cuda.synchronize()
 

@@ -154,17 +154,17 @@ def check_stacks_against_the_oracle(rank, world, dev, expect, report):
                     expect(cr["rel_fro"] <= fro_bound, f"{fmt} {comm} {path} chunks={chunks}: residual stream off the oracle: {cr}")
                     results[(comm, path, chunks)] = (y.clone(), res.clone())
                     if comm == "fused_exchange" and path != "switch_reduce":
-                        # the default delivers GEMM-2's partial results into the summing rank's buffer; pulling them gives the same bytes
-                        expect(stack.delivered and len(shards) > 1, f"{fmt} {path} chunks={chunks}: the partial results were not delivered by the GEMM")
-                        pull = MLP.MlpStack(shards, group=dist.group.WORLD, chunks=chunks, comm=comm, sm_margin=16, peer_path=path, deliver_partials=False)
+                        # GEMM-2 delivering its partial results into the summing rank's buffer gives the same bytes as the exchange kernel pulling them
+                        expect(not stack.delivered, f"{fmt} {path} chunks={chunks}: the default is to pull the partial results")
+                        push = MLP.MlpStack(shards, group=dist.group.WORLD, chunks=chunks, comm=comm, sm_margin=16, peer_path=path, deliver_partials=True)
                         res_p = res0.to(dev)
-                        y_p = pull(x.to(dev), res_p)
+                        y_p = push(x.to(dev), res_p)
                         torch.cuda.synchronize()
-                        pull.check()
-                        expect(not pull.delivered and torch.equal(y_p, y) and torch.equal(res_p, res),
+                        push.check()
+                        expect(push.delivered and len(shards) > 1 and torch.equal(y_p, y) and torch.equal(res_p, res),
                                f"{fmt} {path} chunks={chunks}: delivered and pulled partial results give different bytes")
-                        pull.close()
-                        del pull
+                        push.close()
+                        del push
                     if chunks == 2 and path == "multicast_store":
                         res2 = res0.to(dev)
                         cap = stack.capture(x.to(dev), res2)

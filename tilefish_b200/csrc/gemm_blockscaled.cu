@@ -312,16 +312,26 @@ __device__ __forceinline__ void store_chunk_quantized(const GemmParams& p, const
   p.q_scales[swizzled_scale_offset(row, col >> 5, ((p.n >> 5) + 3) >> 2)] = (uint8_t)scale;
 }
 
+__device__ __forceinline__ void store_256(void* dst, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f, uint32_t g, uint32_t h) {
+  asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(dst), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h) : "memory");
+}
+
 template <int EPI, int FMT>
 __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t (&packed)[16], int row, int col, uint32_t& amax2) {
   if (row >= p.m) return;
   if (p.q_codes && col + 32 <= p.n) store_chunk_quantized<FMT>(p, packed, row, col);
   if (!p.out) return;
   uint16_t* orow = out_row_ptr(p, row) + col;
+  // 32-byte stores (whole L2 sectors, half as many store transactions per row) where the row's chunk is whole and 32-byte aligned
+  const bool wide = col + 32 <= p.n && (reinterpret_cast<uintptr_t>(orow) & 31u) == 0;
+  if (wide) {
+    store_256(orow, packed[0], packed[1], packed[2], packed[3], packed[4], packed[5], packed[6], packed[7]);
+    store_256(orow + 16, packed[8], packed[9], packed[10], packed[11], packed[12], packed[13], packed[14], packed[15]);
+  }
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     if (col + g * 8 + 8 <= p.n) {
-      *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
+      if (!wide) *reinterpret_cast<uint4*>(orow + g * 8) = make_uint4(packed[4 * g], packed[4 * g + 1], packed[4 * g + 2], packed[4 * g + 3]);
       if (p.out_amax) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) amax2 = __vmaxu2(amax2, packed[4 * g + e] & 0x7FFF7FFFu);

@@ -164,7 +164,7 @@ class MlpStack:
     """
 
     def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16,
-                 comm: str = "all_reduce", peer_path: str = "multicast_store", deliver_partials: bool = True) -> None:
+                 comm: str = "all_reduce", peer_path: str = "multicast_store", deliver_partials: bool = False) -> None:
         """``comm``: "all_reduce" (one NCCL bf16 all-reduce per block), "peer_all_reduce" (the same exchange by this package's
         own kernel over symmetric memory, see ``collective.PeerAllReduce``; ``sm_margin`` is also its CTA count) or
         "scatter_gather" (rows of the normalisation sharded over the ranks: reduce-scatter of the partial results +
@@ -172,8 +172,9 @@ class MlpStack:
         scheme as ONE kernel of this package per block: sum of the partial results, residual add, rmsnorm, quantization and the
         gather of the quantized rows, ``tf_tp_norm_exchange``; ``sm_margin`` is its CTA count). ``deliver_partials``
         (fused_exchange, exact peer paths): the second GEMM's epilogue stores each rank's rows of the partial result straight into
-        that rank's buffer (``tf_gemm_blockscaled_scatter``), so the exchange kernel sums local memory only; otherwise, and for
-        shapes that GEMM splits along K, the exchange kernel pulls its rows over peer loads. Same sums, same bytes."""
+        that rank's buffer (``tf_gemm_blockscaled_scatter``), so the exchange kernel sums local memory only; otherwise (the
+        default: measured faster on two GPUs, where the epilogue's 16-byte peer stores slow the GEMM down), and for shapes that
+        GEMM splits along K, the exchange kernel pulls its rows from the peers with bulk copies. Same sums, same bytes."""
         self.layers = layers
         self.deliver_partials = bool(deliver_partials)
         self.delivered = False
