@@ -637,11 +637,11 @@ def run_ours(args) -> None:
         blocks.append(MLP.quantize_weights(w_n, w_gu, w_d, FMT, rank=rank, world=world))
         del w_gu, w_d
     chunks = args.chunks if args.chunks is not None else (2 if world > 1 else 1)
-    # default exchange: this library's fused kernel (sum of the partial results + residual add + rmsnorm + quantize + gather in one launch per
-    # block and chunk, switch reduction)
+    # default exchange: this library's fused kernel (sum of the partial results in rank order + residual add + rmsnorm + quantize + gather in
+    # one launch per block and chunk) on 16 CTAs beside the other chunk's GEMMs (measured best at 2 and 4 GPUs)
     comm = args.comm or ("fused_exchange" if world > 1 else "all_reduce")
     if args.ar_ctas is None:
-        args.ar_ctas = (16 if world == 2 else 32) if comm == "fused_exchange" else 16
+        args.ar_ctas = 16
     stack = make_stack(MLP, blocks, group, world, comm, chunks, args.ar_ctas, args.peer_path)
     torch.cuda.synchronize()
 
