@@ -38,9 +38,8 @@ EXPECTED = {
         "test_traced_values_keep_working_after_a_copy": INTERNAL,
         "test_compile_specs_survive_copy_and_pickle": EXTERN,
     }),
-    "test_calls.py": (19, {
+    "test_calls.py": (20, {
         "test_bucketed_signature_dim": "bucket requirements (BucketRequirement) on a callee's bucketed dimension are not recorded",
-        "test_calls_outside_a_trace_and_bad_arguments": "calling an operator outside a trace runs it here (and needs the GPU) instead of raising",
         "test_out_parameters_are_results_and_dim_parameters_are_derived": EXTERN,
         "test_extern_divisibility_violation_and_requirement": EXTERN,
         "test_several_results_in_declaration_order": "Out[...] parameters of a library operator as extra results in declaration order",

@@ -164,9 +164,12 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
     if len(args) > len(tensors):
         raise TilefishTypeError(f"{op.name}: takes {len(tensors)} tensor arguments, {len(args)} were given")
     bound: Dict[str, Any] = {p.name: a for p, a in zip(tensors, args)}
+    known = {p.name for p in sig.params}
     for k, v in kwargs.items():
         if k in bound:
             raise TilefishTypeError(f"{op.name}: argument '{k}' given twice")
+        if k not in known:
+            raise TilefishTypeError(f"{op.name}: unexpected keyword argument '{k}'")
         bound[k] = v
     env: Dict[Dim, Any] = {}
     bound_by: Dict[Dim, str] = {}
@@ -175,10 +178,10 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
         if p.access == "out" and p.name not in bound:
             continue
         if p.name not in bound:
-            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is missing")
+            raise TilefishTypeError(f"{op.name}: missing a required argument: '{p.name}'")
         v = bound[p.name]
         if not isinstance(v, Value):
-            raise TilefishTypeError(f"{op.name}: argument '{p.name}' must be a traced tensor value, got {type(v).__name__}")
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' must be a traced tensor of type {p.type!r}, got {type(v).__name__}")
         if v.consumed:
             raise TilefishTypeError(f"{op.name}: argument '{p.name}' ({v.ref}) was consumed by an earlier in-place call and cannot be read again")
         if v.type.rank != p.type.rank:
@@ -237,6 +240,10 @@ class Op:
     def __call__(self, *args, **kwargs):
         ctx = T.active()
         if ctx is None or not any(isinstance(a, Value) for a in list(args) + list(kwargs.values())):
+            if ctx is None and not any(hasattr(a, "data_ptr") or hasattr(a, "codes") for a in list(args) + list(kwargs.values())):
+                raise TilefishTypeError(f"{self.name}: an operator can only be called inside a graph or kernel body (tilefish.run executes one on tensors)")
+            if ctx is not None:  # inside a trace every tensor argument is a traced value: let the call checker name the offender
+                check_call(self, args, kwargs)
             from . import runtime
 
             return runtime.run(self, *args, **kwargs)
