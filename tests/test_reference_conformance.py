@@ -38,11 +38,10 @@ EXPECTED = {
         "test_traced_values_keep_working_after_a_copy": INTERNAL,
         "test_compile_specs_survive_copy_and_pickle": EXTERN,
     }),
-    "test_calls.py": (20, {
+    "test_calls.py": (21, {
         "test_bucketed_signature_dim": "bucket requirements (BucketRequirement) on a callee's bucketed dimension are not recorded",
         "test_out_parameters_are_results_and_dim_parameters_are_derived": EXTERN,
         "test_extern_divisibility_violation_and_requirement": EXTERN,
-        "test_several_results_in_declaration_order": "Out[...] parameters of a library operator as extra results in declaration order",
         "test_const_arguments_library_vs_extern": EXTERN,
         "test_const_param_passes_through_to_a_call": "a graph's const parameter passed on to a callee's const",
         "test_declaration_errors": "wording of two declaration errors",

@@ -205,6 +205,9 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
     if len({id(v) for v in written}) != len(written) or any(sum(1 for u in values if u is w) > 1 for w in written):
         raise TilefishTypeError(f"{op.name}: a written argument is passed more than once (aliasing)")
     rets = tuple(TensorType(tuple(_substitute(s, env) for s in r.shape), r.dtype, r.contiguous) for r in sig.returns)
+    # an Out parameter the call does not pass is a result of the call: fresh storage, after the declared results, in declaration order
+    rets += tuple(TensorType(tuple(_substitute(s, env) for s in p.type.shape), p.type.dtype, p.type.contiguous)
+                  for p in tensors if p.access == "out" and p.name not in bound)
     return values, env, rets
 
 
