@@ -38,8 +38,7 @@ EXPECTED = {
         "test_traced_values_keep_working_after_a_copy": INTERNAL,
         "test_compile_specs_survive_copy_and_pickle": EXTERN,
     }),
-    "test_calls.py": (21, {
-        "test_bucketed_signature_dim": "bucket requirements (BucketRequirement) on a callee's bucketed dimension are not recorded",
+    "test_calls.py": (22, {
         "test_out_parameters_are_results_and_dim_parameters_are_derived": EXTERN,
         "test_extern_divisibility_violation_and_requirement": EXTERN,
         "test_const_arguments_library_vs_extern": EXTERN,

@@ -22,7 +22,7 @@ from .errors import (  # noqa: F401
 from .decorators import GraphOp, KernelOp, LibraryOp, Op, graph, kernel, library  # noqa: F401,E402
 from .dims import Dim, DimExpr, cdiv  # noqa: F401,E402
 from .dtypes import BlockScaled, DType, bf16, bool_, e2m1, e4m3, e5m2, f16, f32, i32, i64, u8, ue8m0  # noqa: F401,E402
-from .ir import Graph, Node, Requirement, Scalar, Value  # noqa: F401,E402
+from .ir import BucketRequirement, Graph, Node, Requirement, Scalar, Value  # noqa: F401,E402
 from .trace import exp, max, mean, rsqrt, silu, sum  # noqa: F401,E402,A004
 from .types import ConstType, InOut, Marked, Out, Tensor, TensorType, const  # noqa: F401,E402
 
@@ -34,7 +34,7 @@ __version__ = "0.2.0"
 
 # `from tilefish_b200 import *` leaves the reductions out: `sum` and `max` would shadow the builtins (they stay reachable as attributes)
 __all__ = [
-    "BlockScaled", "ConstType", "DType", "Dim", "DimExpr", "Graph", "GraphOp", "InOut", "KernelOp", "LibraryOp", "Marked", "Node", "Op", "Out",
+    "BlockScaled", "BucketRequirement", "ConstType", "DType", "Dim", "DimExpr", "Graph", "GraphOp", "InOut", "KernelOp", "LibraryOp", "Marked", "Node", "Op", "Out",
     "Requirement", "Scalar", "Tensor", "TensorType", "TilefishAttributeError", "TilefishBuildError", "TilefishDeclarationError", "TilefishError",
     "TilefishLoweringError", "TilefishManifestError", "TilefishPlanError", "TilefishPreconditionError", "TilefishRuntimeError", "TilefishSpecError",
     "TilefishTypeError", "Value", "bf16", "bool_", "cdiv", "const", "e2m1", "e4m3", "e5m2", "exp", "f16", "f32", "graph", "i32", "i64", "kernel",

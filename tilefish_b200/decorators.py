@@ -100,7 +100,7 @@ def _require_divisible(callee: str, pname: str, d: Dim, axis: int, a) -> None:
 
     n = d.divisible_by
     ctx = current_context()
-    known = {r.dim: r.divisor for r in ctx.requirements} if ctx is not None else {}
+    known = {r.dim: r.divisor for r in ctx.requirements if hasattr(r, "divisor")} if ctx is not None else {}
     if divisible(a, n, known):
         return
     if a.is_static:
@@ -108,6 +108,31 @@ def _require_divisible(callee: str, pname: str, d: Dim, axis: int, a) -> None:
     if ctx is None:
         raise TilefishTypeError(f"{callee}: argument '{pname}' binds {d} to {simplify(a)}, which is not provably divisible by {n}")
     ctx.requirements.append(Requirement(a, n, f"{callee}: argument '{pname}'"))
+
+
+def _require_bucket(callee: str, pname: str, d: Dim, axis: int, a, actual) -> None:
+    """The callee's bucketed ``d`` is bound to the caller's size: one of the buckets (static), a bucketed dimension whose buckets all
+    are the callee's, or a requirement recorded on the graph; a static miss and disjoint bucket sets are errors."""
+    from .ir import BucketRequirement
+    from .trace import active as current_context
+
+    want = list(d.buckets)
+    if a.is_static:
+        if a.offset not in d.buckets:
+            raise TilefishTypeError(f"{callee}: argument '{pname}': {d} is bucketed over {want} but dimension {axis} is {a.offset}")
+        return
+    have = actual.buckets if isinstance(actual, Dim) else None
+    if have is not None:
+        if set(have) <= set(want):
+            return
+        if not set(have) & set(want):
+            raise TilefishTypeError(f"{callee}: argument '{pname}': {d} is bucketed over {want} but {actual} has buckets {list(have)} (no bucket in common)")
+    ctx = current_context()
+    if ctx is None:
+        raise TilefishTypeError(f"{callee}: argument '{pname}' binds the bucketed {d} to {actual}, which is not known to be one of {want}")
+    req = BucketRequirement(a, want, f"{callee}: argument '{pname}'")
+    if req not in ctx.requirements:
+        ctx.requirements.append(req)
 
 
 def _unify(callee: str, pname: str, formal, actual, env: Dict[Dim, Any], axis: int = 0, arg_type=None, bound_by: Optional[Dict[Dim, str]] = None) -> None:
@@ -135,6 +160,8 @@ def _unify(callee: str, pname: str, formal, actual, env: Dict[Dim, Any], axis: i
         else:
             if d.divisible_by:
                 _require_divisible(callee, pname, d, axis, a)
+            if d.buckets is not None and coef == 1:
+                _require_bucket(callee, pname, d, axis, a, actual)
             env[d] = actual if coef == 1 else simplify(a)
             if bound_by is not None:
                 bound_by[d] = pname

@@ -125,6 +125,38 @@ class Requirement:
         return f"Requirement({self.dim}, {self.divisor}, {self.origin!r})"
 
 
+class BucketRequirement:
+    """A symbolic size must take one of ``buckets`` because ``origin`` (an operator's argument) is declared over those buckets and the
+    caller's declaration does not prove it; checked against the actual sizes by the host (reference: python/src/tilefish/ir.py)."""
+
+    __slots__ = ("dim", "buckets", "origin")
+
+    def __init__(self, dim, buckets, origin: str) -> None:
+        from .dims import as_expr
+
+        object.__setattr__(self, "dim", as_expr(dim))
+        object.__setattr__(self, "buckets", tuple(buckets))
+        object.__setattr__(self, "origin", origin)
+
+    def __setattr__(self, key, value):
+        raise AttributeError("BucketRequirement is immutable")
+
+    def __reduce__(self):
+        return (BucketRequirement, (self.dim, self.buckets, self.origin))
+
+    def __eq__(self, o) -> bool:
+        return isinstance(o, BucketRequirement) and (self.dim, self.buckets, self.origin) == (o.dim, o.buckets, o.origin)
+
+    def __hash__(self) -> int:
+        return hash((self.dim, self.buckets, self.origin))
+
+    def __str__(self) -> str:
+        return f"{self.dim} in {list(self.buckets)}  (required by {self.origin})"
+
+    def __repr__(self) -> str:
+        return f"BucketRequirement({self.dim}, {list(self.buckets)}, {self.origin!r})"
+
+
 class Graph:
     def __init__(self, kind: str, name: str, inputs: List[Value], consts: List[Tuple[str, DType, Any]], nodes: List[Node], outputs: List[Value],
                  finals: Dict[str, Value], requirements: Tuple[Any, ...] = ()) -> None:

@@ -333,7 +333,12 @@ def _bind_dims(op: Op, tensors: Dict[str, Any]) -> Dict[Dim, int]:
     # what the calls inside the graph rely on beyond the declarations (recorded while the graph was traced)
     for req in getattr(getattr(op, "graph", None), "requirements", ()):
         v = evaluate(req.dim, env)
-        if v is not None and v % req.divisor:
+        if v is None:
+            continue
+        if hasattr(req, "buckets"):
+            if v not in req.buckets:
+                raise TilefishPreconditionError(f"{op.name}: {req.dim} = {v} is not one of {list(req.buckets)} (required by {req.origin})", kind="bucket", arg=None)
+        elif v % req.divisor:
             raise TilefishPreconditionError(f"{op.name}: {req.dim} = {v} is not divisible by {req.divisor} (required by {req.origin})", kind="divisible", arg=None)
     written = [tensors[p.name] for p in op.signature.tensors if p.access != "in" and p.name in tensors]
     for w in written:
