@@ -23,7 +23,7 @@ from .decorators import GraphOp, KernelOp, LibraryOp, Op, graph, kernel, library
 from .dims import Dim, DimExpr, cdiv  # noqa: F401,E402
 from .dtypes import BlockScaled, DType, bf16, bool_, e2m1, e4m3, e5m2, f16, f32, i32, i64, u8, ue8m0  # noqa: F401,E402
 from .ir import BucketRequirement, Graph, Node, Requirement, Scalar, Value  # noqa: F401,E402
-from .trace import exp, max, mean, rsqrt, silu, sum  # noqa: F401,E402,A004
+from .trace import contiguous, exp, gelu, max, mean, rsqrt, silu, sqrt, sum  # noqa: F401,E402,A004
 from .types import ConstType, InOut, Marked, Out, Tensor, TensorType, const  # noqa: F401,E402
 
 mxfp8 = BlockScaled(elem=e4m3, scale=ue8m0, block=32, axis=-1)
@@ -37,8 +37,8 @@ __all__ = [
     "BlockScaled", "BucketRequirement", "ConstType", "DType", "Dim", "DimExpr", "Graph", "GraphOp", "InOut", "KernelOp", "LibraryOp", "Marked", "Node", "Op", "Out",
     "Requirement", "Scalar", "Tensor", "TensorType", "TilefishAttributeError", "TilefishBuildError", "TilefishDeclarationError", "TilefishError",
     "TilefishLoweringError", "TilefishManifestError", "TilefishPlanError", "TilefishPreconditionError", "TilefishRuntimeError", "TilefishSpecError",
-    "TilefishTypeError", "Value", "bf16", "bool_", "cdiv", "const", "e2m1", "e4m3", "e5m2", "exp", "f16", "f32", "graph", "i32", "i64", "kernel",
-    "library", "mean", "mxfp4", "mxfp8", "nvfp4", "rsqrt", "silu", "u8", "ue8m0",
+    "TilefishTypeError", "Value", "bf16", "bool_", "cdiv", "const", "contiguous", "e2m1", "e4m3", "e5m2", "exp", "f16", "gelu", "f32", "graph", "i32", "i64", "kernel",
+    "library", "mean", "mxfp4", "mxfp8", "nvfp4", "rsqrt", "silu", "sqrt", "u8", "ue8m0",
 ]
 
 

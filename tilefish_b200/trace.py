@@ -34,6 +34,13 @@ class TraceContext:
         self.versions: Dict[Value, Value] = {}  # a value an in-place call updated -> the version the call produced
         self.requirements: List = []  # divisibility of symbolic sizes that calls rely on and the declarations do not prove
 
+    def new_value(self, type, name: Optional[str] = None, access: str = "in", is_param: bool = False) -> Value:
+        """A value of this trace that no node produced: a parameter (what the decorators create for every tensor argument)."""
+        ref = f"%{name}" if name else f"%{self.counter}"
+        if not name:
+            self.counter += 1
+        return Value(type, ref, self, is_param=is_param, access=access, name=name)
+
     def latest(self, v: Value) -> Value:
         """The current version of ``v``: what a later read of a tensor that an in-place call updated refers to."""
         while v in self.versions:
@@ -60,7 +67,9 @@ class TraceContext:
 
 def _ctx_of(v: Value) -> TraceContext:
     ctx = active()
-    if ctx is None or v._ctx is not ctx:
+    if ctx is None:
+        return v._ctx  # a context driven by hand (TraceContext.new_value): the value knows its trace
+    if v._ctx is not ctx:
         raise TilefishTypeError(f"{v.ref} is used outside the declaration that traced it")
     return ctx
 
@@ -70,10 +79,36 @@ def _require_computable(v: Value, op: str) -> None:
         raise TilefishTypeError(f"{op}: {v.ref} has dtype {v.type.dtype}, which is storage only; cast it first (.to(f32))")
 
 
+class Const:
+    """A ``const`` parameter as a traced body sees it (reference: python/src/tilefish/trace.py:178-203): it combines with tensors; an
+    untyped one (``dtype`` None) adopts the dtype of the tensor it meets, a typed one must match it."""
+
+    __slots__ = ("name", "value", "dtype")
+
+    def __init__(self, name: str, value, dtype) -> None:
+        self.name, self.value, self.dtype = name, value, dtype
+
+    def __repr__(self) -> str:
+        return f"Const({self.name}={self.value!r})"
+
+    def _refuse(self, other):
+        if isinstance(other, Value):
+            return NotImplemented  # the tensor's reflected operator handles it
+        raise TilefishTypeError(f"const parameter '{self.name}' can only be combined with a tensor value, got {type(other).__name__}")
+
+    __add__ = __radd__ = __sub__ = __rsub__ = __mul__ = __rmul__ = __truediv__ = __rtruediv__ = _refuse
+
+
 def _operand(x, like: Value, op: str):
     """A tensor operand as is; a python scalar or const adopts ``like``'s dtype."""
     if isinstance(x, Value):
         return x
+    if isinstance(x, Const):
+        if x.value is None:
+            raise TilefishTypeError(f"{op}: const parameter '{x.name}' has no default value to trace with")
+        if x.dtype is not None and x.dtype is not like.type.dtype:
+            raise TilefishTypeError(f"{op}: const {x.name} is {x.dtype} but the tensor is {like.type.dtype}")
+        return Scalar(x.value, like.type.dtype, x.name)
     if isinstance(x, Scalar):
         if x.dtype is not like.type.dtype:
             raise TilefishTypeError(f"{op}: const {x.name} is {x.dtype} but the tensor is {like.type.dtype}")
@@ -210,6 +245,21 @@ _install()
 # ---- public math ops ----------------------------------------------------------------------------------------------------
 def silu(x: Value) -> Value:
     return unary_f32("silu", x)
+
+
+def sqrt(x: Value) -> Value:
+    return unary_f32("sqrt", x)
+
+
+def gelu(x: Value) -> Value:
+    return unary_f32("gelu", x)
+
+
+def contiguous(x: Value) -> Value:
+    """A dense copy of a strided view (the type's ``contiguous`` flag set); a contiguous tensor is returned as is."""
+    if x.type.contiguous:
+        return x
+    return _ctx_of(x).emit("contiguous", (x,), (TensorType(x.type.shape, x.type.dtype, contiguous=True),))[0]
 
 
 def rsqrt(x: Value) -> Value:
