@@ -611,26 +611,28 @@ __global__ void __launch_bounds__(544, 1) tp_norm_exchange_kernel(const NxParams
       }
     };
     if (rounds == 1) {
-      // rows of up to one piece per thread: two rows per round (in the producer's order), so that a warp's two quantizations interleave
+      // rows of up to one piece per thread: kRows2 rows per round (in the producer's order), so that a warp's quantizations interleave
+      constexpr int kRows2 = 4;
       const bool active = tid - lane < nvec16;  // whole warps only: the quantizer and the scale packing shuffle
-      for (int base = blockIdx.x; base < rows_local; base += gridDim.x * 2) {
-        const int row_b = base + (int)gridDim.x;
-        const bool two = row_b < rows_local;
-        uint32_t wa[8] = {0, 0, 0, 0, 0, 0, 0, 0}, wb[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        bool has_a = false, has_b = false;
-        int s_next = 0;
-        if (active) has_a = fetch(seg, s_next, tid, wa);
-        pass_rest(seg, s_next);
-        seg += (uint32_t)nseg2;
-        if (two) {
-          s_next = 0;
-          if (active) has_b = fetch(seg, s_next, tid, wb);
-          pass_rest(seg, s_next);
-          seg += (uint32_t)nseg2;
+      for (int base = blockIdx.x; base < rows_local; base += gridDim.x * kRows2) {
+        uint32_t wq[kRows2][8];
+        bool has[kRows2];
+#pragma unroll
+        for (int rw = 0; rw < kRows2; ++rw) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) wq[rw][e] = 0;
+          has[rw] = false;
+          if (base + rw * (int)gridDim.x < rows_local) {
+            int s_next = 0;
+            if (active) has[rw] = fetch(seg, s_next, tid, wq[rw]);
+            pass_rest(seg, s_next);
+            seg += (uint32_t)nseg2;
+          }
         }
         if (active) {
-          quantize_store_piece<QFMT>(p, q, wa, has_a, row0 + base, tid, gs, inv_t);
-          if (two) quantize_store_piece<QFMT>(p, q, wb, has_b, row0 + row_b, tid, gs, inv_t);
+#pragma unroll
+          for (int rw = 0; rw < kRows2; ++rw)
+            if (base + rw * (int)gridDim.x < rows_local) quantize_store_piece<QFMT>(p, q, wq[rw], has[rw], row0 + base + rw * (int)gridDim.x, tid, gs, inv_t);
         }
         if (abort_flag) break;  // a warp's own waits return at once after the flag is up; nothing here meets the other warps
       }

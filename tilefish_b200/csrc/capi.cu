@@ -49,7 +49,7 @@ tf_status tf_set_programmatic_launch(int32_t enabled) {
   return TF_OK;
 }
 
-const char* tf_version(void) { return "tilefish_b200 0.1.0 (sm_100a)"; }
+const char* tf_version(void) { return "tilefish_b200 0.2.0 (sm_100a)"; }
 const char* tf_last_error(void) { return g_last_error.c_str(); }
 
 }  // extern "C"
