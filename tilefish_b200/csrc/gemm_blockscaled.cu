@@ -355,11 +355,15 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, const uint32_t 
 }
 
 // Which epilogue warps read chunk `c` (32 accumulator columns): GRP < 0: this warp reads all of them (the CTA-pair kernel has four
-// epilogue warps); GRP 0 / 1: the one-CTA kernel's two groups of four warps share the columns, even chunks to group 0 and odd ones to
-// group 1 (with the SiLU gate: by the gate chunk; its up chunk goes with it).
+// epilogue warps); GRP 0 / 1: the one-CTA kernel's two groups of four warps share the columns, alternating between the groups (with the
+// SiLU gate: by the gate chunk; its up chunk goes with it).
 template <int GRP, int EPI, int BLOCK_N>
 __device__ __forceinline__ constexpr bool chunk_is_mine(int c) {
-  return GRP < 0 || (((EPI == TF_EPI_SILU_GATE) ? (c % (BLOCK_N / 64)) : c) & 1) == GRP;
+  // the unit a group owns is a PAIR of adjacent chunks where there are at least four (a thread then writes 128 contiguous bytes of its
+  // output row, a whole line), else single chunks
+  constexpr int kUnits = (EPI == TF_EPI_SILU_GATE) ? BLOCK_N / 64 : BLOCK_N / 32;
+  const int u = (EPI == TF_EPI_SILU_GATE) ? (c % (BLOCK_N / 64)) : c;
+  return GRP < 0 || ((kUnits >= 4 ? (u >> 1) : u) & 1) == GRP;
 }
 
 // One tile's epilogue for accumulator BUF (compile time, so that the chunks held in registers are indexed statically).
