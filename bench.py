@@ -581,25 +581,39 @@ def row_sharded_quantize_line(torch, K, group, world, rank, dev, pk):
 
     m, k = 65536 // world, 4096
     g = torch.Generator(device=dev).manual_seed(rank)
-    x = torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16)
+    # rotating inputs larger than L2 in total, so that every call reads its rows from HBM
+    n_bufs = max(2, -(-(300 << 20) // (m * k * 2)))
+    xs = [torch.randn((m, k), generator=g, device=dev).to(torch.bfloat16) for _ in range(n_bufs)]
     out = {}
+    calls = 12
     for fmt, bpe in BYTES_PER_ELEM.items():
-        for _ in range(3):
-            quantize_rows_sharded(x, fmt, group)
+        for i in range(3):
+            quantize_rows_sharded(xs[i % n_bufs], fmt, group)
         dist.barrier()
         torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(10):
-            quantize_rows_sharded(x, fmt, group)
-        e.record()
-        e.synchronize()
-        t = torch.tensor([s.elapsed_time(e) / 10], device=dev)
+        graph = torch.cuda.CUDAGraph()  # no host time between the calls (the nvfp4 calls carry their 4-byte all-reduce into the graph)
+        with torch.cuda.graph(graph):
+            for i in range(calls):
+                quantize_rows_sharded(xs[i % n_bufs], fmt, group)
+        graph.replay()
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(3):
+            dist.barrier()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            graph.replay()
+            e.record()
+            e.synchronize()
+            best = min(best, s.elapsed_time(e) / calls)
+        del graph
+        t = torch.tensor([best], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us = float(t.item()) * 1e3
         total_bpe = bpe + (2 if fmt == "nvfp4" else 0)
         out[fmt] = {"us": round(us, 1), "aggregate_GBps": round(65536 * k * total_bpe / us / 1e3, 1), "frac_of_n_x_hbm_peak": round(65536 * k * total_bpe / us / 1e3 / (world * pk["hbm_gbs"]), 3)}
-    out["note"] = f"65536 x 4096 rows split over {world} ranks, eager launches back to back (max over ranks); nvfp4 includes the amax pass and the 4-byte max all-reduce"
+    out["note"] = (f"65536 x 4096 rows split over {world} ranks, {calls} calls over {n_bufs} rotating inputs in one CUDA graph (best of 3 replays, max over ranks); "
+                   "nvfp4 includes the amax pass and the 4-byte max all-reduce")
     return out
 
 
@@ -801,6 +815,22 @@ def run_ours(args) -> None:
     if rank != 0:
         cleanup_ranks(world)
         return
+    # N > 1: the per-launch times of the step include the moments when the two row chunks' GEMMs share the SMs. The same kernel on the same
+    # operands alone, on the SMs the step leaves it (148 - exchange CTAs), 10 launches in one CUDA graph:
+    alone_us = None
+    if world > 1 and stack_chunks > 1:
+        from tilefish_b200 import _native as N_
+
+        xa = torch.randn((m // stack_chunks, H), generator=torch.Generator(device=dev).manual_seed(11), device=dev).to(torch.bfloat16)
+        qa = K.quantize(xa, FMT)
+        out_a = torch.empty((m // stack_chunks, F // world), dtype=torch.bfloat16, device=dev)
+        am = torch.zeros(1, device=dev)
+        N_.check(N_.load().tf_set_sm_margin(args.ar_ctas), "tf_set_sm_margin")
+        try:
+            alone_us = graph_us([lambda: K.gemm_blockscaled(qa, blocks[0].w_gu, epilogue="silu_gate", out=out_a, amax_out=am)] * 10, torch)
+        finally:
+            N_.check(N_.load().tf_set_sm_margin(0), "tf_set_sm_margin")
+        del xa, qa, out_a
     del blocks
     gc.collect()
     torch.cuda.empty_cache()
@@ -818,6 +848,10 @@ def run_ours(args) -> None:
                               else f"4 x sustained bf16 {pk['bf16_tflops_sustained']} TFLOP/s ({pk['source']}): this torch build has no block-scaled library GEMM")
                              + f". Nominal dense FP4 is 9000: frac_of_nominal = {achieved / 9000.0:.4f}; frac of 4 x sustained bf16 = {achieved / (4 * pk['bf16_tflops_sustained']):.4f}",
                 "launches_timed": len(gemm_ms), "avg_launch_ms": round(avg_ms, 4),
+                **({"alone_on_the_step_s_sms": {"sms": 148 - args.ar_ctas, "us": round(alone_us, 1), "TFLOPs": round(flops / alone_us / 1e6, 1),
+                                                "frac": round(flops / alone_us / 1e6 / peak, 4),
+                                                "note": "the same kernel and shape alone, 10 launches in one CUDA graph; the in-step figure includes the moments "
+                                                        "when both row chunks' GEMMs share the SMs"}} if alone_us else {}),
                 "timing": "CUDA events around each launch " + ("in an instrumented eager pass after the timed region (the timed region replays a CUDA graph)"
                                                                if world > 1 else "inside the timed region")}
     line = {
