@@ -341,7 +341,7 @@ struct NxRing {
   }
 };
 
-template <int VPT, int QFMT>
+template <int VPT, int QFMT, bool SW>  // SW: the partial results are summed by the switch (multimem.ld_reduce), not from the ring
 __global__ void __launch_bounds__(544, 1) tp_norm_exchange_kernel(const NxParams q, int stages, int stage_bytes) {
   extern __shared__ __align__(128) uint8_t nx_smem[];
   __shared__ int abort_flag;
@@ -425,6 +425,21 @@ __global__ void __launch_bounds__(544, 1) tp_norm_exchange_kernel(const NxParams
     for (int base = blockIdx.x; base < rows_local; base += gridDim.x * kRows) {
       float r[kRows][VPT][8];
       float acc[kRows];
+      // the switch's sums of this round's vectors: all requested before the first is used (each takes a round trip through the switch)
+      uint4 xs[SW ? kRows : 1][SW ? VPT : 1];
+      if (SW && q.sum_peers) {
+#pragma unroll
+        for (int rw = 0; rw < kRows; ++rw) {
+          const int row = base + rw * (int)gridDim.x;
+#pragma unroll
+          for (int i = 0; i < VPT; ++i) {
+            const int v = tid + i * nthreads;
+            xs[SW ? rw : 0][SW ? i : 0] = make_uint4(0, 0, 0, 0);
+            if (row < rows_local && v < nvec)
+              multimem_ld_reduce_bf16x8(p.mc_ptr + q.partial_off + (((long long)row0 + row) * nvec + v) * 16, xs[SW ? rw : 0][SW ? i : 0]);
+          }
+        }
+      }
 #pragma unroll
       for (int rw = 0; rw < kRows; ++rw) {
         const int row = base + rw * (int)gridDim.x;
@@ -459,8 +474,8 @@ __global__ void __launch_bounds__(544, 1) tp_norm_exchange_kernel(const NxParams
               const uint32_t slot = (uint32_t)(v & (kNxSegVecs - 1));
               if (!q.sum_peers) {
                 xv = lds_128(sb + slot * 16);
-              } else if (p.reduce_in_switch) {
-                multimem_ld_reduce_bf16x8(p.mc_ptr + q.partial_off + (grow * nvec + v) * 16, xv);
+              } else if (SW) {
+                xv = xs[SW ? rw : 0][SW ? i : 0];
               } else {
                 float s8[8];
 #pragma unroll
@@ -699,20 +714,26 @@ extern "C" tf_status tf_allreduce_bf16(const uint64_t* buffer_ptrs, const uint64
   return TF_OK;
 }
 
-template <int VPT, int QFMT>
-static cudaError_t launch_norm_exchange_fmt(int grid, int threads, cudaStream_t stream, const NxParams& q, int stages, int stage_bytes) {
+template <int VPT, int QFMT, bool SW>
+static cudaError_t launch_norm_exchange_sw(int grid, int threads, cudaStream_t stream, const NxParams& q, int stages, int stage_bytes) {
   const size_t smem = (size_t)stages * stage_bytes + 16 * (size_t)stages;
   static thread_local int configured_dev = -1;  // per instantiation: the kernel may use all of the SM's shared memory
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (configured_dev != dev) {
-    e = cudaFuncSetAttribute(tp_norm_exchange_kernel<VPT, QFMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, kNxSmemBudget + 16 * kNxMaxStages);
+    e = cudaFuncSetAttribute(tp_norm_exchange_kernel<VPT, QFMT, SW>, cudaFuncAttributeMaxDynamicSharedMemorySize, kNxSmemBudget + 16 * kNxMaxStages);
     if (e != cudaSuccess) return e;
     configured_dev = dev;
   }
-  tp_norm_exchange_kernel<VPT, QFMT><<<grid, threads + 32, smem, stream>>>(q, stages, stage_bytes);
+  tp_norm_exchange_kernel<VPT, QFMT, SW><<<grid, threads + 32, smem, stream>>>(q, stages, stage_bytes);
   return cudaGetLastError();
+}
+
+template <int VPT, int QFMT>
+static cudaError_t launch_norm_exchange_fmt(int grid, int threads, cudaStream_t stream, const NxParams& q, int stages, int stage_bytes) {
+  if (q.sum_peers && q.ar.reduce_in_switch) return launch_norm_exchange_sw<VPT, QFMT, true>(grid, threads, stream, q, stages, stage_bytes);
+  return launch_norm_exchange_sw<VPT, QFMT, false>(grid, threads, stream, q, stages, stage_bytes);
 }
 
 template <int VPT>

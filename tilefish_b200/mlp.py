@@ -164,7 +164,8 @@ class MlpStack:
     """
 
     def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16,
-                 comm: str = "all_reduce", peer_path: str = "multicast_store", deliver_partials: bool = False) -> None:
+                 comm: str = "all_reduce", peer_path: str = "multicast_store", deliver_partials: bool = False,
+                 exclusive_gemms: bool = False) -> None:
         """``comm``: "all_reduce" (one NCCL bf16 all-reduce per block), "peer_all_reduce" (the same exchange by this package's
         own kernel over symmetric memory, see ``collective.PeerAllReduce``; ``sm_margin`` is also its CTA count) or
         "scatter_gather" (rows of the normalisation sharded over the ranks: reduce-scatter of the partial results +
@@ -174,8 +175,12 @@ class MlpStack:
         (fused_exchange, exact peer paths): the second GEMM's epilogue stores each rank's rows of the partial result straight into
         that rank's buffer (``tf_gemm_blockscaled_scatter``), so the exchange kernel sums local memory only; otherwise (the
         default: measured faster on two GPUs, where the epilogue's 16-byte peer stores slow the GEMM down), and for shapes that
-        GEMM splits along K, the exchange kernel pulls its rows from the peers with bulk copies. Same sums, same bytes."""
+        GEMM splits along K, the exchange kernel pulls its rows from the peers with bulk copies. Same sums, same bytes.
+        ``exclusive_gemms`` (fused_exchange with more than one chunk): the chunks' GEMMs run one chunk at a time (an event chain),
+        so that only the exchange kernel ever runs beside a GEMM. Off by default: on B200 it measured 2 % slower on two GPUs (the
+        tail of one chunk's GEMM no longer overlaps the head of the other's) and the same on eight."""
         self.layers = layers
+        self.exclusive_gemms = bool(exclusive_gemms)
         self.deliver_partials = bool(deliver_partials)
         self.delivered = False
         self.eps = eps
@@ -412,6 +417,19 @@ class MlpStack:
             ev.record(st)
             self._last_reduce = ev
 
+        last_gemms = [None]
+
+        def gemms_begin():
+            # One chunk's GEMMs at a time: only the exchange kernel then ever runs beside a GEMM (an option; see the constructor).
+            if self.exclusive_gemms and multi and last_gemms[0] is not None:
+                torch.cuda.current_stream().wait_event(last_gemms[0])
+
+        def gemms_end():
+            if self.exclusive_gemms and multi:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream())
+                last_gemms[0] = ev
+
         if multi:
             N.check(N.load().tf_set_sm_margin(self.sm_margin), "tf_set_sm_margin")
         try:
@@ -454,6 +472,7 @@ class MlpStack:
                                                             h_scratch=self._scratch[ci][key], amax=am[0:1] if am is not None else None, eps=self.eps,
                                                             fmt=fmt, channel=ci))
                         hq = K.BlockScaledTensor(fmt, (rows, h), v["codes"], v["scales"], v["gs"], "swizzled", gs_rows=r if fmt == "nvfp4" else 0)
+                        gemms_begin()
                         if fmt == "nvfp4":
                             a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", amax_out=am[1:2])
                             aq = K.quantize(a, fmt, amax=am[1:2])
@@ -464,6 +483,7 @@ class MlpStack:
                             K.gemm_blockscaled_scatter(aq, w.w_d, [p + v["off"][0] + rank * r * h * 2 for p in peer.buffer_ptrs], r, h)
                         else:
                             K.gemm_blockscaled(aq, w.w_d, out=v["partial"])
+                        gemms_end()
             for ci in range(c):
                 v = views[ci]
                 with torch.cuda.stream(streams[ci]):
