@@ -127,6 +127,25 @@ TF_API tf_status tf_residual_add_rmsnorm(const void* x, void* residual, const vo
                                   int32_t q_format, void* q_codes, void* q_scales, int32_t q_layout, const float* q_global_scale,
                                   float* out_amax, void* stream);
 
+/* Few rows (m <= the number of SMs, e.g. a decode step): residual_add_rmsnorm AND the BlockScaled quantization of its result in one
+ * launch, one CTA per row; what the reference's graph does with a kernel launch (python/src/tilefish/_cuda.py:356-458) plus a cast
+ * it types but does not run (python/src/tilefish/ops.py:556-559). Same arithmetic, order and roundings as tf_residual_add_rmsnorm
+ * followed by tf_quantize_*: the bytes are identical.
+ *   x         bf16 [m, d], or NULL when the input is given as split-K partial sums:
+ *   partials / splits   the f32 planes [splits][m][d] tf_gemm_blockscaled_partials left in its workspace: summed in split order,
+ *             multiplied by a_global_scale[a_global_scale_rows ? row / a_global_scale_rows : 0] * b_global_scale[0] (both NULL: 1)
+ *             and rounded to bf16, exactly as that GEMM's own reduction pass would have stored them
+ *   residual f32 [m, d] (updated in place), w bf16 [d], out bf16 [m, d] or NULL; d a multiple of 32
+ *   q_format  TF_FMT_*; q_codes, q_scales (swizzled) as tf_quantize_* writes them, EXCEPT that padding bytes of q_scales are not
+ *             touched: zero the buffer once when it is allocated
+ *   nvfp4: the tensor-wide scale amax / 2688 is formed inside the launch (the CTAs meet once at a bounded barrier; a timeout is
+ *             reported by tf_device_status) and stored to q_global_scale[0]; sync points at two 32-bit words (8-byte aligned) that
+ *             the caller zeroes before EVERY call (amax bits, arrivals). Other formats: q_global_scale and sync may be NULL. */
+TF_API tf_status tf_rmsnorm_quantize_rows(const void* x, const float* partials, int32_t splits, const float* a_global_scale,
+                                          const float* b_global_scale, int64_t a_global_scale_rows, void* residual, const void* w, void* out,
+                                          int64_t m, int64_t d, float eps, int32_t q_format, void* q_codes, void* q_scales,
+                                          float* q_global_scale, uint32_t* sync, void* stream);
+
 /* SiLU gate (README.md:83-84; the fused region of python/src/tilefish/_fusion.py):
  *   out[m, j] = bf16( silu(f32(gate[m, j])) * f32(up[m, j]) ), silu(x) = x * (1 / (1 + exp(-x))).
  *   gate, up bf16 [m, f] with row strides ldg, ldu (the column halves of a [m, 2f] tensor t are gate = t, up = t + f,
@@ -180,6 +199,15 @@ TF_API int64_t tf_gemm_static_scratch_bytes(void);
 TF_API tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
                                      const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n,
                                      int64_t k, int32_t format, int32_t epilogue, void* epilogue_arg, float* out_amax, void* stream);
+
+/* The first pass of a split-K problem only (epilogue TF_EPI_NONE): the f32 partial sums stay in the workspace as `*splits` planes
+ * [splits][m][n] for a consumer that sums them itself (tf_rmsnorm_quantize_rows: the few-rows step between two blocks, where a separate
+ * reduction launch costs as much as the arithmetic). No counterpart in the reference. Shapes that are not split along K
+ * (tf_gemm_splits == 1) are refused with TF_ERR_UNSUPPORTED. Other arguments as tf_gemm_blockscaled (one global scale for `a`). */
+TF_API int32_t tf_gemm_splits(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue);
+TF_API tf_status tf_gemm_blockscaled_partials(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
+                                              const void* b_scales, const float* b_global_scale, int64_t m, int64_t n, int64_t k, int32_t format,
+                                              void* workspace, int64_t workspace_bytes, int32_t* splits, void* stream);
 
 /* The GEMM with a scattered output: the tensor-parallel second GEMM (w_d split along K) whose epilogue delivers each row block of
  * its partial result straight to the rank that will sum it, so that no separate kernel has to pull the partial results across

@@ -48,6 +48,9 @@ SIGNATURES = {
     "tf_residual_add_rmsnorm": (c_int32, [_P, _P, _P, _P, c_int64, c_int64, c_float, c_int32, _P, _P, c_int32, _P, _P, _P]),
     "tf_silu_gate": (c_int32, [_P, _P, c_int64, c_int64, c_int64, c_int64, _P, c_int64, _P]),
     "tf_gemm_workspace_bytes": (c_int64, [c_int64, c_int64, c_int64, c_int32, c_int32]),
+    "tf_gemm_splits": (c_int32, [c_int64, c_int64, c_int64, c_int32, c_int32]),
+    "tf_gemm_blockscaled_partials": (c_int32, [_P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int32, _P, c_int64, _P, _P]),
+    "tf_rmsnorm_quantize_rows": (c_int32, [_P, _P, c_int32, _P, _P, c_int64, _P, _P, _P, c_int64, c_int64, c_float, c_int32, _P, _P, _P, _P, _P]),
     "tf_gemm_blockscaled": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, _P, _P, c_int64, _P, c_int64, _P]),
     "tf_gemm_static_scratch_bytes": (c_int64, []),
     "tf_gemm_blockscaled_static": (c_int32, [_P, _P, _P, _P, _P, _P, _P, c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, _P, _P, _P]),

@@ -1195,7 +1195,8 @@ static bool use_pair_kernel(const GemmParams& p, const SplitPlan& sp) {
 }
 
 template <int FMT>
-static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int epilogue, const SplitPlan& sp, cudaStream_t stream) {
+static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, GemmParams p, int epilogue, const SplitPlan& sp, cudaStream_t stream,
+                               bool partials_only = false) {
   if (sp.splits > 1) {
     // first pass: plain accumulation over all accumulator columns into the workspace; second pass: reduce + epilogue
     const int n_out = p.n;
@@ -1207,6 +1208,7 @@ static tf_status dispatch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, Gem
     p.q_codes = nullptr;  // the quantized copy is produced by the second pass
     tf_status st = sp.block_n == 128 ? launch_gemm<FMT, 128, TF_EPI_NONE, true>(ta, tb, p, stream) : launch_gemm<FMT, 256, TF_EPI_NONE, true>(ta, tb, p, stream);
     if (st != TF_OK) return st;
+    if (partials_only) return TF_OK;  // the caller's next kernel sums the planes (tf_gemm_blockscaled_partials)
     p.q_codes = qc;
     const int64_t total = (int64_t)p.m * (n_out >> 3);
     const int64_t need = (total + 255) / 256, cap = (int64_t)sm_count() * 8;
@@ -1324,6 +1326,11 @@ static tf_status static_scratch_address(void** out) {
   return TF_OK;
 }
 
+int32_t tf_gemm_splits(int64_t m, int64_t n, int64_t k, int32_t format, int32_t epilogue) {
+  if (m <= 0 || n <= 0 || k <= 0 || format < TF_FMT_MXFP8 || format > TF_FMT_NVFP4 || epilogue < TF_EPI_NONE || epilogue > TF_EPI_RESIDUAL) return 0;
+  return split_plan(m, n, format == TF_FMT_MXFP8 ? k : k / 2, epilogue).splits;
+}
+
 int64_t tf_gemm_static_scratch_bytes(void) { return kStaticScratchBytes; }
 
 tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
@@ -1347,18 +1354,19 @@ tf_status tf_gemm_blockscaled_static(const void* a_codes, const void* a_scales, 
 
 }  // extern "C"
 
-// Both GEMM entry points. `scatter_ptrs` (null for tf_gemm_blockscaled): the destinations of the row blocks, see GemmParams.
+// The GEMM entry points. `scatter_ptrs` (null for tf_gemm_blockscaled): the destinations of the row blocks, see GemmParams.
+// `partial_splits` (non-null for tf_gemm_blockscaled_partials): only the first pass of a split-K problem runs; receives the number of planes.
 static tf_status gemm_entry(const char* fn, const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes,
                             const void* b_scales, const float* b_global_scale, void* out, int64_t ldo, int64_t m, int64_t n, int64_t k, int32_t format,
                             int32_t epilogue, void* epilogue_arg, float* out_amax, void* q_codes, void* q_scales, int64_t a_global_scale_rows,
                             void* workspace, int64_t workspace_bytes, const uint64_t* scatter_ptrs, int32_t owners, int64_t rows_per_owner,
-                            void* stream_) {
+                            void* stream_, int32_t* partial_splits = nullptr) {
   cudaStream_t stream = (cudaStream_t)stream_;
   TF_CHECK_ARG(format >= TF_FMT_MXFP8 && format <= TF_FMT_NVFP4, "%s: unknown format %d", fn, format);
   TF_CHECK_ARG(epilogue >= TF_EPI_NONE && epilogue <= TF_EPI_RESIDUAL, "%s: unknown epilogue %d", fn, epilogue);
   TF_CHECK_ARG(m >= 0 && n > 0 && k > 0, "%s: bad shape m=%lld n=%lld k=%lld", fn, (long long)m, (long long)n, (long long)k);
   if (m == 0) return TF_OK;
-  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && (out || q_codes), "%s: null pointer", fn);
+  TF_CHECK_ARG(a_codes && a_scales && b_codes && b_scales && (out || q_codes || partial_splits), "%s: null pointer", fn);
   TF_CHECK_ARG((q_codes == nullptr) == (q_scales == nullptr), "%s: q_codes and q_scales go together", fn);
   if (q_codes) {
     if (format == TF_FMT_NVFP4)
@@ -1429,6 +1437,10 @@ static tf_status gemm_entry(const char* fn, const void* a_codes, const void* a_s
     p.scatter_rows = (int)rows_per_owner;
     for (int i = 0; i < owners; ++i) p.scatter_out[i] = reinterpret_cast<uint16_t*>(scatter_ptrs[i]);
   }
+  if (partial_splits) {
+    if (sp.splits <= 1) return fail(TF_ERR_UNSUPPORTED, "%s: this shape is not split along K (tf_gemm_splits == 1): there are no partial sums to leave", fn);
+    *partial_splits = sp.splits;
+  }
   p.splits = sp.splits;
   p.k_stages_per_split = sp.k_stages_per_split;
   p.ws = static_cast<float*>(workspace);
@@ -1440,9 +1452,9 @@ static tf_status gemm_entry(const char* fn, const void* a_codes, const void* a_s
     TF_CHECK_ALIGNED(workspace, 256, "workspace");
   }
   switch (format) {
-    case TF_FMT_MXFP8: return dispatch_gemm<TF_FMT_MXFP8>(ta, tb, p, epilogue, sp, stream);
-    case TF_FMT_MXFP4: return dispatch_gemm<TF_FMT_MXFP4>(ta, tb, p, epilogue, sp, stream);
-    default: return dispatch_gemm<TF_FMT_NVFP4>(ta, tb, p, epilogue, sp, stream);
+    case TF_FMT_MXFP8: return dispatch_gemm<TF_FMT_MXFP8>(ta, tb, p, epilogue, sp, stream, partial_splits != nullptr);
+    case TF_FMT_MXFP4: return dispatch_gemm<TF_FMT_MXFP4>(ta, tb, p, epilogue, sp, stream, partial_splits != nullptr);
+    default: return dispatch_gemm<TF_FMT_NVFP4>(ta, tb, p, epilogue, sp, stream, partial_splits != nullptr);
   }
 }
 
@@ -1455,6 +1467,15 @@ tf_status tf_gemm_blockscaled(const void* a_codes, const void* a_scales, const f
   clear_error();
   return gemm_entry(__func__, a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, out, ldo, m, n, k, format, epilogue, epilogue_arg,
                     out_amax, q_codes, q_scales, a_global_scale_rows, workspace, workspace_bytes, nullptr, 0, 0, stream);
+}
+
+tf_status tf_gemm_blockscaled_partials(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,
+                                       const float* b_global_scale, int64_t m, int64_t n, int64_t k, int32_t format, void* workspace,
+                                       int64_t workspace_bytes, int32_t* splits, void* stream) {
+  clear_error();
+  TF_CHECK_ARG(splits != nullptr, "%s: null pointer", __func__);
+  return gemm_entry(__func__, a_codes, a_scales, a_global_scale, b_codes, b_scales, b_global_scale, nullptr, n, m, n, k, format, TF_EPI_NONE, nullptr,
+                    nullptr, nullptr, nullptr, 0, workspace, workspace_bytes, nullptr, 0, 0, stream, splits);
 }
 
 tf_status tf_gemm_blockscaled_scatter(const void* a_codes, const void* a_scales, const float* a_global_scale, const void* b_codes, const void* b_scales,

@@ -408,6 +408,103 @@ def gemm_blockscaled_scatter(a: BlockScaledTensor, b: BlockScaledTensor, out_ptr
     )
 
 
+def gemm_splits(m: int, n: int, k: int, fmt: str, epilogue: str = "none") -> int:
+    """How many K ranges the GEMM cuts this problem into (1: not split; more than 1 only for few rows)."""
+    return int(N.load().tf_gemm_splits(m, n, k, FORMATS[fmt], EPILOGUES[epilogue]))
+
+
+class SplitKPartials:
+    """The f32 partial sums a split-K GEMM left in its workspace: ``splits`` planes [M, N], to be summed in split order, scaled by
+    the product of the operands' nvfp4 global scales and rounded to bf16 by the consumer (``rmsnorm_quantize_rows``)."""
+
+    __slots__ = ("workspace", "splits", "shape", "a_global_scale", "b_global_scale")
+
+    def __init__(self, workspace, splits, shape, a_global_scale, b_global_scale) -> None:
+        self.workspace, self.splits, self.shape = workspace, splits, shape
+        self.a_global_scale, self.b_global_scale = a_global_scale, b_global_scale
+
+
+def gemm_blockscaled_partials(a: BlockScaledTensor, b: BlockScaledTensor, *, workspace=None, stream=None) -> SplitKPartials:
+    """The first pass of a split-K GEMM only: ``deq(a) @ deq(b)^T`` stays in ``workspace`` as f32 partial sums for a consumer that
+    sums them itself. Only for shapes the GEMM splits along K (``gemm_splits(...) > 1``: few rows, long K)."""
+    torch = _torch()
+    _pre(isinstance(a, BlockScaledTensor) and isinstance(b, BlockScaledTensor), "a and b must be BlockScaledTensor", "dtype")
+    _pre(a.fmt == b.fmt, f"a is {a.fmt} but b is {b.fmt}: block-scaled formats must match exactly", "dtype", "b")
+    _pre(a.layout == "swizzled" and b.layout == "swizzled", "the GEMM consumes swizzled scales", "contiguous")
+    m, k = a.shape
+    n, kb = b.shape
+    _pre(k == kb, f"K differs: a is {a.shape}, b is {b.shape}", "shape", "b")
+    _pre(a.gs_rows == 0, "partial sums carry one global scale for the whole of a", "argument", "a")
+    _pre(gemm_splits(m, n, k, a.fmt) > 1, "this shape is not split along K: there are no partial sums to leave", "shape", "a")
+    for t, nm in ((a.codes, "a.codes"), (b.codes, "b.codes"), (a.scales, "a.scales"), (b.scales, "b.scales")):
+        _check(t, nm, torch.uint8, None, a.device)
+        _dense(t, nm)
+    if a.fmt == "nvfp4":
+        _pre(a.global_scale is not None and b.global_scale is not None, "nvfp4 operands need their global scales", "argument")
+    need = gemm_workspace_bytes(m, n, k, a.fmt, "none")
+    if workspace is None:
+        workspace = torch.empty(need, dtype=torch.uint8, device=a.device)
+    _pre(workspace.numel() * workspace.element_size() >= need, f"workspace: {need} bytes needed", "workspace", "workspace")
+    splits = ctypes.c_int32(0)
+    N.check(
+        N.load().tf_gemm_blockscaled_partials(
+            a.codes.data_ptr(), a.scales.data_ptr(), a.global_scale.data_ptr() if a.global_scale is not None else None,
+            b.codes.data_ptr(), b.scales.data_ptr(), b.global_scale.data_ptr() if b.global_scale is not None else None,
+            m, n, k, FORMATS[a.fmt], workspace.data_ptr(), workspace.numel() * workspace.element_size(), ctypes.byref(splits), _stream(stream)),
+        "tf_gemm_blockscaled_partials",
+    )
+    return SplitKPartials(workspace, int(splits.value), (m, n), a.global_scale, b.global_scale)
+
+
+def rmsnorm_quantize_rows(x, residual, w, eps: float, fmt: str, q_out: BlockScaledTensor, *, sync=None, out=None, stream=None) -> BlockScaledTensor:
+    """Few rows (at most one per SM): ``residual += x``, rmsnorm and the BlockScaled quantization of the result in ONE launch; the
+    same bytes as ``residual_add_rmsnorm`` followed by ``quantize``. ``x`` is a bf16 [M, D] tensor or the ``SplitKPartials`` of the
+    GEMM that produced it (then that GEMM's reduction pass is part of this launch too). ``q_out`` is preallocated storage whose
+    scale bytes were zeroed when it was allocated (padding is never written); for nvfp4 it carries the float32 [1] that receives
+    the tensor-wide scale, and ``sync`` is an int32 [2] device tensor the caller zeroes before every call."""
+    torch = _torch()
+    _pre(fmt in FORMATS, f"unknown block-scaled format {fmt!r}", "dtype", "fmt")
+    _check(residual, "residual", torch.float32, 2)
+    dev = residual.device
+    m, d = residual.shape
+    _check(w, "w", torch.bfloat16, 1, dev)
+    _dense(residual, "residual")
+    _dense(w, "w")
+    _pre(tuple(w.shape) == (d,), f"w: shape {tuple(w.shape)}, expected {(d,)}", "shape", "w")
+    _pre(d % 32 == 0, f"D={d} is not a multiple of 32", "divisible", "residual")
+    _pre(q_out.fmt == fmt and q_out.shape == (m, d) and q_out.layout == "swizzled", "q_out: wrong format or shape", "shape", "q_out")
+    xp, pp, splits, ags, bgs = None, None, 0, None, None
+    if isinstance(x, SplitKPartials):
+        _pre(x.shape == (m, d), f"partial sums of shape {x.shape}, expected {(m, d)}", "shape", "x")
+        pp, splits = x.workspace.data_ptr(), x.splits
+        if x.a_global_scale is not None:
+            ags, bgs = x.a_global_scale.data_ptr(), x.b_global_scale.data_ptr()
+    else:
+        _check(x, "x", torch.bfloat16, 2, dev)
+        _dense(x, "x")
+        _pre(tuple(x.shape) == (m, d), f"x: shape {tuple(x.shape)}, expected {(m, d)}", "shape", "x")
+        xp = x.data_ptr()
+    if out is not None:
+        _check(out, "out", torch.bfloat16, 2, dev)
+        _dense(out, "out")
+        _pre(tuple(out.shape) == (m, d), "out: wrong shape", "shape", "out")
+    if m == 0:
+        return q_out
+    gs_ptr, sync_ptr = None, None
+    if fmt == "nvfp4":
+        _pre(q_out.global_scale is not None and sync is not None, "nvfp4 needs q_out.global_scale and the zeroed sync words", "argument", "sync")
+        _check(sync, "sync", torch.int32, None, dev, align=8)
+        _pre(sync.numel() >= 2, "sync: two 32-bit words", "shape", "sync")
+        gs_ptr, sync_ptr = q_out.global_scale.data_ptr(), sync.data_ptr()
+    N.check(
+        N.load().tf_rmsnorm_quantize_rows(xp, pp, splits, ags, bgs, 0, residual.data_ptr(), w.data_ptr(), out.data_ptr() if out is not None else None,
+                                          m, d, float(eps), FORMATS[fmt], q_out.codes.data_ptr(), q_out.scales.data_ptr(),
+                                          gs_ptr, sync_ptr, _stream(stream)),
+        "tf_rmsnorm_quantize_rows",
+    )
+    return q_out
+
+
 def gemm(a, b: BlockScaledTensor, *, epilogue: str = "none", out=None, residual=None, a_global_scale=None, a_amax=None, amax_out=None,
          stream=None):
     """The library ``gemm``: ``a`` is bf16 [M, K] (quantized on the fly in b's format) or already a BlockScaledTensor."""

@@ -165,7 +165,7 @@ class MlpStack:
 
     def __init__(self, layers: List[MlpWeights], eps: float = 1e-6, group=None, chunks: int = 1, sm_margin: int = 16,
                  comm: str = "all_reduce", peer_path: str = "multicast_store", deliver_partials: bool = False,
-                 exclusive_gemms: bool = False) -> None:
+                 exclusive_gemms: bool = False, fuse_few_rows: bool = True) -> None:
         """``comm``: "all_reduce" (one NCCL bf16 all-reduce per block), "peer_all_reduce" (the same exchange by this package's
         own kernel over symmetric memory, see ``collective.PeerAllReduce``; ``sm_margin`` is also its CTA count) or
         "scatter_gather" (rows of the normalisation sharded over the ranks: reduce-scatter of the partial results +
@@ -178,9 +178,13 @@ class MlpStack:
         GEMM splits along K, the exchange kernel pulls its rows from the peers with bulk copies. Same sums, same bytes.
         ``exclusive_gemms`` (fused_exchange with more than one chunk): the chunks' GEMMs run one chunk at a time (an event chain),
         so that only the exchange kernel ever runs beside a GEMM. Off by default: on B200 it measured 2 % slower on two GPUs (the
-        tail of one chunk's GEMM no longer overlaps the head of the other's) and the same on eight."""
+        tail of one chunk's GEMM no longer overlaps the head of the other's) and the same on eight.
+        ``fuse_few_rows`` (one GPU, at most 128 rows, shapes whose second GEMM is split along K: the decode step): the reduction of
+        that GEMM's partial sums, the next block's residual add and rmsnorm and the quantization of its result are one launch
+        (``tf_rmsnorm_quantize_rows``) instead of three; same bytes."""
         self.layers = layers
         self.exclusive_gemms = bool(exclusive_gemms)
+        self.fuse_few_rows = bool(fuse_few_rows)
         self.deliver_partials = bool(deliver_partials)
         self.delivered = False
         self.eps = eps
@@ -232,11 +236,61 @@ class MlpStack:
             self._peer.arm_poll()
             return out
         if self.chunks <= 1:
+            if self.group is None and self._few_rows_applies(x):
+                return self._forward_few_rows(x, residual)
             slots = self._amax_slots(0, x.device)
             for w, am in zip(self.layers, slots):
                 x = decoder_block(x, residual, w, self.eps, group=self.group, scratch=self._scratch[0], amax=am)
             return x
         return self._forward_chunked(x, residual)
+
+    def _few_rows_applies(self, x) -> bool:
+        if not (self.fuse_few_rows and self.layers and x.dim() == 2 and 0 < x.shape[0] <= 128 and x.shape[1] % 32 == 0):
+            return False
+        w0 = self.layers[0]
+        m, h = x.shape
+        f = w0.w_d.shape[1]
+        same = all(w.fmt == w0.fmt and w.w_d.shape == w0.w_d.shape and w.w_gu.shape == w0.w_gu.shape for w in self.layers)
+        return same and w0.w_d.shape[0] == h and K.gemm_splits(m, h, f, w0.fmt) > 1
+
+    def _forward_few_rows(self, x, residual):
+        """The decode step on one GPU. Per block: rmsnorm_quantize_rows (fed by the bf16 input, or by the split-K partial sums of the
+        previous block's second GEMM) -> gemm + SiLU gate -> (quantize) -> gemm that leaves its partial sums; the last block's
+        second GEMM finishes its own sum. Three launches fewer per block than decoder_block, the same bytes."""
+        import torch
+
+        m, h = x.shape
+        w0 = self.layers[0]
+        fmt, f = w0.fmt, w0.w_d.shape[1]
+        key = ("few_rows", m, h, f, fmt, str(x.device))
+        st = self._scratch[0].get(key)
+        if st is None:
+            nv = fmt == "nvfp4"
+            st = self._scratch[0][key] = {
+                # the scale buffer is zeroed once: the kernel never writes its padding
+                "hq": K.BlockScaledTensor(fmt, (m, h), torch.empty((m, h // K.ELEMS_PER_BYTE[fmt]), dtype=torch.uint8, device=x.device),
+                                          torch.zeros(K.scale_bytes(fmt, m, h), dtype=torch.uint8, device=x.device),
+                                          torch.empty(1, dtype=torch.float32, device=x.device) if nv else None, "swizzled"),
+                "ws": torch.empty(K.gemm_workspace_bytes(m, h, f, fmt), dtype=torch.uint8, device=x.device),
+                "sync": torch.zeros(2 * len(self.layers), dtype=torch.int32, device=x.device) if nv else None,
+            }
+        if st["sync"] is not None:
+            st["sync"].zero_()
+        slots = self._amax_slots(0, x.device)
+        src, y = x, None
+        last = len(self.layers) - 1
+        for li, w in enumerate(self.layers):
+            hq = K.rmsnorm_quantize_rows(src, residual, w.w_n, self.eps, fmt, st["hq"], sync=st["sync"][2 * li:2 * li + 2] if st["sync"] is not None else None)
+            if fmt == "nvfp4":
+                a = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", amax_out=slots[li][1:2])
+                aq = K.quantize(a, fmt, amax=slots[li][1:2])
+            else:
+                _, aq = K.gemm_blockscaled(hq, w.w_gu, epilogue="silu_gate", quantize_out=True, want_bf16=False)
+            if li < last:
+                src = K.gemm_blockscaled_partials(aq, w.w_d, workspace=st["ws"])
+            else:
+                y = K.gemm_blockscaled(aq, w.w_d)
+        return y
 
     def _forward_chunked(self, x, residual):
         import torch
