@@ -121,7 +121,7 @@ def test_call_checker_refusals():
         @tilefish.kernel
         def bad3(x: Tensor[M, D, bf16], y: Tensor[M, D, f32]) -> Tensor[M, D, f32]:
             return x + y
-    with pytest.raises(TilefishTypeError, match="storage only"):
+    with pytest.raises(TilefishTypeError, match="storage dtype"):
         @tilefish.kernel
         def bad4(x: Tensor[M, D, e4m3]) -> Tensor[M, D, e4m3]:
             return x + x
@@ -547,3 +547,91 @@ def test_symbolic_divisibility_becomes_a_requirement_on_the_graph():
         @tilefish.graph
         def bad(x: Tensor[M, 100, bf16], w: Tensor[256, 100, bf16]):
             return gemm_plain(x, w)
+
+
+def test_tracer_rules_of_the_elementwise_language():
+    """The rules the reference's tracer tests pin (python/tests/test_trace.py), on values made by hand in a fresh trace."""
+    from tilefish_b200 import Out, i32
+    from tilefish_b200.ir import Scalar
+    from tilefish_b200.trace import Const, TraceContext
+
+    ctx = TraceContext("test", "graph")
+    n = [0]
+
+    def val(t, name=None, access="in"):
+        n[0] += 1
+        return ctx.new_value(t, name=name or f"p{n[0]}", access=access, is_param=True)
+
+    m = Dim("m")
+    x = val(Tensor[m, D, bf16])
+    r = 2 * x + 0.5  # python numbers adopt the tensor's dtype; the operand order of a reflected operator is kept
+    assert r.type == Tensor[m, D, bf16] and ctx.nodes[0].inputs == (Scalar(2.0, bf16), x) and ctx.nodes[1].inputs[1] == Scalar(0.5, bf16)
+    assert tilefish.silu(x).type == x.type and x.to(bf16) is x  # math functions take any float dtype; a cast to the same dtype is no node
+    before = len(ctx.nodes)
+    with pytest.raises(TilefishTypeError, match=r"add \(\+\): no implicit promotion"):
+        x + val(Tensor[m, D, f32])
+    with pytest.raises(TilefishTypeError, match=r"cannot broadcast .* dimension D vs m at axis -1"):
+        x * val(Tensor[m, bf16])
+    with pytest.raises(TilefishTypeError, match="is a float scalar"):
+        val(Tensor[m, i32]) + 0.5
+    with pytest.raises(TilefishTypeError, match=r"const 'eps' is const\[f32\] but the other operand has dtype bf16"):
+        x + Const("eps", 1e-6, f32)
+    with pytest.raises(TilefishTypeError, match="python number or a const parameter"):
+        x + True
+    for use in (lambda v: v ** 2, lambda v: abs(v), lambda v: v @ v, lambda v: len(v)):
+        with pytest.raises(TilefishTypeError, match="not supported in M1"):
+            use(x)
+    with pytest.raises(TilefishTypeError, match="truth value"):
+        bool(x)
+    assert len(ctx.nodes) == before  # a refused operation leaves nothing behind
+    # reductions follow numpy; no axis means all of them
+    y = val(Tensor[m, D, f32])
+    assert tilefish.sum(y).type == Tensor[f32] and y.mean(axis=1).type == Tensor[m, f32]
+    assert tilefish.max(y, axis=(0, 1), keepdims=True).type == Tensor[1, 1, f32]
+    with pytest.raises(TilefishTypeError, match="duplicate axes"):
+        tilefish.sum(y, axis=(0, -2))
+    # stores: an InOut parameter is read at its stored copy afterwards, an Out parameter is write-only and has no version
+    res = val(Tensor[m, D, f32], "res", "inout")
+    res[...] = res + 1
+    version = res.live
+    assert version is not res and ctx.nodes[-1].op == "store" and ctx.nodes[-1].outputs == (version,)
+    res * 2
+    assert ctx.nodes[-1].inputs[0] is version
+    out = val(Tensor[m, D, f32], "y", "out")
+    out[...] = y
+    assert ctx.nodes[-1].outputs == ()
+    with pytest.raises(TilefishTypeError, match="Out parameter 'y', which is write-only"):
+        out + 1
+    with pytest.raises(TilefishTypeError, match=r"store into 'res': expected Tensor\[m, D, f32\], got Tensor\[m, D, bf16\]"):
+        res[...] = x
+    with pytest.raises(TilefishTypeError, match="read-only"):
+        y[...] = y
+    # split: equal chunks or explicit sizes; an axis is always given
+    q, k = val(Tensor[m, 100, f32]).split([60, 40], axis=1)
+    assert q.type == Tensor[m, 60, f32].as_view() and k.shape[1] == 40
+    with pytest.raises(TilefishTypeError, match="add up to 90 but axis 1"):
+        val(Tensor[m, 100, f32]).split([60, 30], axis=1)
+    with pytest.raises(TilefishTypeError, match="needs a size and an axis"):
+        y.split(2)
+    with pytest.raises(TilefishTypeError, match="chunk type is invalid.*not divisible by block=32"):
+        val(Tensor[m, 128, mxfp8]).split(16, axis=1)
+    assert Out is not None
+
+
+def test_a_call_may_give_a_const_another_value_and_pass_its_own_const_on():
+    from tilefish_b200 import i32
+
+    @tilefish.library("scale_by")
+    def scale_by(x: Tensor[M, bf16], *, factor: const[f32] = 1.0, steps: const[i32] = 1) -> Tensor[M, bf16]: ...
+
+    @tilefish.graph
+    def g(x: Tensor[M, bf16], *, f: const[f32] = 3.0):
+        return scale_by(x, factor=2), scale_by(x), scale_by(x, factor=f)
+
+    assert [n.attrs["consts"] for n in g.graph.nodes] == [{"factor": 2.0, "steps": 1}, {"factor": 1.0, "steps": 1}, {"factor": 3.0, "steps": 1}]
+    assert isinstance(g.graph.nodes[0].attrs["consts"]["factor"], float)
+    with pytest.raises(TilefishTypeError, match="argument 'steps' is const.*needs an int"):
+
+        @tilefish.graph
+        def bad(x: Tensor[M, bf16]):
+            return scale_by(x, steps=1.5)

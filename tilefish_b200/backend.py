@@ -218,7 +218,7 @@ def compile_graph(op: GraphOp, fuse: bool = True) -> Tuple[List[Buffer], List[St
             if impl == "residual_add_rmsnorm":
                 args = {p.name if i > 2 else ("x", "residual", "w")[i]: name_of[v] for i, (p, v) in enumerate(zip(params, n.inputs))}
                 args["out"] = new_buffer(n.outputs[0])
-                st = Step(callee.name, "kernel", "tf_residual_add_rmsnorm", args, {"eps": float(callee.signature.consts[0].default)})
+                st = Step(callee.name, "kernel", "tf_residual_add_rmsnorm", args, {"eps": float(n.attrs.get("consts", {}).get(callee.signature.consts[0].name, callee.signature.consts[0].default))})
             else:
                 gv, uv = n.inputs
                 args = {"gate": name_of[gv], "up": name_of[uv], "out": new_buffer(n.outputs[0])}

@@ -185,7 +185,7 @@ def _substitute(x, env: Dict[Dim, Any]):
     return simplify(total)
 
 
-def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple[List[Value], Dict[Dim, Any], Tuple[TensorType, ...]]:
+def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple[List[Value], Dict[Dim, Any], Tuple[TensorType, ...], Dict[str, Any]]:
     sig = op.signature
     tensors = sig.tensors
     if len(args) > len(tensors):
@@ -220,9 +220,7 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
         for axis, (formal, actual) in enumerate(zip(p.type.shape, v.type.shape)):
             _unify(op.name, p.name, formal, actual, env, axis, v.type, bound_by)
         values.append(v)
-    for p in sig.consts:
-        if p.name in bound and bound[p.name] != p.default:
-            raise TilefishTypeError(f"{op.name}: const '{p.name}' is compiled in as {p.default!r}; a call may restate, not change, it")
+    consts = {p.name: (_const_argument(op, p, bound[p.name]) if p.name in bound else p.default) for p in sig.consts}
     # writing in place to a read-only input of the graph being traced would change the caller's tensor behind its back
     for p, v in zip(tensors, values):
         if p.access == "inout" and getattr(v, "is_param", False) and v.access == "in":
@@ -235,7 +233,23 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
     # an Out parameter the call does not pass is a result of the call: fresh storage, after the declared results, in declaration order
     rets += tuple(TensorType(tuple(_substitute(s, env) for s in p.type.shape), p.type.dtype, p.type.contiguous)
                   for p in tensors if p.access == "out" and p.name not in bound)
-    return values, env, rets
+    return values, env, rets, consts
+
+
+def _const_argument(op: "Op", p: Param, value):
+    """A const argument given at a call: a python number, or a const parameter of the declaration being traced (passed through with the
+    value it has there), as a value of the const's dtype."""
+    if isinstance(value, (Scalar, T.Const)):
+        value = value.value
+    dt = p.const_dtype
+    ok = isinstance(value, (int, float)) and not isinstance(value, bool)
+    if dt is not None and dt.is_int:
+        if not ok or isinstance(value, float):
+            raise TilefishTypeError(f"{op.name}: argument '{p.name}' is const[{dt}] and needs an int, got {value!r}")
+        return int(value)
+    if not ok:
+        raise TilefishTypeError(f"{op.name}: argument '{p.name}' is const[{dt}] and needs a number, got {value!r}")
+    return float(value) if dt is None or dt.is_float else value
 
 
 def _op_by_name(module: str, qualname: str):
@@ -277,15 +291,14 @@ class Op:
             from . import runtime
 
             return runtime.run(self, *args, **kwargs)
-        if ctx.kind != "graph":
-            raise TilefishTypeError(f"{self.name}: operators can only be called from a @graph body, not from the kernel '{ctx.name}'")
-        values, _, rets = check_call(self, args, kwargs)
+        # a kernel body may call a declared operator too (the call is traced as a node); such a kernel matches none of this backend's
+        # hand-written kernels, so running it is refused by the lowering, not here
+        values, _, rets, consts = check_call(self, args, kwargs)
         values = [ctx.latest(v) for v in values]  # a tensor an earlier in-place call updated is read at its current version
         attrs = self._call_attrs()
         # the call node as the reference prints it (python/src/tilefish/ir.py:133-206): after the declared results one output per InOut
-        # parameter (the version of the tensor the call leaves behind), the compiled-in consts, the names of the InOut parameters
+        # parameter (the version of the tensor the call leaves behind), the consts with the values this call gives them, the names of the InOut parameters
         updated = [(p, v) for p, v in zip(self.signature.tensors, values) if p.access == "inout"]
-        consts = {c.name: c.default for c in self.signature.consts}
         if consts:
             attrs["consts"] = consts
         if updated:

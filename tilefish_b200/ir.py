@@ -24,6 +24,14 @@ class Scalar:
     def __repr__(self) -> str:
         return f"{self.name}:{self.dtype}" if self.name else f"{self.value!r}:{self.dtype}"
 
+    def __eq__(self, o) -> bool:
+        if not isinstance(o, Scalar):
+            return NotImplemented
+        return (self.value, self.dtype, self.name) == (o.value, o.dtype, o.name) and type(self.value) is type(o.value)
+
+    def __hash__(self) -> int:
+        return hash((self.value, str(self.dtype), self.name))
+
 
 class Value:
     """An SSA value of a trace. Arithmetic and methods on it append nodes to the active trace (see trace.py)."""

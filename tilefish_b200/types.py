@@ -61,6 +61,10 @@ class TensorType:
     def as_view(self) -> "TensorType":
         return TensorType(self.shape, self.dtype, contiguous=False)
 
+    def materialized(self) -> "TensorType":
+        """The type of a dense copy: a view's contiguous twin, a contiguous type itself."""
+        return self if self.contiguous else TensorType(self.shape, self.dtype, contiguous=True)
+
     def with_dtype(self, dtype) -> "TensorType":
         return TensorType(self.shape, dtype, self.contiguous)
 
@@ -133,7 +137,8 @@ Out = _MarkFactory("out")
 
 
 class ConstType:
-    """``const[f32]``: a keyword-only scalar compiled into the kernel; a call may restate, not change, its default."""
+    """``const[f32]``: a keyword-only scalar of a declaration; a call inside a graph may give it another value than its default (the call
+    node records it), ``tilefish.run`` of a built plan may only restate the value the plan was built with."""
 
     __slots__ = ("dtype",)
 
