@@ -20,7 +20,6 @@ REF_TESTS = "/root/reference/python/tests"
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 TRITON = "names a Triton type or lowers through Triton: there is no Triton in this backend"
-EXTERN = "declares a tilefish.extern (Triton / CUDA source) operator: externs are outside this backend"
 
 # file -> (tests that must pass at least, {test id (prefix) -> why it cannot pass here})
 EXPECTED = {
@@ -32,18 +31,12 @@ EXPECTED = {
         "test_triton_scalar_names": TRITON,
     }),
     "test_copy.py": (31, {
-        "test_compile_specs_survive_copy_and_pickle": EXTERN,
+        "test_compile_specs_survive_copy_and_pickle": "tilefish.aot: compile specs of Triton kernels",
     }),
     "test_trace.py": (66, {
         "test_a_view_is_stored_into_an_inout_parameter_of_a_graph_body": "uses Value.permute: transposed views are not part of this backend's language",
     }),
-    "test_calls.py": (23, {
-        "test_out_parameters_are_results_and_dim_parameters_are_derived": EXTERN,
-        "test_extern_divisibility_violation_and_requirement": EXTERN,
-        "test_const_arguments_library_vs_extern": EXTERN,
-        "test_declaration_errors": "wording of two declaration errors",
-        "test_extern_declaration_errors": EXTERN,
-    }),
+    "test_calls.py": (28, {}),
 }
 
 

@@ -635,3 +635,43 @@ def test_a_call_may_give_a_const_another_value_and_pass_its_own_const_on():
         @tilefish.graph
         def bad(x: Tensor[M, bf16]):
             return scale_by(x, steps=1.5)
+
+
+def test_an_extern_kernel_is_declared_and_traced_but_not_lowered():
+    from tilefish_b200 import Out, Requirement
+
+    n = Dim("n", divisible_by=16)
+
+    @tilefish.extern(triton="my_kernels:gelu", grid=lambda n: (tilefish.cdiv(n, 1024),))
+    def gelu(x: Tensor[n, bf16], y: Out[Tensor[n, bf16]], n_elem: n, BLOCK: const = 1024): ...
+
+    @tilefish.graph
+    def g(x: Tensor[4096, bf16]):
+        return gelu(x)
+
+    (node,) = g.graph.nodes
+    assert node.attrs == {"kind": "extern", "triton": "my_kernels:gelu", "consts": {"BLOCK": 1024}}
+    assert node.inputs == (g.graph.inputs[0],) and g.graph.outputs[0].type == Tensor[4096, bf16]  # y is a result, n_elem is derived
+
+    s = Dim("s")
+
+    @tilefish.graph
+    def sym(x: Tensor[s, bf16]):
+        return gelu(x)
+
+    assert sym.graph.requirements == (Requirement(s, 16, "gelu: argument 'x'"),)
+    with pytest.raises(TilefishTypeError, match="constexpr 'BLOCK' is fixed to 1024 by the extern declaration"):
+
+        @tilefish.graph
+        def changed(x: Tensor[4096, bf16]):
+            return gelu(x, BLOCK=512)
+
+    with pytest.raises(TilefishDeclarationError, match="module:function"):
+        tilefish.extern(triton="no_colon")
+    with pytest.raises(TilefishDeclarationError, match="grid parameter 'q' is not a dimension"):
+
+        @tilefish.extern(triton="m:f", grid=lambda q: (q,))
+        def e3(x: Tensor[n, bf16]): ...
+
+    with pytest.raises(TilefishLoweringError, match="extern kernel"):
+        tilefish.plan(g)

@@ -19,7 +19,7 @@ from .errors import (  # noqa: F401
     TilefishTypeError,
 )
 
-from .decorators import GraphOp, KernelOp, LibraryOp, Op, graph, kernel, library  # noqa: F401,E402
+from .decorators import ExternOp, GraphOp, KernelOp, LibraryOp, Op, extern, graph, kernel, library  # noqa: F401,E402
 from .dims import Dim, DimExpr, cdiv  # noqa: F401,E402
 from .dtypes import BlockScaled, DType, bf16, bool_, e2m1, e4m3, e5m2, f16, f32, i32, i64, u8, ue8m0  # noqa: F401,E402
 from .ir import BucketRequirement, Graph, Node, Requirement, Scalar, Value  # noqa: F401,E402
@@ -37,7 +37,7 @@ __all__ = [
     "BlockScaled", "BucketRequirement", "ConstType", "DType", "Dim", "DimExpr", "Graph", "GraphOp", "InOut", "KernelOp", "LibraryOp", "Marked", "Node", "Op", "Out",
     "Requirement", "Scalar", "Tensor", "TensorType", "TilefishAttributeError", "TilefishBuildError", "TilefishDeclarationError", "TilefishError",
     "TilefishLoweringError", "TilefishManifestError", "TilefishPlanError", "TilefishPreconditionError", "TilefishRuntimeError", "TilefishSpecError",
-    "TilefishTypeError", "Value", "bf16", "bool_", "cdiv", "const", "contiguous", "e2m1", "e4m3", "e5m2", "exp", "f16", "gelu", "f32", "graph", "i32", "i64", "kernel",
+    "TilefishTypeError", "Value", "bf16", "bool_", "cdiv", "const", "contiguous", "e2m1", "e4m3", "e5m2", "exp", "extern", "f16", "gelu", "f32", "graph", "i32", "i64", "kernel",
     "library", "mean", "mxfp4", "mxfp8", "nvfp4", "rsqrt", "silu", "sqrt", "u8", "ue8m0",
 ]
 

@@ -13,7 +13,7 @@ also reduces the amax the quantizer needs.
 
 from typing import Any, Dict, List, Optional, Tuple
 
-from .decorators import GraphOp, KernelOp, LibraryOp
+from .decorators import ExternOp, GraphOp, KernelOp, LibraryOp
 from .dims import Dim, as_expr, evaluate
 from .dtypes import BlockScaled, bf16, f32
 from .errors import TilefishLoweringError, TilefishPlanError
@@ -212,6 +212,9 @@ def compile_graph(op: GraphOp, fuse: bool = True) -> Tuple[List[Buffer], List[St
         if n in skip:
             continue
         callee = n.callee
+        if isinstance(callee, ExternOp):
+            raise TilefishLoweringError(f"graph '{g.name}': '{callee.name}' is an extern kernel ({callee.triton}); this backend has no Triton and loads "
+                                        "no foreign binaries: only the hand-written sm_100a kernels run", rule="no-extern")
         if isinstance(callee, KernelOp):
             impl = match_kernel(callee)
             params = callee.signature.tensors

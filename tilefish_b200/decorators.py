@@ -14,7 +14,7 @@ import inspect
 from typing import Any, Dict, List, Optional, Tuple
 
 from . import trace as T
-from .dims import Dim, as_expr, divisible, simplify, symbols
+from .dims import Dim, DimExpr, as_expr, divisible, simplify, symbols
 from .dtypes import DType, same_format
 from .errors import TilefishDeclarationError, TilefishTypeError
 from .ir import Graph, Scalar, Value
@@ -22,15 +22,18 @@ from .types import ConstType, Marked, TensorType
 
 
 class Param:
-    __slots__ = ("name", "type", "access", "is_const", "const_dtype", "default")
+    __slots__ = ("name", "type", "access", "is_const", "const_dtype", "default", "dim")
 
     def __init__(self, name, type_=None, access="in", is_const=False, const_dtype=None, default=None):
         self.name, self.type, self.access = name, type_, access
         self.is_const, self.const_dtype, self.default = is_const, const_dtype, default
+        self.dim = None  # an extern stub's runtime dimension parameter (`n_elem: n`): derived from the tensors at a call
 
     def __repr__(self) -> str:
         if self.is_const:
-            return f"{self.name}: const[{self.const_dtype}] = {self.default!r}"
+            return f"{self.name}: const[{self.const_dtype}] = {self.default!r}" if self.const_dtype is not None else f"{self.name}: const = {self.default!r}"
+        if self.dim is not None:
+            return f"{self.name}: {self.dim}"
         t = repr(self.type)
         if self.access == "inout":
             t = f"InOut[{t}]"
@@ -46,7 +49,7 @@ class Signature:
 
     @property
     def tensors(self) -> Tuple[Param, ...]:
-        return tuple(p for p in self.params if not p.is_const)
+        return tuple(p for p in self.params if not p.is_const and p.dim is None)
 
     @property
     def consts(self) -> Tuple[Param, ...]:
@@ -67,6 +70,10 @@ def parse_signature(fn, what: str) -> Signature:
         if isinstance(ann, str):
             raise TilefishDeclarationError(f"{what} '{fn.__name__}': annotations must be evaluated at declaration; remove "
                                            "`from __future__ import annotations` from the declaring module")
+        if p.kind in (inspect.Parameter.VAR_POSITIONAL, inspect.Parameter.VAR_KEYWORD):
+            raise TilefishDeclarationError(f"{what} '{fn.__name__}': *args/**kwargs are not allowed: every parameter is declared with its type")
+        if what == "extern" and _extern_scalar(fn, name, p, params):
+            continue
         if isinstance(ann, TensorType):
             params.append(Param(name, ann, "in"))
         elif isinstance(ann, Marked):
@@ -77,8 +84,11 @@ def parse_signature(fn, what: str) -> Signature:
             if ann.dtype is None:
                 raise TilefishDeclarationError(f"{what} '{fn.__name__}': const parameter '{name}' needs a dtype (const[f32])")
             params.append(Param(name, None, "in", True, ann.dtype, p.default))
-        else:
+        elif ann is inspect.Parameter.empty:
             raise TilefishDeclarationError(f"{what} '{fn.__name__}': parameter '{name}' needs an annotation: Tensor[...], InOut[...], Out[...] or const[...]")
+        else:
+            raise TilefishDeclarationError(f"{what} '{fn.__name__}': parameter '{name}' has the unsupported annotation {ann!r}; a parameter is "
+                                           "Tensor[...], InOut[...], Out[...] or const[...]")
     ret = sig.return_annotation
     if ret is inspect.Signature.empty or ret is None:
         returns: Tuple[TensorType, ...] = ()
@@ -89,6 +99,27 @@ def parse_signature(fn, what: str) -> Signature:
     else:
         raise TilefishDeclarationError(f"{what} '{fn.__name__}': the return annotation must be a tensor type or a tuple of them")
     return Signature(params, returns)
+
+
+def _extern_scalar(fn, name: str, p, params: List[Param]) -> bool:
+    """The scalar parameters only an extern stub has: a runtime dimension (``n_elem: n``, derived from the tensors at a call) and a
+    constexpr (``BLOCK: const = 1024``, typed or not, positional, fixed by the declaration). Appends it and returns True."""
+    ann = p.annotation
+    if isinstance(ann, (Dim, DimExpr)):
+        e = as_expr(ann)
+        if e.is_static:
+            raise TilefishDeclarationError(f"extern '{fn.__name__}': parameter '{name}' is annotated with the static dimension {ann}; a size known at "
+                                           f"declaration is a constexpr: write `{name}: const = {ann}`")
+        q = Param(name, None, "in")
+        q.dim = ann
+        params.append(q)
+        return True
+    if isinstance(ann, ConstType):
+        if p.default is inspect.Parameter.empty:
+            raise TilefishDeclarationError(f"extern '{fn.__name__}': constexpr '{name}' needs a default: the value compiled into the binary")
+        params.append(Param(name, None, "in", True, ann.dtype, p.default))
+        return True
+    return False
 
 
 # ---- call type-checking: unify the callee's dimensions with the arguments' -------------------------------------------
@@ -220,7 +251,7 @@ def check_call(op: "Op", args: Tuple[Any, ...], kwargs: Dict[str, Any]) -> Tuple
         for axis, (formal, actual) in enumerate(zip(p.type.shape, v.type.shape)):
             _unify(op.name, p.name, formal, actual, env, axis, v.type, bound_by)
         values.append(v)
-    consts = {p.name: (_const_argument(op, p, bound[p.name]) if p.name in bound else p.default) for p in sig.consts}
+    consts = {p.name: (op.check_const(p, bound[p.name]) if p.name in bound else p.default) for p in sig.consts}
     # writing in place to a read-only input of the graph being traced would change the caller's tensor behind its back
     for p, v in zip(tensors, values):
         if p.access == "inout" and getattr(v, "is_param", False) and v.access == "in":
@@ -326,6 +357,10 @@ class Op:
     def _call_attrs(self) -> Dict[str, Any]:
         return {"kind": self.kind}
 
+    def check_const(self, p: Param, value):
+        """A const argument given at a call, as a value of the const's dtype."""
+        return _const_argument(self, p, value)
+
     def __repr__(self) -> str:
         return f"<{type(self).__name__} {self.name}{self.signature!r}>"
 
@@ -420,6 +455,20 @@ def kernel(fn=None, *, name: Optional[str] = None, num_warps: Optional[int] = No
     return wrap(fn) if callable(fn) else wrap
 
 
+def _results_are_determined(sig: Signature, what: str, name: str) -> None:
+    """An opaque operator's results may only mention dimensions that a call can read off its input tensors."""
+    known = set()
+    for p in sig.tensors:
+        if p.access != "out":
+            for sz in p.type.shape:
+                known.update(d.name for d in symbols(sz))
+    results = [(f"return value {i}", r) for i, r in enumerate(sig.returns)] + [(f"Out parameter '{p.name}'", p.type) for p in sig.tensors if p.access == "out"]
+    for label, t in results:
+        free = sorted({d.name for sz in t.shape for d in symbols(sz) if d.is_dynamic} - known)
+        if free:
+            raise TilefishDeclarationError(f"{what} '{name}': {label} mentions dimension(s) {', '.join(free)} that no input tensor determines")
+
+
 def library(name=None, *, acc: Optional[DType] = None, impl: Optional[str] = None, **ignored):
     """``@tilefish.library("gemm", acc=f32)``: a signature with an opaque body (``...``)."""
     if callable(name):
@@ -428,8 +477,59 @@ def library(name=None, *, acc: Optional[DType] = None, impl: Optional[str] = Non
     def wrap(f):
         sig = parse_signature(f, "library")
         if not sig.returns and not any(p.access != "in" for p in sig.tensors):
-            raise TilefishDeclarationError(f"library '{f.__name__}': needs a return type or an Out/InOut parameter")
+            raise TilefishDeclarationError(f"library '{f.__name__}': produces nothing: declare a return type (-> Tensor[...]) or an Out[...] / InOut[...] parameter")
+        _results_are_determined(sig, "library", f.__name__)
         return LibraryOp(f, name, sig, acc, impl)
+
+    return wrap
+
+
+class ExternOp(Op):
+    """A kernel that lives outside this package (``@tilefish.extern(triton="module:function", grid=...)``). It can be declared, called
+    from graph bodies and type-checked like any operator; this backend has no Triton and generates no code, so a graph that contains
+    one is refused when it is lowered."""
+
+    kind = "extern"
+
+    def __init__(self, fn, name, signature, triton: str, grid, options: Dict[str, Any]) -> None:
+        super().__init__(fn, name, signature)
+        self.triton, self.grid, self.options = triton, grid, options
+
+    def _call_attrs(self):
+        return {"kind": "extern", "triton": self.triton}
+
+    def check_const(self, p: Param, value):
+        if isinstance(value, (Scalar, T.Const)):
+            value = value.value
+        if value != p.default:
+            raise TilefishTypeError(f"{self.name}: constexpr '{p.name}' is fixed to {p.default} by the extern declaration (it is compiled into the "
+                                    f"binary) and cannot be changed to {value!r} at a call")
+        return value
+
+
+def extern(*, triton: Optional[str] = None, grid=None, num_warps: int = 4, name: Optional[str] = None, **options):
+    """``@tilefish.extern(triton="module:function", grid=lambda n: (cdiv(n, 1024),))``: the declaration of a kernel written elsewhere.
+    The stub lists the kernel's parameters: tensors (``Out[...]`` ones are the results of a call), runtime dimensions (``n_elem: n``)
+    and constexprs (``BLOCK: const = 1024``); it returns nothing. Declaring and tracing work here; running does not (no Triton)."""
+    if not isinstance(triton, str) or triton.count(":") != 1 or not all(triton.split(":")):
+        raise TilefishDeclarationError(f"extern: triton= names the kernel as 'module:function', got {triton!r}")
+    if not isinstance(num_warps, int) or num_warps <= 0 or num_warps & (num_warps - 1):
+        raise TilefishDeclarationError(f"extern: num_warps must be a power of two, got {num_warps!r}")
+
+    def wrap(f):
+        sig = parse_signature(f, "extern")
+        if sig.returns:
+            raise TilefishDeclarationError(f"extern '{f.__name__}': a kernel returns nothing: declare its results as Out[...] parameters")
+        dims = set()
+        for p in sig.params:
+            for sz in (p.type.shape if p.type is not None else ([p.dim] if p.dim is not None else [])):
+                dims.update(d.name for d in symbols(sz))
+        if callable(grid):
+            for q in inspect.signature(grid).parameters:
+                if q not in dims:
+                    raise TilefishDeclarationError(f"extern '{f.__name__}': grid parameter '{q}' is not a dimension of the signature ({', '.join(sorted(dims))})")
+        _results_are_determined(sig, "extern", f.__name__)
+        return ExternOp(f, name, sig, triton, grid, dict(options, num_warps=num_warps))
 
     return wrap
 
