@@ -511,6 +511,8 @@ def extern(*, triton: Optional[str] = None, grid=None, num_warps: int = 4, name:
     """``@tilefish.extern(triton="module:function", grid=lambda n: (cdiv(n, 1024),))``: the declaration of a kernel written elsewhere.
     The stub lists the kernel's parameters: tensors (``Out[...]`` ones are the results of a call), runtime dimensions (``n_elem: n``)
     and constexprs (``BLOCK: const = 1024``); it returns nothing. Declaring and tracing work here; running does not (no Triton)."""
+    if callable(triton) and getattr(triton, "__module__", None) and getattr(triton, "__name__", None):
+        triton = f"{triton.__module__}:{triton.__name__}"  # the kernel itself: recorded by reference, never called here
     if not isinstance(triton, str) or triton.count(":") != 1 or not all(triton.split(":")):
         raise TilefishDeclarationError(f"extern: triton= names the kernel as 'module:function', got {triton!r}")
     if not isinstance(num_warps, int) or num_warps <= 0 or num_warps & (num_warps - 1):
