@@ -513,7 +513,7 @@ def parity_check(torch, K, MLP, blocks, group, world, rank, dev, comm, ctas, pee
         # nvfp4, two blocks of the benchmark's shape. Where the GPU's and the host's bf16 activations differ by one ulp (accumulation order over
         # K = 8192 / 28672, the approximate exponential of the SiLU) an e2m1 code can flip or a block scale move by one e4m3 step, so the
         # difference is noise with a heavy tail: its maximum grows with the number of elements compared (measured 0.07-0.16 of max|ref| over
-        # 1-4 M elements), its bulk does not. The verdict therefore rests on the relative Frobenius error (<= 5e-2; measured 0.017-0.021) and on
+        # 1-4 M elements), its bulk does not. The check therefore rests on the relative Frobenius error (<= 5e-2; measured 0.017-0.021) and on
         # the 99.99th percentile of |d| (<= 2**-3 max|ref|), with the maximum only guarded against a gross error (<= 2**-1). For scale: two runs
         # whose inputs differ by one bf16 ulp are 7e-2 apart, any nvfp4 run is 0.19 from the unquantized arithmetic, and a wrong exchange (a
         # rank's partial result missing) is beyond 0.5. With the switch's own reduction, whose sums are one bf16 step off in a fifth of the
