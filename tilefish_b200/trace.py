@@ -306,6 +306,24 @@ def split(x: Value, size=_MISSING, axis=_MISSING) -> Tuple[Value, ...]:
     return ctx.emit("split", (x,), tuple(types), {"axis": ax, "sizes": tuple(sizes)})
 
 
+def permute(x: Value, *axes) -> Value:
+    """A transposed view: the axes in another order (a strided view; nothing is copied)."""
+    ctx = _ctx_of(x) if isinstance(x, Value) else None
+    x = _read(x, ctx, "permute")
+    if len(axes) == 1 and isinstance(axes[0], (tuple, list)):
+        axes = tuple(axes[0])
+    rank = x.type.rank
+    if not all(isinstance(a, int) and not isinstance(a, bool) for a in axes):
+        raise TilefishTypeError(f"permute: axes must be ints, got {axes!r}")
+    norm = tuple(a + rank if a < 0 else a for a in axes)
+    if sorted(norm) != list(range(rank)):
+        raise TilefishTypeError(f"permute: {axes!r} is not a permutation of the {rank} axes of {x.type!r}")
+    if norm == tuple(range(rank)):
+        return x
+    t = TensorType(tuple(x.type.shape[a] for a in norm), x.type.dtype, contiguous=False)
+    return ctx.emit("permute", (x,), (t,), {"axes": norm})[0]
+
+
 def store(target: Value, value) -> None:
     ctx = _ctx_of(target)
     what = f"store into '{target.name}'" if target.name else f"store into {target.ref}"
@@ -394,6 +412,7 @@ def _install() -> None:
     for name in ("__invert__", "__and__", "__rand__", "__or__", "__ror__", "__xor__", "__rxor__"):
         setattr(Value, name, refuse("bitwise operators are not supported: a tensor of numbers is not a mask"))
     Value.reshape = refuse("reshape is not part of this backend's language")
+    Value.permute = lambda self, *axes: permute(self, *axes)
 
     def missing(self, name):
         raise TilefishAttributeError(f"traced values have no attribute {name!r}")
